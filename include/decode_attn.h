@@ -1,0 +1,168 @@
+/*
+ * decode_attn.h - C ABI of the B200 (sm_100a) generation-phase attention over a paged KV cache.
+ *
+ * Drop-in boundary for the generation branch of the reference's GPT attention plugin:
+ *   GPTAttentionPluginCommon::enqueueGeneration
+ *       cpp/tensorrt_llm/plugins/gptAttentionCommon/gptAttentionCommon.cpp:1159-1364
+ * i.e. everything that branch does today through masked_multihead_attention()
+ *   (cpp/tensorrt_llm/kernels/decoderMaskedMultiheadAttention.h:230-243) or DecoderXQARunner::dispatch
+ *   (cpp/tensorrt_llm/kernels/decoderMaskedMultiheadAttention/decoderXQARunner.h:172-181):
+ * for every sequence, append the new token's K/V to its cache block (quantising on write),
+ * then compute softmax(q K^T / (sqrt(Dh) q_scaling)) V over past + new token, reading the paged,
+ * optionally INT8 / FP8-E4M3 cache through the per-sequence block-pointer table.
+ *
+ * Plain C: pointers and sizes only, no C++/torch types.  All entry points return an int status
+ * (DX_OK == 0); nothing throws across the boundary, nothing calls exit().
+ *
+ * Ownership: the caller owns every buffer (packed QKV, KV pool, pointer table, scales, output,
+ * workspace).  dx_attn_enqueue_generation() is asynchronous on the given stream, allocates no device
+ * memory and never synchronises.  The KV pool is mutated in place (new token appended), as in the
+ * reference.
+ */
+#ifndef DECODE_ATTN_H_
+#define DECODE_ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DX_ABI_VERSION 1
+
+/* Status codes. */
+enum
+{
+    DX_OK = 0,
+    DX_ERR_BAD_ARG = 1,     /* null / misaligned pointer, negative size, inconsistent lengths           */
+    DX_ERR_UNSUPPORTED = 2, /* head size / dtype / feature outside what this library implements         */
+    DX_ERR_WORKSPACE = 3,   /* workspace smaller than dx_attn_workspace_size() asks for                 */
+    DX_ERR_CUDA = 4,        /* a CUDA runtime call failed; dx_attn_last_cuda_error() has the code       */
+    DX_ERR_TIMEOUT = 5,     /* a bounded device-side wait gave up (reported by dx_attn_device_status)    */
+    DX_ERR_BOUNDS = 6       /* dx_attn_validate(): a block pointer or length is outside the given pool  */
+};
+
+/* Activation dtype (reference: plugin field "type_id", nvinfer1::DataType kHALF / kBF16). */
+enum
+{
+    DX_DTYPE_FP16 = 0,
+    DX_DTYPE_BF16 = 1
+};
+
+/* KV-cache quantisation bits, same values as tensorrt_llm::common::QuantMode
+ * (cpp/tensorrt_llm/common/quantization.h:79-87, tensorrt_llm/quantization/mode.py:47-49). */
+#define DX_QUANT_INT8_KV_CACHE (1 << 6)
+#define DX_QUANT_FP8_KV_CACHE (1 << 7)
+
+/* Static attributes.  Field names follow the plugin's creator fields
+ * (cpp/tensorrt_llm/plugins/gptAttentionCommon/gptAttentionCommon.cpp:1558-1596). */
+typedef struct dx_attn_config
+{
+    uint32_t struct_size; /* = sizeof(dx_attn_config); lets the struct grow compatibly */
+    int32_t layer_idx;
+    int32_t num_heads;    /* q heads on THIS rank (already divided by tp_size, as the plugin is built) */
+    int32_t num_kv_heads; /* kv heads on this rank; num_heads % num_kv_heads == 0                     */
+    int32_t head_size;    /* 64 or 128                                                                */
+    float q_scaling;      /* softmax scale = 1 / (sqrt(head_size) * q_scaling)                        */
+    int32_t tp_size;      /* recorded only: heads are sharded by the caller, no communication here    */
+    int32_t tp_rank;
+    int32_t multi_block_mode;    /* 0: one CTA walks a whole sequence; 1: split-K + LSE merge allowed  */
+    int32_t enable_xqa;          /* accepted for compatibility, ignored                                */
+    int32_t kv_cache_quant_mode; /* 0, DX_QUANT_INT8_KV_CACHE or DX_QUANT_FP8_KV_CACHE                */
+    int32_t paged_kv_cache;      /* must be 1                                                          */
+    int32_t tokens_per_block;    /* power of two, 16..256                                              */
+    int32_t type_id;             /* DX_DTYPE_FP16 / DX_DTYPE_BF16                                      */
+    int32_t device;              /* CUDA device ordinal this handle launches on                        */
+} dx_attn_config;
+
+/* Per-call arguments.  Field names and meaning follow
+ * GPTAttentionPluginCommon::EnqueueGenerationParams
+ *   (cpp/tensorrt_llm/plugins/gptAttentionCommon/gptAttentionCommon.h:127-166)
+ * and the plugin's input list (cpp/tensorrt_llm/plugins/gptAttentionPlugin/gptAttentionPlugin.h:43-68). */
+typedef struct dx_attn_generation_params
+{
+    uint32_t struct_size; /* = sizeof(dx_attn_generation_params) */
+    /* device, T [num_requests, (num_heads + 2*num_kv_heads) * head_size]: Q | K | V of the new token
+     * (bias / rotary embedding already applied). */
+    const void* attention_input;
+    /* device, int32 [num_requests]: sequence length INCLUDING the new token; the new token is
+     * written at cache index sequence_lengths[b] - 1. */
+    const int32_t* sequence_lengths;
+    /* host, int32 [num_requests]: past length of every sequence (== sequence_lengths[b] - 1).
+     * Used on the host to size the launch; may be NULL if past_kv_length is given. */
+    const int32_t* host_past_key_value_lengths;
+    /* max over the batch of the past length (the plugin computes it from the host array,
+     * gptAttentionPlugin.cpp:558-563).  Ignored when host_past_key_value_lengths != NULL. */
+    int32_t past_kv_length;
+    int32_t beam_width;                   /* must be 1                                              */
+    int32_t num_requests;                 /* batch                                                  */
+    int32_t max_blocks_per_sequence;      /* M: row length of the pointer table                     */
+    int32_t max_attention_window;         /* cache capacity in tokens; must be >= past length + 1   */
+    int32_t cyclic_attention_window_size; /* must be >= past length + 1 (no wrap implemented)       */
+    int32_t sink_token_length;            /* must be 0                                              */
+    /* device, int64 [num_requests, 2, M]: KVBlockArray::data for this layer - K row then V row of
+     * device pointers per sequence (cpp/tensorrt_llm/kernels/kvCacheUtils.h:36-153). */
+    const int64_t* block_pointers;
+    /* optional host mirror of block_pointers (plugin input host_kv_cache_block_pointers); only
+     * used by dx_attn_validate(). */
+    const int64_t* host_block_pointers;
+    const float* kv_scale_orig_quant; /* device float[1]: multiply to quantise                     */
+    const float* kv_scale_quant_orig; /* device float[1]: multiply to dequantise                   */
+    void* context_buf;                /* device, T [num_requests, num_heads * head_size]: output   */
+    void* workspace;                  /* device, >= dx_attn_workspace_size(); 128-byte aligned      */
+    size_t workspace_bytes;
+    const int32_t* cache_indir; /* must be NULL (beam search not implemented)                      */
+} dx_attn_generation_params;
+
+typedef struct dx_attn dx_attn_t;
+
+/* Replaces GPTAttentionPluginCommon's constructor checks + initialize()
+ * (gptAttentionCommon.cpp:445-464, :1423-1490).  Queries the device (SM count, shared memory),
+ * sets kernel attributes and allocates one 256-byte device status word. */
+int dx_attn_create(const dx_attn_config* config, dx_attn_t** out);
+void dx_attn_destroy(dx_attn_t* handle);
+
+/* Replaces GPTAttentionPluginCommon::getWorkspaceSizeForGeneration (gptAttentionCommon.cpp:585-626).
+ * Upper bound for any call with num_requests <= batch; 0 when multi_block_mode is off. */
+size_t dx_attn_workspace_size(const dx_attn_t* handle, int32_t batch, int32_t max_past_len);
+
+/* Replaces GPTAttentionPluginCommon::enqueueGeneration (gptAttentionCommon.cpp:1159-1364). */
+int dx_attn_enqueue_generation(dx_attn_t* handle, const dx_attn_generation_params* params, void* cuda_stream);
+
+/* Same call for callers whose step inputs live in HOST memory (pinned or pageable): copies
+ * attention_input, sequence_lengths and block_pointers to device staging owned by the handle
+ * (grown on demand, the only allocation this library ever makes after create), runs the step and
+ * copies context_buf back to the host pointer.  All of params' attention_input, sequence_lengths,
+ * block_pointers and context_buf are HOST pointers here; the scales, the KV pool and the workspace
+ * stay on the device.  Asynchronous on the stream unless sync != 0.  Mirrors what the reference
+ * runtime does every step before enqueueV3 (tensorrt_llm/runtime/generation.py:2219-2221). */
+int dx_attn_enqueue_generation_host(
+    dx_attn_t* handle, const dx_attn_generation_params* params, void* cuda_stream, int32_t sync);
+
+/* Host-side check of a block-pointer table against the pool it must point into; launches nothing.
+ * Stands in for the bounds checking the reference does not have (its kernels trust the table). */
+int dx_attn_validate(const dx_attn_t* handle, const int64_t* host_block_pointers,
+    const int32_t* host_past_key_value_lengths, int32_t num_requests, int32_t max_blocks_per_sequence,
+    const void* pool_base, size_t pool_bytes);
+
+/* Number of split-K partitions and tokens per partition the next enqueue would use for this batch /
+ * max past length (reference analogue: multi_block_grid_setup,
+ * cpp/tensorrt_llm/kernels/decoderMaskedMultiheadAttention/decoderMaskedMultiheadAttentionLaunch.h:94-143). */
+int dx_attn_plan(const dx_attn_t* handle, int32_t batch, int32_t max_past_len, int32_t* num_partitions,
+    int32_t* tokens_per_partition, int32_t* kernel_kind);
+
+/* Reads (synchronously) and clears the device status word: DX_OK or DX_ERR_TIMEOUT. */
+int dx_attn_device_status(dx_attn_t* handle);
+/* Last cudaError_t seen by this handle (0 if none). */
+int dx_attn_last_cuda_error(const dx_attn_t* handle);
+/* Kernels launched by this handle since creation (for launch accounting in benchmarks). */
+int64_t dx_attn_launch_count(const dx_attn_t* handle);
+
+const char* dx_strerror(int status);
+int dx_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DECODE_ATTN_H_ */

@@ -1,0 +1,125 @@
+/*
+ * TEST INFRASTRUCTURE ONLY - never linked into, imported by or called from the product library.
+ *
+ * Thin driver around the reference's own masked-multihead-attention (MMHA) CUDA source, compiled
+ * for sm_100a straight from the reference tree (nothing is copied: the reference headers are
+ * #included from where they lie, see oracle/Makefile).  It instantiates only the paged-KV,
+ * self-attention launcher for one (T, Dh) pair per translation unit (REF_T / REF_DH) and exposes
+ * a C entry point that fills Masked_multihead_attention_params the way
+ * cpp/tensorrt_llm/plugins/gptAttentionCommon/gptAttentionCommon.cpp:243-349
+ * (fusedQKV_masked_attention_dispatch) and :1159-1364 (enqueueGeneration) do.
+ *
+ * Used by the GPU parity tests to pin the oracle (KV bytes written, paging, attention output)
+ * against the reference kernel itself, and by bench.py as the "reference kernel recompiled for
+ * B200" timing line.
+ */
+#include "tensorrt_llm/kernels/decoderMaskedMultiheadAttention/decoderMaskedMultiheadAttentionLaunch.h"
+
+#include <cstdint>
+#include <cstring>
+
+#ifndef REF_DH
+#error "REF_DH must be defined"
+#endif
+
+#if REF_T_IS_BF16
+using RefT = __nv_bfloat16;
+#define REF_FN(name) name##_bf16
+#else
+using RefT = uint16_t; // the reference spells fp16 as uint16_t in MMHA
+#define REF_FN(name) name##_fp16
+#endif
+
+#define REF_CAT2(a, b) a##_##b
+#define REF_CAT(a, b) REF_CAT2(a, b)
+
+namespace tensorrt_llm
+{
+namespace kernels
+{
+namespace mmha
+{
+template void mmha_launch_kernel<RefT, KVBlockArray, Masked_multihead_attention_params<RefT>, REF_DH, false>(
+    const Masked_multihead_attention_params<RefT>& params, const KVBlockArray& kv_cache_buffer,
+    const KVLinearBuffer& shift_k_cache, const cudaStream_t& stream);
+} // namespace mmha
+} // namespace kernels
+} // namespace tensorrt_llm
+
+using namespace tensorrt_llm::kernels;
+
+/* Returns 0 on success, a cudaError_t value otherwise.
+ * workspace layout (caller allocates, 128-byte aligned sub-buffers, same order as the plugin):
+ *   partial_out [tiles,B,H,Dh] T | partial_sum [B*H*tiles] f32 | partial_max [B*H*tiles] f32 | block_counter [B*H] i32
+ * tiles == 0 disables multi-block mode. */
+extern "C" int REF_CAT(REF_FN(ref_mmha), REF_DH)(const void* qkv, void* out, const int32_t* sequence_length_dev,
+    int64_t* block_pointers_dev, int32_t batch, int32_t num_heads, int32_t num_kv_heads, int32_t max_blocks_per_seq,
+    int32_t tokens_per_block, int32_t max_attention_window, int32_t past_kv_length, float q_scaling,
+    const float* kv_scale_orig_quant_dev, const float* kv_scale_quant_orig_dev, int32_t int8_kv, int32_t fp8_kv,
+    int32_t tiles, void* workspace, int32_t sm_count, cudaStream_t stream)
+{
+    const int Dh = REF_DH;
+    const size_t elem = (int8_kv || fp8_kv) ? 1 : sizeof(RefT);
+    KVBlockArray kv(batch, max_blocks_per_seq, tokens_per_block, (int32_t) (num_kv_heads * Dh * elem),
+        max_attention_window, /*sink*/ 0, false);
+    kv.data = block_pointers_dev;
+    KVLinearBuffer shift_k;
+
+    Masked_multihead_attention_params<RefT> p;
+    memset(&p, 0, sizeof(p));
+    const int hq = num_heads * Dh, hkv = num_kv_heads * Dh;
+    p.out = reinterpret_cast<RefT*>(out);
+    p.q = reinterpret_cast<const RefT*>(qkv);
+    p.k = p.q + hq;
+    p.v = p.q + hq + hkv;
+    p.int8_kv_cache = int8_kv != 0;
+    p.fp8_kv_cache = fp8_kv != 0;
+    if (int8_kv || fp8_kv)
+    {
+        p.kv_scale_orig_quant = kv_scale_orig_quant_dev;
+        p.kv_scale_quant_orig = kv_scale_quant_orig_dev;
+    }
+    p.stride = hq + 2 * hkv;
+    p.batch_size = batch;
+    p.beam_width = 1;
+    p.max_attention_window_size = max_attention_window;
+    p.cyclic_attention_window_size = max_attention_window;
+    p.sink_token_length = 0;
+    p.length_per_sample = sequence_length_dev;
+    p.timestep = past_kv_length;
+    p.num_heads = num_heads;
+    p.num_kv_heads = num_kv_heads;
+    p.hidden_size_per_head = Dh;
+    p.position_embedding_type = PositionEmbeddingType::kLEARNED_ABSOLUTE;
+    p.inv_sqrt_dh = 1.F / (sqrtf((float) Dh) * q_scaling);
+    p.multi_processor_count = sm_count;
+    p.multi_block_mode = tiles > 1;
+    if (tiles > 1)
+    {
+        auto up = [](size_t x) { return (x + 127) / 128 * 128; };
+        char* w = reinterpret_cast<char*>(workspace);
+        size_t off = 0;
+        p.partial_out = reinterpret_cast<RefT*>(w + off);
+        off += up(sizeof(RefT) * (size_t) batch * num_heads * Dh * tiles);
+        p.partial_sum = reinterpret_cast<float*>(w + off);
+        off += up(sizeof(float) * (size_t) batch * num_heads * tiles);
+        p.partial_max = reinterpret_cast<float*>(w + off);
+        off += up(sizeof(float) * (size_t) batch * num_heads * tiles);
+        p.block_counter = reinterpret_cast<int*>(w + off);
+        p.min_seq_len_tile = 1;
+        p.max_seq_len_tile = tiles;
+        cudaError_t e = cudaMemsetAsync(p.block_counter, 0, sizeof(int) * (size_t) batch * num_heads, stream);
+        if (e != cudaSuccess)
+            return (int) e;
+    }
+    try
+    {
+        mmha::mmha_launch_kernel<RefT, KVBlockArray, Masked_multihead_attention_params<RefT>, REF_DH, false>(
+            p, kv, shift_k, stream);
+    }
+    catch (...)
+    {
+        return -1;
+    }
+    return (int) cudaGetLastError();
+}

@@ -1,0 +1,523 @@
+// C-ABI implementation: argument checking, launch planning (split-K), workspace carving and the
+// kernel launches for the generation-phase attention.  Host logic mirrors
+//   GPTAttentionPluginCommon::enqueueGeneration
+//     cpp/tensorrt_llm/plugins/gptAttentionCommon/gptAttentionCommon.cpp:1159-1364
+// and the launcher side of the reference kernels
+//     cpp/tensorrt_llm/kernels/decoderMaskedMultiheadAttention/decoderMaskedMultiheadAttentionLaunch.h:94-295.
+#include <algorithm>
+#include <atomic>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+
+#include "../../include/decode_attn.h"
+#include "dx_launch.h"
+#include "dx_merge_kernel.cuh"
+
+using namespace dx;
+
+namespace
+{
+
+enum KernelKind : int
+{
+    KIND_MHA = 0, // CUDA-core kernel, one CTA per q head
+    KIND_GQA = 1  // tensor-core kernel, one CTA per kv head (x 16-head slice)
+};
+
+struct Plan
+{
+    int kind = KIND_MHA;
+    int hgroups = 1;    // 16-head slices per kv head (GQA kernel)
+    bool heads16 = false;
+    int rows = 0;       // grid.y * grid.z
+    int nsplit = 1;     // grid.x
+    int chunk_tokens = 0;
+    size_t part_o_bytes = 0, part_ml_bytes = 0;
+    size_t workspace() const
+    {
+        return part_o_bytes + part_ml_bytes;
+    }
+};
+
+size_t align_up(size_t x, size_t a)
+{
+    return (x + a - 1) / a * a;
+}
+
+} // namespace
+
+struct dx_attn
+{
+    dx_attn_config cfg{};
+    int sm_count = 0;
+    int max_smem_optin = 0;
+    int cache_kind = CACHE_T;
+    int tpb_log2 = 0;
+    int group = 1; // q heads per kv head
+    int waves = 6; // split-K target: CTAs ~ waves * resident CTAs
+    int min_chunk = 512;
+    KernelInfo k_mha{}, k_gqa8{}, k_gqa16{}, k_merge{};
+    int32_t* status_dev = nullptr;
+    int last_cuda_error = 0;
+    std::atomic<int64_t> launches{0};
+    // staging for the host-buffer entry point
+    void* stage_dev = nullptr;
+    size_t stage_bytes = 0;
+};
+
+namespace
+{
+
+Plan make_plan(const dx_attn* h, int batch, int max_past_len)
+{
+    Plan p;
+    const dx_attn_config& c = h->cfg;
+    const bool grouped = h->group > 1 && h->cache_kind != CACHE_T && c.tokens_per_block >= 32;
+    p.kind = grouped ? KIND_GQA : KIND_MHA;
+    int resident = 2;
+    if (grouped)
+    {
+        p.hgroups = (h->group + 15) / 16;
+        p.heads16 = h->group > 8;
+        p.rows = batch * c.num_kv_heads * p.hgroups;
+        resident = 2;
+    }
+    else
+    {
+        p.rows = batch * c.num_heads;
+        resident = 3;
+    }
+    const int total = max_past_len + 1;
+    int n = 1;
+    if (c.multi_block_mode)
+    {
+        const long target = (long) h->sm_count * resident * h->waves;
+        n = (int) ((target + p.rows - 1) / std::max(1, p.rows));
+        n = std::min(n, (total + h->min_chunk - 1) / h->min_chunk);
+        n = std::max(n, 1);
+    }
+    int chunk = (total + n - 1) / n;
+    chunk = (int) align_up((size_t) chunk, 128);
+    p.chunk_tokens = chunk;
+    p.nsplit = (total + chunk - 1) / chunk;
+    if (p.nsplit > 1)
+    {
+        const size_t qrows = (size_t) batch * c.num_heads;
+        p.part_o_bytes = align_up(qrows * p.nsplit * c.head_size * sizeof(float), 128);
+        p.part_ml_bytes = align_up(qrows * p.nsplit * sizeof(float2), 128);
+    }
+    return p;
+}
+
+int check_cuda(dx_attn* h, cudaError_t e)
+{
+    if (e == cudaSuccess)
+        return DX_OK;
+    h->last_cuda_error = (int) e;
+    return DX_ERR_CUDA;
+}
+
+int set_smem(dx_attn* h, const KernelInfo& k)
+{
+    if (!k.fn)
+        return DX_OK;
+    if (k.smem > h->max_smem_optin)
+        return DX_ERR_UNSUPPORTED;
+    return check_cuda(h, cudaFuncSetAttribute(k.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, k.smem));
+}
+
+template <typename T, int DH>
+const void* merge_fn()
+{
+    return reinterpret_cast<const void*>(&lse_merge_kernel<T, DH>);
+}
+
+} // namespace
+
+namespace dx
+{
+KernelInfo merge_kernel_info(int dtype, int dh)
+{
+    KernelInfo k;
+    if (dh == 64)
+        k.fn = dtype == 0 ? merge_fn<__half, 64>() : merge_fn<__nv_bfloat16, 64>();
+    else if (dh == 128)
+        k.fn = dtype == 0 ? merge_fn<__half, 128>() : merge_fn<__nv_bfloat16, 128>();
+    return k;
+}
+} // namespace dx
+
+extern "C" {
+
+int dx_abi_version(void)
+{
+    return DX_ABI_VERSION;
+}
+
+const char* dx_strerror(int status)
+{
+    switch (status)
+    {
+    case DX_OK: return "ok";
+    case DX_ERR_BAD_ARG: return "bad argument";
+    case DX_ERR_UNSUPPORTED: return "unsupported configuration";
+    case DX_ERR_WORKSPACE: return "workspace too small";
+    case DX_ERR_CUDA: return "CUDA runtime error";
+    case DX_ERR_TIMEOUT: return "device-side wait timed out";
+    case DX_ERR_BOUNDS: return "block pointer or length out of bounds";
+    default: return "unknown status";
+    }
+}
+
+int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
+{
+    if (!config || !out)
+        return DX_ERR_BAD_ARG;
+    *out = nullptr;
+    if (config->struct_size != sizeof(dx_attn_config))
+        return DX_ERR_BAD_ARG;
+    const dx_attn_config& c = *config;
+    if (c.num_heads <= 0 || c.num_kv_heads <= 0 || c.num_heads % c.num_kv_heads != 0)
+        return DX_ERR_BAD_ARG;
+    if (!(c.q_scaling > 0.f) || c.tokens_per_block <= 0 || (c.tokens_per_block & (c.tokens_per_block - 1)))
+        return DX_ERR_BAD_ARG;
+    if (c.head_size != 64 && c.head_size != 128)
+        return DX_ERR_UNSUPPORTED;
+    if (c.type_id != DX_DTYPE_FP16 && c.type_id != DX_DTYPE_BF16)
+        return DX_ERR_UNSUPPORTED;
+    if (!c.paged_kv_cache || c.tokens_per_block < 16 || c.tokens_per_block > 256)
+        return DX_ERR_UNSUPPORTED;
+    const int q = c.kv_cache_quant_mode & (DX_QUANT_INT8_KV_CACHE | DX_QUANT_FP8_KV_CACHE);
+    if (q == (DX_QUANT_INT8_KV_CACHE | DX_QUANT_FP8_KV_CACHE))
+        return DX_ERR_BAD_ARG;
+
+    dx_attn* h = new (std::nothrow) dx_attn;
+    if (!h)
+        return DX_ERR_BAD_ARG;
+    h->cfg = c;
+    h->cache_kind = q == DX_QUANT_INT8_KV_CACHE ? CACHE_INT8 : (q == DX_QUANT_FP8_KV_CACHE ? CACHE_FP8 : CACHE_T);
+    h->group = c.num_heads / c.num_kv_heads;
+    while ((1 << h->tpb_log2) < c.tokens_per_block)
+        ++h->tpb_log2;
+    if (const char* w = getenv("DX_ATTN_WAVES"))
+        h->waves = std::max(1, atoi(w));
+    if (const char* w = getenv("DX_ATTN_MIN_CHUNK"))
+        h->min_chunk = std::max(128, atoi(w));
+
+    int st = check_cuda(h, cudaSetDevice(c.device));
+    if (st == DX_OK)
+        st = check_cuda(h, cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, c.device));
+    if (st == DX_OK)
+        st = check_cuda(
+            h, cudaDeviceGetAttribute(&h->max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, c.device));
+    if (st == DX_OK)
+    {
+        h->k_mha = mha_kernel_info(c.type_id, h->cache_kind, c.head_size);
+        h->k_merge = merge_kernel_info(c.type_id, c.head_size);
+        if (h->cache_kind != CACHE_T)
+        {
+            h->k_gqa8 = gqa_kernel_info(c.type_id, h->cache_kind, c.head_size, false);
+            h->k_gqa16 = gqa_kernel_info(c.type_id, h->cache_kind, c.head_size, true);
+        }
+        if (!h->k_mha.fn || !h->k_merge.fn)
+            st = DX_ERR_UNSUPPORTED;
+    }
+    if (st == DX_OK)
+        st = set_smem(h, h->k_mha);
+    if (st == DX_OK)
+        st = set_smem(h, h->k_gqa8);
+    if (st == DX_OK)
+        st = set_smem(h, h->k_gqa16);
+    if (st == DX_OK)
+        st = check_cuda(h, cudaMalloc(reinterpret_cast<void**>(&h->status_dev), 256));
+    if (st == DX_OK)
+        st = check_cuda(h, cudaMemset(h->status_dev, 0, 256));
+    if (st != DX_OK)
+    {
+        if (h->status_dev)
+            cudaFree(h->status_dev);
+        delete h;
+        return st;
+    }
+    *out = h;
+    return DX_OK;
+}
+
+void dx_attn_destroy(dx_attn_t* h)
+{
+    if (!h)
+        return;
+    cudaSetDevice(h->cfg.device);
+    if (h->status_dev)
+        cudaFree(h->status_dev);
+    if (h->stage_dev)
+        cudaFree(h->stage_dev);
+    delete h;
+}
+
+size_t dx_attn_workspace_size(const dx_attn_t* h, int32_t batch, int32_t max_past_len)
+{
+    if (!h || batch <= 0 || max_past_len < 0 || !h->cfg.multi_block_mode)
+        return 0;
+    // The partition count depends on the batch actually enqueued; cover every batch up to `batch`.
+    size_t need = 0;
+    for (int b = 1; b <= batch; ++b)
+        need = std::max(need, make_plan(h, b, max_past_len).workspace());
+    return need;
+}
+
+int dx_attn_plan(const dx_attn_t* h, int32_t batch, int32_t max_past_len, int32_t* num_partitions,
+    int32_t* tokens_per_partition, int32_t* kernel_kind)
+{
+    if (!h || batch <= 0 || max_past_len < 0)
+        return DX_ERR_BAD_ARG;
+    const Plan p = make_plan(h, batch, max_past_len);
+    if (num_partitions)
+        *num_partitions = p.nsplit;
+    if (tokens_per_partition)
+        *tokens_per_partition = p.chunk_tokens;
+    if (kernel_kind)
+        *kernel_kind = p.kind;
+    return DX_OK;
+}
+
+int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* params, void* cuda_stream)
+{
+    if (!h || !params || params->struct_size != sizeof(dx_attn_generation_params))
+        return DX_ERR_BAD_ARG;
+    const dx_attn_generation_params& p = *params;
+    const dx_attn_config& c = h->cfg;
+    if (p.num_requests < 0 || p.max_blocks_per_sequence <= 0)
+        return DX_ERR_BAD_ARG;
+    if (p.num_requests == 0)
+        return DX_OK; // empty batch: nothing to do, nothing launched
+    if (!p.attention_input || !p.sequence_lengths || !p.block_pointers || !p.context_buf)
+        return DX_ERR_BAD_ARG;
+    if (((uintptr_t) p.attention_input | (uintptr_t) p.context_buf) & 15)
+        return DX_ERR_BAD_ARG;
+    if (((uintptr_t) p.block_pointers & 7) || ((uintptr_t) p.sequence_lengths & 3))
+        return DX_ERR_BAD_ARG;
+    if (h->cache_kind != CACHE_T && (!p.kv_scale_orig_quant || !p.kv_scale_quant_orig))
+        return DX_ERR_BAD_ARG;
+    if (p.beam_width != 1 || p.cache_indir != nullptr || p.sink_token_length != 0)
+        return DX_ERR_UNSUPPORTED;
+
+    int max_past = p.past_kv_length;
+    if (p.host_past_key_value_lengths)
+    {
+        max_past = 0;
+        for (int i = 0; i < p.num_requests; ++i)
+        {
+            const int v = p.host_past_key_value_lengths[i];
+            if (v < 0)
+                return DX_ERR_BAD_ARG;
+            max_past = std::max(max_past, v);
+        }
+    }
+    if (max_past < 0)
+        return DX_ERR_BAD_ARG;
+    if ((int64_t) max_past + 1 > (int64_t) p.max_blocks_per_sequence * c.tokens_per_block)
+        return DX_ERR_BAD_ARG; // the table cannot hold that many tokens
+    if (p.cyclic_attention_window_size < max_past + 1 || p.max_attention_window < max_past + 1)
+        return DX_ERR_UNSUPPORTED; // sliding-window / cyclic cache is not implemented
+
+    const Plan plan = make_plan(h, p.num_requests, max_past);
+    if (plan.kind == KIND_MHA && c.tokens_per_block < 16)
+        return DX_ERR_UNSUPPORTED;
+    if (plan.nsplit > 1)
+    {
+        if (!p.workspace || ((uintptr_t) p.workspace & 127))
+            return p.workspace ? DX_ERR_BAD_ARG : DX_ERR_WORKSPACE;
+        if (p.workspace_bytes < plan.workspace())
+            return DX_ERR_WORKSPACE;
+    }
+
+    AttnArgs a{};
+    a.qkv = p.attention_input;
+    a.out = p.context_buf;
+    a.seq_len = p.sequence_lengths;
+    a.block_ptrs = p.block_pointers;
+    a.scale_orig_quant = p.kv_scale_orig_quant;
+    a.scale_quant_orig = p.kv_scale_quant_orig;
+    a.part_o = plan.nsplit > 1 ? reinterpret_cast<float*>(p.workspace) : nullptr;
+    a.part_ml = plan.nsplit > 1 ? reinterpret_cast<float2*>(reinterpret_cast<char*>(p.workspace) + plan.part_o_bytes)
+                                : nullptr;
+    a.status = h->status_dev;
+    a.batch = p.num_requests;
+    a.num_heads = c.num_heads;
+    a.num_kv_heads = c.num_kv_heads;
+    a.max_blocks_per_seq = p.max_blocks_per_sequence;
+    a.tpb_log2 = h->tpb_log2;
+    a.chunk_tokens = plan.chunk_tokens;
+    a.nsplit = plan.nsplit;
+    a.softmax_scale_log2 = 1.4426950408889634f / (sqrtf((float) c.head_size) * c.q_scaling);
+
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+    int st = check_cuda(h, cudaSetDevice(c.device));
+    if (st != DX_OK)
+        return st;
+
+    if (plan.kind == KIND_GQA)
+    {
+        const KernelInfo& k = plan.heads16 ? h->k_gqa16 : h->k_gqa8;
+        if (!k.fn)
+            return DX_ERR_UNSUPPORTED;
+        int hgroups = plan.hgroups;
+        void* args[] = {&a, &hgroups};
+        dim3 grid(plan.nsplit, c.num_kv_heads * plan.hgroups, p.num_requests);
+        st = check_cuda(h, cudaLaunchKernel(k.fn, grid, dim3(128), args, (size_t) k.smem, stream));
+    }
+    else
+    {
+        void* args[] = {&a};
+        dim3 grid(plan.nsplit, c.num_heads, p.num_requests);
+        st = check_cuda(h, cudaLaunchKernel(h->k_mha.fn, grid, dim3(128), args, (size_t) h->k_mha.smem, stream));
+    }
+    if (st != DX_OK)
+        return st;
+    h->launches.fetch_add(1);
+
+    if (plan.nsplit > 1)
+    {
+        void* args[] = {&a};
+        const int rows = p.num_requests * c.num_heads;
+        st = check_cuda(h, cudaLaunchKernel(h->k_merge.fn, dim3((rows + 3) / 4), dim3(128), args, 0, stream));
+        if (st != DX_OK)
+            return st;
+        h->launches.fetch_add(1);
+    }
+    return DX_OK;
+}
+
+int dx_attn_enqueue_generation_host(
+    dx_attn_t* h, const dx_attn_generation_params* params, void* cuda_stream, int32_t sync)
+{
+    if (!h || !params || params->struct_size != sizeof(dx_attn_generation_params))
+        return DX_ERR_BAD_ARG;
+    dx_attn_generation_params p = *params;
+    const dx_attn_config& c = h->cfg;
+    if (p.num_requests < 0 || p.max_blocks_per_sequence <= 0)
+        return DX_ERR_BAD_ARG;
+    if (p.num_requests == 0)
+        return DX_OK;
+    if (!p.attention_input || !p.sequence_lengths || !p.block_pointers || !p.context_buf)
+        return DX_ERR_BAD_ARG;
+    const size_t B = (size_t) p.num_requests;
+    const size_t qkv_bytes = B * (size_t) (c.num_heads + 2 * c.num_kv_heads) * c.head_size * 2;
+    const size_t out_bytes = B * (size_t) c.num_heads * c.head_size * 2;
+    const size_t tbl_bytes = B * 2 * (size_t) p.max_blocks_per_sequence * sizeof(int64_t);
+    const size_t len_bytes = B * sizeof(int32_t);
+    const size_t o_qkv = 0, o_out = align_up(qkv_bytes, 256), o_tbl = o_out + align_up(out_bytes, 256),
+                 o_len = o_tbl + align_up(tbl_bytes, 256), total = o_len + align_up(len_bytes, 256);
+
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+    int st = check_cuda(h, cudaSetDevice(c.device));
+    if (st != DX_OK)
+        return st;
+    if (h->stage_bytes < total)
+    {
+        // Growing the staging area is the one allocation made after create(); it synchronises.
+        if (h->stage_dev)
+        {
+            st = check_cuda(h, cudaDeviceSynchronize());
+            if (st != DX_OK)
+                return st;
+            cudaFree(h->stage_dev);
+            h->stage_dev = nullptr;
+            h->stage_bytes = 0;
+        }
+        st = check_cuda(h, cudaMalloc(&h->stage_dev, total));
+        if (st != DX_OK)
+            return st;
+        h->stage_bytes = total;
+    }
+    char* base = reinterpret_cast<char*>(h->stage_dev);
+    st = check_cuda(h, cudaMemcpyAsync(base + o_qkv, p.attention_input, qkv_bytes, cudaMemcpyHostToDevice, stream));
+    if (st == DX_OK)
+        st = check_cuda(h, cudaMemcpyAsync(base + o_tbl, p.block_pointers, tbl_bytes, cudaMemcpyHostToDevice, stream));
+    if (st == DX_OK)
+        st = check_cuda(
+            h, cudaMemcpyAsync(base + o_len, p.sequence_lengths, len_bytes, cudaMemcpyHostToDevice, stream));
+    if (st != DX_OK)
+        return st;
+    void* host_out = p.context_buf;
+    p.attention_input = base + o_qkv;
+    p.block_pointers = reinterpret_cast<const int64_t*>(base + o_tbl);
+    p.sequence_lengths = reinterpret_cast<const int32_t*>(base + o_len);
+    p.context_buf = base + o_out;
+    st = dx_attn_enqueue_generation(h, &p, cuda_stream);
+    if (st != DX_OK)
+        return st;
+    st = check_cuda(h, cudaMemcpyAsync(host_out, base + o_out, out_bytes, cudaMemcpyDeviceToHost, stream));
+    if (st == DX_OK && sync)
+        st = check_cuda(h, cudaStreamSynchronize(stream));
+    return st;
+}
+
+int dx_attn_validate(const dx_attn_t* h, const int64_t* host_block_pointers,
+    const int32_t* host_past_key_value_lengths, int32_t num_requests, int32_t max_blocks_per_sequence,
+    const void* pool_base, size_t pool_bytes)
+{
+    if (!h || !host_block_pointers || !host_past_key_value_lengths || num_requests < 0
+        || max_blocks_per_sequence <= 0 || !pool_base)
+        return DX_ERR_BAD_ARG;
+    const dx_attn_config& c = h->cfg;
+    const size_t esz = h->cache_kind == CACHE_T ? 2 : 1;
+    const size_t block_bytes = (size_t) c.num_kv_heads * c.tokens_per_block * c.head_size * esz;
+    const uintptr_t lo = (uintptr_t) pool_base, hi = lo + pool_bytes;
+    for (int b = 0; b < num_requests; ++b)
+    {
+        const int past = host_past_key_value_lengths[b];
+        if (past < 0)
+            return DX_ERR_BAD_ARG;
+        const int64_t need = ((int64_t) past + 1 + c.tokens_per_block - 1) / c.tokens_per_block;
+        if (need > max_blocks_per_sequence)
+            return DX_ERR_BOUNDS;
+        for (int kv = 0; kv < 2; ++kv)
+        {
+            const int64_t* row = host_block_pointers + ((size_t) b * 2 + kv) * max_blocks_per_sequence;
+            for (int64_t i = 0; i < need; ++i)
+            {
+                const uintptr_t ptr = (uintptr_t) row[i];
+                if (ptr & 15)
+                    return DX_ERR_BAD_ARG;
+                if (ptr < lo || ptr + block_bytes > hi)
+                    return DX_ERR_BOUNDS;
+            }
+        }
+    }
+    return DX_OK;
+}
+
+int dx_attn_device_status(dx_attn_t* h)
+{
+    if (!h)
+        return DX_ERR_BAD_ARG;
+    int32_t v = 0;
+    int st = check_cuda(h, cudaSetDevice(h->cfg.device));
+    if (st == DX_OK)
+        st = check_cuda(h, cudaMemcpy(&v, h->status_dev, sizeof(v), cudaMemcpyDeviceToHost));
+    if (st != DX_OK)
+        return st;
+    if (v != 0)
+    {
+        st = check_cuda(h, cudaMemset(h->status_dev, 0, sizeof(v)));
+        if (st != DX_OK)
+            return st;
+    }
+    return v == 0 ? DX_OK : (v == STATUS_TIMEOUT ? DX_ERR_TIMEOUT : DX_ERR_CUDA);
+}
+
+int dx_attn_last_cuda_error(const dx_attn_t* h)
+{
+    return h ? h->last_cuda_error : 0;
+}
+
+int64_t dx_attn_launch_count(const dx_attn_t* h)
+{
+    return h ? h->launches.load() : 0;
+}
+
+} // extern "C"

@@ -1,0 +1,264 @@
+// Shared device helpers for the decode-attention kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace dx
+{
+
+// Cache element kinds.
+enum CacheKind : int
+{
+    CACHE_T = 0,    // same 16-bit type as the activations, no quantisation
+    CACHE_INT8 = 1, // int8, per-tensor scale
+    CACHE_FP8 = 2   // e4m3, per-tensor scale
+};
+
+// Arguments shared by every attention kernel.  Passed by value (fits the 4 KB parameter space).
+struct AttnArgs
+{
+    const void* qkv;              // T [B, (H + 2 Hkv) Dh]
+    void* out;                    // T [B, H Dh]
+    const int32_t* seq_len;       // int32 [B], includes the new token
+    const int64_t* block_ptrs;    // int64 [B, 2, M]
+    const float* scale_orig_quant; // device float[1] or nullptr
+    const float* scale_quant_orig; // device float[1] or nullptr
+    float* part_o;                // fp32 [B*H, nsplit, Dh]  (split-K partial numerators)
+    float2* part_ml;              // (m, l) [B*H, nsplit]     (running max in log2 units, denominator)
+    int32_t* status;              // device status word (0 ok)
+    int32_t batch;
+    int32_t num_heads;
+    int32_t num_kv_heads;
+    int32_t max_blocks_per_seq;
+    int32_t tpb_log2;
+    int32_t chunk_tokens; // tokens per split-K partition (multiple of the kernel's token group)
+    int32_t nsplit;       // grid.x; 1 => kernels write the final output themselves
+    float softmax_scale_log2; // log2(e) / (sqrt(Dh) * q_scaling)
+};
+
+static constexpr int32_t STATUS_TIMEOUT = 5;
+
+// ----------------------------------------------------------------------------------------------
+// PTX wrappers
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait: every spin in this library has an iteration limit.  Returns false when it gave up.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity)
+{
+#pragma unroll 1
+    for (int it = 0; it < (1 << 22); ++it)
+    {
+        if (mbar_try_wait(bar, parity))
+            return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void fence_mbar_init()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// 1-D bulk async copy global -> this CTA's shared memory, completion counted in bytes on an
+// mbarrier.  dst, src 16-byte aligned, bytes a multiple of 16.  Never multicast.
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+            smem_u32(dst_smem)),
+        "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// 16-byte Ampere-style async copy (used where the destination layout is swizzled per 16 B).
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src_gmem)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem) : "memory");
+}
+
+// Makes the executing thread's prior cp.async operations arrive on the mbarrier when they land.
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t* bar)
+{
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void griddep_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void griddep_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// ----------------------------------------------------------------------------------------------
+// 16-bit activation type helpers
+// ----------------------------------------------------------------------------------------------
+template <typename T>
+struct TypeOps;
+
+template <>
+struct TypeOps<__half>
+{
+    using T2 = __half2;
+    static __device__ __forceinline__ float to_float(__half x)
+    {
+        return __half2float(x);
+    }
+    static __device__ __forceinline__ __half from_float(float x)
+    {
+        return __float2half_rn(x);
+    }
+    static __device__ __forceinline__ float2 unpack2(uint32_t w)
+    {
+        return __half22float2(*reinterpret_cast<const __half2*>(&w));
+    }
+    static __device__ __forceinline__ uint32_t pack2(float a, float b)
+    {
+        __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+    // scale_T * x_T with one rounding to T, then RN-even saturating-finite e4m3: the byte the
+    // reference stores (decoderMaskedMultiheadAttentionUtils.h:3753-3763 with T_scale = half).
+    static __device__ __forceinline__ uint8_t quant_fp8(__half x, __half scale)
+    {
+        __half p = __hmul(scale, x);
+        return (uint8_t) __nv_cvt_halfraw_to_fp8(static_cast<__half_raw>(p), __NV_SATFINITE, __NV_E4M3);
+    }
+};
+
+template <>
+struct TypeOps<__nv_bfloat16>
+{
+    using T2 = __nv_bfloat162;
+    static __device__ __forceinline__ float to_float(__nv_bfloat16 x)
+    {
+        return __bfloat162float(x);
+    }
+    static __device__ __forceinline__ __nv_bfloat16 from_float(float x)
+    {
+        return __float2bfloat16_rn(x);
+    }
+    static __device__ __forceinline__ float2 unpack2(uint32_t w)
+    {
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    }
+    static __device__ __forceinline__ uint32_t pack2(float a, float b)
+    {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+    static __device__ __forceinline__ uint8_t quant_fp8(__nv_bfloat16 x, __nv_bfloat16 scale)
+    {
+        __nv_bfloat16 p = __hmul(scale, x);
+        return (uint8_t) __nv_cvt_bfloat16raw_to_fp8(static_cast<__nv_bfloat16_raw>(p), __NV_SATFINITE, __NV_E4M3);
+    }
+};
+
+// round-to-nearest-even, saturating float -> int8: the instruction the reference issues
+// (decoderMaskedMultiheadAttentionUtils.h:3629-3639).
+__device__ __forceinline__ int8_t quant_int8(float x)
+{
+    short r;
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=h"(r) : "f"(x));
+    return (int8_t) r;
+}
+
+// Quantise 4 consecutive activations (two packed 32-bit words of T) into 4 cache bytes.
+template <typename T, int CACHE>
+__device__ __forceinline__ uint32_t quant4(uint32_t w0, uint32_t w1, float scale_f32, T scale_t)
+{
+    const T* a = reinterpret_cast<const T*>(&w0);
+    const T* b = reinterpret_cast<const T*>(&w1);
+    uint32_t r;
+    if constexpr (CACHE == CACHE_INT8)
+    {
+        uint32_t b0 = (uint8_t) quant_int8(TypeOps<T>::to_float(a[0]) * scale_f32);
+        uint32_t b1 = (uint8_t) quant_int8(TypeOps<T>::to_float(a[1]) * scale_f32);
+        uint32_t b2 = (uint8_t) quant_int8(TypeOps<T>::to_float(b[0]) * scale_f32);
+        uint32_t b3 = (uint8_t) quant_int8(TypeOps<T>::to_float(b[1]) * scale_f32);
+        r = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+    }
+    else
+    {
+        uint32_t b0 = TypeOps<T>::quant_fp8(a[0], scale_t);
+        uint32_t b1 = TypeOps<T>::quant_fp8(a[1], scale_t);
+        uint32_t b2 = TypeOps<T>::quant_fp8(b[0], scale_t);
+        uint32_t b3 = TypeOps<T>::quant_fp8(b[1], scale_t);
+        r = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+    }
+    return r;
+}
+
+// ----------------------------------------------------------------------------------------------
+// Dequantise-in-register: 4 packed cache bytes -> 4 floats (without the per-tensor scale, which
+// the callers fold into q and into the final normalisation).
+// ----------------------------------------------------------------------------------------------
+template <int CACHE>
+__device__ __forceinline__ void dequant4(uint32_t w, float (&f)[4])
+{
+    if constexpr (CACHE == CACHE_INT8)
+    {
+        // byte -> 2^23 + (byte ^ 0x80) by byte permute, then subtract 2^23 + 128: exact.
+        const uint32_t u = w ^ 0x80808080u;
+        f[0] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.f;
+        f[1] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.f;
+        f[2] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.f;
+        f[3] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.f;
+    }
+    else
+    {
+        __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t) (w & 0xffffu), __NV_E4M3);
+        __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t) (w >> 16), __NV_E4M3);
+        float2 a = __half22float2(*reinterpret_cast<__half2*>(&lo));
+        float2 b = __half22float2(*reinterpret_cast<__half2*>(&hi));
+        f[0] = a.x;
+        f[1] = a.y;
+        f[2] = b.x;
+        f[3] = b.y;
+    }
+}
+
+} // namespace dx

@@ -1,0 +1,17 @@
+// Internal: kernel lookup shared by the C-ABI translation unit and the instantiation units.
+#pragma once
+#include "dx_common.cuh"
+
+namespace dx
+{
+struct KernelInfo
+{
+    const void* fn = nullptr; // __global__ function address for cudaLaunchKernel
+    int smem = 0;             // dynamic shared memory per CTA, bytes
+};
+
+// dtype: 0 fp16, 1 bf16.  cache: CacheKind.  dh: 64 or 128.
+KernelInfo mha_kernel_info(int dtype, int cache, int dh);
+KernelInfo gqa_kernel_info(int dtype, int cache, int dh, bool heads16);
+KernelInfo merge_kernel_info(int dtype, int dh);
+} // namespace dx

@@ -1,0 +1,38 @@
+// Instantiations of the CUDA-core multi-head decode kernel.
+#include "dx_launch.h"
+#include "dx_mha_kernel.cuh"
+
+namespace dx
+{
+template <typename T, int CACHE, int DH>
+static KernelInfo mk()
+{
+    KernelInfo k;
+    k.fn = reinterpret_cast<const void*>(&mha_decode_kernel<T, CACHE, DH>);
+    k.smem = MhaTraits<CACHE, DH>::SMEM_BYTES;
+    return k;
+}
+
+template <typename T>
+static KernelInfo by_cache_dh(int cache, int dh)
+{
+    if (dh == 64)
+    {
+        if (cache == CACHE_T) return mk<T, CACHE_T, 64>();
+        if (cache == CACHE_INT8) return mk<T, CACHE_INT8, 64>();
+        if (cache == CACHE_FP8) return mk<T, CACHE_FP8, 64>();
+    }
+    else if (dh == 128)
+    {
+        if (cache == CACHE_T) return mk<T, CACHE_T, 128>();
+        if (cache == CACHE_INT8) return mk<T, CACHE_INT8, 128>();
+        if (cache == CACHE_FP8) return mk<T, CACHE_FP8, 128>();
+    }
+    return KernelInfo{};
+}
+
+KernelInfo mha_kernel_info(int dtype, int cache, int dh)
+{
+    return dtype == 0 ? by_cache_dh<__half>(cache, dh) : by_cache_dh<__nv_bfloat16>(cache, dh);
+}
+} // namespace dx

@@ -1,0 +1,303 @@
+"""Host-side mirror of the reference operator for the generation phase, over the C ABI.
+
+``GPTAttentionPlugin`` keeps the static attributes of the reference plugin
+(cpp/tensorrt_llm/plugins/gptAttentionCommon/gptAttentionCommon.cpp:1558-1596) and its
+``enqueue_generation`` takes the per-step tensors of ``tensorrt_llm.functional.gpt_attention``
+(tensorrt_llm/functional.py:3487-3906: qkv, sequence_length, host_past_key_value_lengths,
+kv_cache_block_pointers, kv_orig_quant_scale, kv_quant_orig_scale ...) with the same names and
+meaning.  torch is used only for device memory and streams; all compute happens in
+libdecode_attn.so, which must be present - there is no fallback path.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+DX_OK, DX_ERR_BAD_ARG, DX_ERR_UNSUPPORTED, DX_ERR_WORKSPACE, DX_ERR_CUDA, DX_ERR_TIMEOUT, DX_ERR_BOUNDS = range(7)
+DX_DTYPE_FP16, DX_DTYPE_BF16 = 0, 1
+
+_LIB: Optional[ctypes.CDLL] = None
+
+
+class QuantMode:
+    """Bit values of tensorrt_llm.quantization.mode.QuantMode that concern the KV cache
+    (tensorrt_llm/quantization/mode.py:47-49)."""
+    NONE = 0
+    INT8_KV_CACHE = 1 << 6
+    FP8_KV_CACHE = 1 << 7
+
+
+class DecodeAttnError(RuntimeError):
+    def __init__(self, status: int, what: str):
+        self.status = status
+        super().__init__(f"{what}: {_strerror(status)} (status {status})")
+
+
+class _Config(ctypes.Structure):
+    _fields_ = [("struct_size", ctypes.c_uint32), ("layer_idx", ctypes.c_int32), ("num_heads", ctypes.c_int32),
+                ("num_kv_heads", ctypes.c_int32), ("head_size", ctypes.c_int32), ("q_scaling", ctypes.c_float),
+                ("tp_size", ctypes.c_int32), ("tp_rank", ctypes.c_int32), ("multi_block_mode", ctypes.c_int32),
+                ("enable_xqa", ctypes.c_int32), ("kv_cache_quant_mode", ctypes.c_int32),
+                ("paged_kv_cache", ctypes.c_int32), ("tokens_per_block", ctypes.c_int32),
+                ("type_id", ctypes.c_int32), ("device", ctypes.c_int32)]
+
+
+class _GenParams(ctypes.Structure):
+    _fields_ = [("struct_size", ctypes.c_uint32), ("attention_input", ctypes.c_void_p),
+                ("sequence_lengths", ctypes.c_void_p), ("host_past_key_value_lengths", ctypes.c_void_p),
+                ("past_kv_length", ctypes.c_int32), ("beam_width", ctypes.c_int32),
+                ("num_requests", ctypes.c_int32), ("max_blocks_per_sequence", ctypes.c_int32),
+                ("max_attention_window", ctypes.c_int32), ("cyclic_attention_window_size", ctypes.c_int32),
+                ("sink_token_length", ctypes.c_int32), ("block_pointers", ctypes.c_void_p),
+                ("host_block_pointers", ctypes.c_void_p), ("kv_scale_orig_quant", ctypes.c_void_p),
+                ("kv_scale_quant_orig", ctypes.c_void_p), ("context_buf", ctypes.c_void_p),
+                ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
+                ("cache_indir", ctypes.c_void_p)]
+
+
+EXPORTED_SYMBOLS = [
+    "dx_abi_version", "dx_strerror", "dx_attn_create", "dx_attn_destroy", "dx_attn_workspace_size",
+    "dx_attn_enqueue_generation", "dx_attn_enqueue_generation_host", "dx_attn_validate", "dx_attn_plan",
+    "dx_attn_device_status", "dx_attn_last_cuda_error", "dx_attn_launch_count",
+]
+
+
+def library_path() -> Path:
+    return Path(__file__).resolve().parent / "libdecode_attn.so"
+
+
+def load_library() -> ctypes.CDLL:
+    """Loads libdecode_attn.so; raises if it has not been built (no fallback exists)."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = library_path()
+    if not path.exists():
+        raise RuntimeError(f"{path} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'`; "
+                           "this package has no non-CUDA path")
+    lib = ctypes.CDLL(str(path))
+    lib.dx_abi_version.restype = ctypes.c_int
+    lib.dx_strerror.restype = ctypes.c_char_p
+    lib.dx_strerror.argtypes = [ctypes.c_int]
+    lib.dx_attn_create.restype = ctypes.c_int
+    lib.dx_attn_create.argtypes = [ctypes.POINTER(_Config), ctypes.POINTER(ctypes.c_void_p)]
+    lib.dx_attn_destroy.restype = None
+    lib.dx_attn_destroy.argtypes = [ctypes.c_void_p]
+    lib.dx_attn_workspace_size.restype = ctypes.c_size_t
+    lib.dx_attn_workspace_size.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32]
+    lib.dx_attn_enqueue_generation.restype = ctypes.c_int
+    lib.dx_attn_enqueue_generation.argtypes = [ctypes.c_void_p, ctypes.POINTER(_GenParams), ctypes.c_void_p]
+    lib.dx_attn_enqueue_generation_host.restype = ctypes.c_int
+    lib.dx_attn_enqueue_generation_host.argtypes = [ctypes.c_void_p, ctypes.POINTER(_GenParams), ctypes.c_void_p,
+                                                    ctypes.c_int32]
+    lib.dx_attn_validate.restype = ctypes.c_int
+    lib.dx_attn_validate.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
+                                     ctypes.c_int32, ctypes.c_void_p, ctypes.c_size_t]
+    lib.dx_attn_plan.restype = ctypes.c_int
+    lib.dx_attn_plan.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(ctypes.c_int32),
+                                 ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]
+    lib.dx_attn_device_status.restype = ctypes.c_int
+    lib.dx_attn_device_status.argtypes = [ctypes.c_void_p]
+    lib.dx_attn_last_cuda_error.restype = ctypes.c_int
+    lib.dx_attn_last_cuda_error.argtypes = [ctypes.c_void_p]
+    lib.dx_attn_launch_count.restype = ctypes.c_int64
+    lib.dx_attn_launch_count.argtypes = [ctypes.c_void_p]
+    if lib.dx_abi_version() != 1:
+        raise RuntimeError("libdecode_attn.so has an unexpected ABI version")
+    _LIB = lib
+    return lib
+
+
+def _strerror(status: int) -> str:
+    return load_library().dx_strerror(status).decode()
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+class GPTAttentionPlugin:
+    """One instance per (GPU, layer configuration), like one plugin object per engine layer."""
+
+    def __init__(self, *, num_heads: int, num_kv_heads: int, head_size: int, q_scaling: float = 1.0,
+                 tp_size: int = 1, tp_rank: int = 0, multi_block_mode: bool = False, enable_xqa: bool = True,
+                 kv_cache_quant_mode: int = QuantMode.NONE, paged_kv_cache: bool = True, tokens_per_block: int = 64,
+                 type_id: torch.dtype = torch.float16, layer_idx: int = 0, device: int = 0):
+        if type_id not in (torch.float16, torch.bfloat16):
+            raise DecodeAttnError(DX_ERR_UNSUPPORTED, "type_id")
+        self.lib = load_library()
+        self.dtype = type_id
+        self.num_heads, self.num_kv_heads, self.head_size = num_heads, num_kv_heads, head_size
+        self.tokens_per_block = tokens_per_block
+        self.kv_cache_quant_mode = kv_cache_quant_mode
+        self.device = device
+        cfg = _Config(ctypes.sizeof(_Config), layer_idx, num_heads, num_kv_heads, head_size, q_scaling, tp_size,
+                      tp_rank, int(multi_block_mode), int(enable_xqa), kv_cache_quant_mode, int(paged_kv_cache),
+                      tokens_per_block, DX_DTYPE_FP16 if type_id == torch.float16 else DX_DTYPE_BF16, device)
+        handle = ctypes.c_void_p()
+        st = self.lib.dx_attn_create(ctypes.byref(cfg), ctypes.byref(handle))
+        if st != DX_OK:
+            raise DecodeAttnError(st, "dx_attn_create")
+        self._h = handle
+        self._workspace: Optional[torch.Tensor] = None
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self.lib.dx_attn_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # --- reference: getWorkspaceSizeForGeneration ---
+    def get_workspace_size(self, batch: int, max_past_len: int) -> int:
+        return int(self.lib.dx_attn_workspace_size(self._h, batch, max_past_len))
+
+    def plan(self, batch: int, max_past_len: int):
+        n, c, k = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_int32()
+        st = self.lib.dx_attn_plan(self._h, batch, max_past_len, ctypes.byref(n), ctypes.byref(c), ctypes.byref(k))
+        if st != DX_OK:
+            raise DecodeAttnError(st, "dx_attn_plan")
+        return {"num_partitions": n.value, "tokens_per_partition": c.value,
+                "kernel": "gqa_tensor_core" if k.value == 1 else "mha_cuda_core"}
+
+    def launch_count(self) -> int:
+        return int(self.lib.dx_attn_launch_count(self._h))
+
+    def device_status(self) -> int:
+        return int(self.lib.dx_attn_device_status(self._h))
+
+    def validate(self, host_kv_cache_block_pointers: torch.Tensor, host_past_key_value_lengths: torch.Tensor,
+                 pool_base: int, pool_bytes: int) -> int:
+        t = host_kv_cache_block_pointers.contiguous()
+        l = host_past_key_value_lengths.to(torch.int32).contiguous()
+        return int(self.lib.dx_attn_validate(self._h, t.data_ptr(), l.data_ptr(), l.numel(), t.shape[-1],
+                                             pool_base, pool_bytes))
+
+    def _params(self, qkv, sequence_length, host_past_key_value_lengths, kv_cache_block_pointers,
+                kv_orig_quant_scale, kv_quant_orig_scale, out, workspace, max_attention_window,
+                host_kv_cache_block_pointers=None, cache_indirection=None, beam_width=1, sink_token_length=0):
+        B = qkv.shape[0]
+        M = kv_cache_block_pointers.shape[-1]
+        hp = host_past_key_value_lengths
+        max_past = int(hp.max()) if hp is not None and hp.numel() else 0
+        window = max_attention_window if max_attention_window is not None else M * self.tokens_per_block
+        p = _GenParams()
+        p.struct_size = ctypes.sizeof(_GenParams)
+        p.attention_input = _ptr(qkv)
+        p.sequence_lengths = _ptr(sequence_length)
+        p.host_past_key_value_lengths = _ptr(hp)
+        p.past_kv_length = max_past
+        p.beam_width = beam_width
+        p.num_requests = B
+        p.max_blocks_per_sequence = M
+        p.max_attention_window = window
+        p.cyclic_attention_window_size = window
+        p.sink_token_length = sink_token_length
+        p.block_pointers = _ptr(kv_cache_block_pointers)
+        p.host_block_pointers = _ptr(host_kv_cache_block_pointers)
+        p.kv_scale_orig_quant = _ptr(kv_orig_quant_scale)
+        p.kv_scale_quant_orig = _ptr(kv_quant_orig_scale)
+        p.context_buf = _ptr(out)
+        p.workspace = _ptr(workspace)
+        p.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+        p.cache_indir = _ptr(cache_indirection)
+        return p, max_past
+
+    def _ensure_workspace(self, batch: int, max_past: int, device) -> Optional[torch.Tensor]:
+        need = self.get_workspace_size(batch, max_past)
+        if need == 0:
+            return None
+        if self._workspace is None or self._workspace.numel() < need or self._workspace.device != device:
+            self._workspace = torch.empty(need, dtype=torch.uint8, device=device)
+        return self._workspace
+
+    # --- reference: enqueueGeneration ---
+    def enqueue_generation(self, qkv: torch.Tensor, sequence_length: torch.Tensor,
+                           host_past_key_value_lengths: torch.Tensor, kv_cache_block_pointers: torch.Tensor,
+                           kv_orig_quant_scale: Optional[torch.Tensor] = None,
+                           kv_quant_orig_scale: Optional[torch.Tensor] = None, *, out: Optional[torch.Tensor] = None,
+                           workspace: Optional[torch.Tensor] = None, max_attention_window: Optional[int] = None,
+                           host_kv_cache_block_pointers: Optional[torch.Tensor] = None,
+                           cache_indirection: Optional[torch.Tensor] = None, beam_width: int = 1,
+                           sink_token_length: int = 0, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+        """qkv: T [B, (H+2Hkv)*Dh] (device); sequence_length: int32 [B] (device, includes the new token);
+        host_past_key_value_lengths: int32 [B] (host); kv_cache_block_pointers: int64 [B, 2, M] (device).
+        Appends the new token to the cache and returns the attention output T [B, H*Dh].  Asynchronous."""
+        if not qkv.is_cuda:
+            raise DecodeAttnError(DX_ERR_BAD_ARG, "enqueue_generation needs device tensors (no CPU path exists)")
+        if qkv.dtype != self.dtype:
+            raise DecodeAttnError(DX_ERR_BAD_ARG, "qkv dtype")
+        B = qkv.shape[0]
+        if out is None:
+            out = torch.empty(B, self.num_heads * self.head_size, dtype=self.dtype, device=qkv.device)
+        hp = host_past_key_value_lengths.to(torch.int32).contiguous()
+        max_past = int(hp.max()) if hp.numel() else 0
+        if workspace is None:
+            workspace = self._ensure_workspace(B, max_past, qkv.device)
+        p, _ = self._params(qkv, sequence_length, hp, kv_cache_block_pointers, kv_orig_quant_scale,
+                            kv_quant_orig_scale, out, workspace, max_attention_window,
+                            host_kv_cache_block_pointers, cache_indirection, beam_width, sink_token_length)
+        s = stream if stream is not None else torch.cuda.current_stream(qkv.device)
+        st = self.lib.dx_attn_enqueue_generation(self._h, ctypes.byref(p), ctypes.c_void_p(s.cuda_stream))
+        if st != DX_OK:
+            raise DecodeAttnError(st, "dx_attn_enqueue_generation")
+        return out
+
+    def enqueue_generation_host(self, qkv: torch.Tensor, sequence_length: torch.Tensor,
+                                host_past_key_value_lengths: torch.Tensor, kv_cache_block_pointers: torch.Tensor,
+                                kv_orig_quant_scale: Optional[torch.Tensor], kv_quant_orig_scale: Optional[torch.Tensor],
+                                out: torch.Tensor, *, workspace: Optional[torch.Tensor] = None,
+                                max_attention_window: Optional[int] = None, sync: bool = True,
+                                stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+        """Same step with the step inputs (qkv, sequence_length, block pointers) and the output in HOST
+        memory; scales, KV pool and workspace are device resident."""
+        for t in (qkv, sequence_length, kv_cache_block_pointers, out):
+            if t.is_cuda:
+                raise DecodeAttnError(DX_ERR_BAD_ARG, "enqueue_generation_host takes host tensors")
+        hp = host_past_key_value_lengths.to(torch.int32).contiguous()
+        max_past = int(hp.max()) if hp.numel() else 0
+        dev = torch.device("cuda", self.device)
+        if workspace is None:
+            workspace = self._ensure_workspace(qkv.shape[0], max_past, dev)
+        p, _ = self._params(qkv, sequence_length, hp, kv_cache_block_pointers, kv_orig_quant_scale,
+                            kv_quant_orig_scale, out, workspace, max_attention_window)
+        s = stream if stream is not None else torch.cuda.current_stream(dev)
+        st = self.lib.dx_attn_enqueue_generation_host(self._h, ctypes.byref(p), ctypes.c_void_p(s.cuda_stream),
+                                                      int(sync))
+        if st != DX_OK:
+            raise DecodeAttnError(st, "dx_attn_enqueue_generation_host")
+        return out
+
+
+def gpt_attention(*, qkv: torch.Tensor, sequence_length: torch.Tensor, host_past_key_value_lengths: torch.Tensor,
+                  kv_cache_block_pointers: torch.Tensor, num_heads: int, num_kv_heads: int,
+                  hidden_size_per_head: int, q_scaling: float = 1.0, kv_orig_quant_scale=None,
+                  kv_quant_orig_scale=None, kv_cache_quant_mode: int = QuantMode.NONE, tokens_per_block: int = 64,
+                  multi_block_mode: bool = False, max_attention_window: Optional[int] = None,
+                  plugin: Optional[GPTAttentionPlugin] = None) -> torch.Tensor:
+    """Functional form with the argument names of tensorrt_llm.functional.gpt_attention
+    (tensorrt_llm/functional.py:3487) restricted to the generation phase with a paged cache."""
+    own = plugin is None
+    if own:
+        plugin = GPTAttentionPlugin(num_heads=num_heads, num_kv_heads=num_kv_heads, head_size=hidden_size_per_head,
+                                    q_scaling=q_scaling, multi_block_mode=multi_block_mode,
+                                    kv_cache_quant_mode=kv_cache_quant_mode, tokens_per_block=tokens_per_block,
+                                    type_id=qkv.dtype, device=qkv.device.index or 0)
+    try:
+        out = plugin.enqueue_generation(qkv, sequence_length, host_past_key_value_lengths, kv_cache_block_pointers,
+                                        kv_orig_quant_scale, kv_quant_orig_scale,
+                                        max_attention_window=max_attention_window)
+        if own:
+            torch.cuda.synchronize(qkv.device)
+    finally:
+        if own:
+            plugin.close()
+    return out
