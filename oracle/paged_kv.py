@@ -45,6 +45,7 @@ class PagedPoolModel:
         self.free: List[int] = list(free_order) if free_order is not None else list(range(blocks))
         assert sorted(self.free) == list(range(blocks))
         self.seq_blocks: List[List[int]] = []
+        self.lens: List[int] = []
 
     @property
     def pool_bytes(self) -> int:
@@ -54,7 +55,16 @@ class PagedPoolModel:
         need = (tokens + tokens_per_block - 1) // tokens_per_block
         assert need <= self.max_blocks_per_seq and need <= len(self.free)
         self.seq_blocks.append([self.free.pop(0) for _ in range(need)])
+        self.lens.append(tokens)
         return len(self.seq_blocks) - 1
+
+    def step(self, tokens_per_block: int) -> None:
+        """One generation step for every sequence: a sequence whose next token starts a new block
+        gets one more block first (kv_cache_manager.py:305-345, no cyclic cache, beam width 1)."""
+        for b in range(len(self.seq_blocks)):
+            if self.lens[b] % tokens_per_block == 0:
+                self.seq_blocks[b].append(self.free.pop(0))
+            self.lens[b] += 1
 
     def k_offset(self, block_idx: int) -> int:
         return block_idx * self.blk_bytes

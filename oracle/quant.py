@@ -17,6 +17,16 @@ import torch
 CACHE_T, CACHE_INT8, CACHE_FP8 = 0, 1, 2
 
 
+def int8_from_f32(x: torch.Tensor) -> torch.Tensor:
+    """cvt.rni.sat.s8.f32: round half to even, saturate to [-128, 127]."""
+    return torch.round(x.to(torch.float32)).clamp_(-128, 127).to(torch.int8)
+
+
+def fp8_from_f32(x: torch.Tensor) -> torch.Tensor:
+    """float -> e4m3, round to nearest even, saturating to +-448 (__NV_SATFINITE); returns uint8."""
+    return x.to(torch.float32).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+
+
 def quantize_kv(x: torch.Tensor, scale_orig_quant: float, mode: int) -> torch.Tensor:
     """x: tensor of the activation dtype T (fp16/bf16), any shape [..., Dh].
     Returns uint8 bytes of shape [..., Dh * elem_bytes] exactly as the cache stores them."""
@@ -26,13 +36,11 @@ def quantize_kv(x: torch.Tensor, scale_orig_quant: float, mode: int) -> torch.Te
     s32 = torch.tensor(scale_orig_quant, dtype=torch.float32)
     if mode == CACHE_INT8:
         # one fp32 multiply, round half to even (torch.round), saturate
-        q = torch.round(x.to(torch.float32) * s32).clamp_(-128, 127).to(torch.int8)
-        return q.view(torch.uint8)
+        return int8_from_f32(x.to(torch.float32) * s32).view(torch.uint8)
     if mode == CACHE_FP8:
         st = s32.to(x.dtype)
         prod = x * st  # one rounding to T (the exact product fits fp32)
-        sat = prod.to(torch.float32).clamp_(-448.0, 448.0)  # SATFINITE
-        return sat.to(torch.float8_e4m3fn).view(torch.uint8)
+        return fp8_from_f32(prod.to(torch.float32))
     raise ValueError(mode)
 
 

@@ -201,6 +201,28 @@ def to_device(w: DecodeWorkload, device: torch.device | str) -> DecodeWorkload:
         kv_quant_orig_scale=None if w.kv_quant_orig_scale is None else w.kv_quant_orig_scale.to(device))
 
 
+def shard_workload(w: DecodeWorkload, tp_size: int, tp_rank: int) -> DecodeWorkload:
+    """The slice of a full workload that tensor-parallel rank tp_rank owns: its q heads, its kv
+    heads and only those heads of every cache block (block = [Hkv_local, tokens, Dh]).  Same
+    lengths and page table on every rank; no data is shared between ranks."""
+    c = w.cfg
+    assert c.num_heads % tp_size == 0 and c.num_kv_heads % tp_size == 0
+    lc = shard_config(c, tp_size)
+    H, Hkv, Dh = c.num_heads, c.num_kv_heads, c.head_size
+    h0, k0 = tp_rank * lc.num_heads, tp_rank * lc.num_kv_heads
+    q = w.qkv[:, h0 * Dh:(h0 + lc.num_heads) * Dh]
+    k = w.qkv[:, (H + k0) * Dh:(H + k0 + lc.num_kv_heads) * Dh]
+    v = w.qkv[:, (H + Hkv + k0) * Dh:(H + Hkv + k0 + lc.num_kv_heads) * Dh]
+    qkv = torch.cat([q, k, v], dim=1).contiguous()
+    row = c.tokens_per_block * Dh * c.elem_bytes
+    pool = w.pool.view(2 * w.blocks, Hkv, row)[:, k0:k0 + lc.num_kv_heads].contiguous().view(-1)
+    offs = torch.where(w.offset_table >= 0, w.offset_table // c.block_bytes * lc.block_bytes, w.offset_table)
+    base = pool.data_ptr()
+    ptrs = torch.where(offs >= 0, offs + base, torch.zeros_like(offs))
+    return dataclasses.replace(w, cfg=lc, qkv=qkv, pool=pool, offset_table=offs,
+                               kv_cache_block_pointers=ptrs.to(pool.device), host_kv_cache_block_pointers=ptrs.clone())
+
+
 def make_plugin(cfg: DecodeConfig, device_index: int = 0, *, tp_size: int = 1, tp_rank: int = 0,
                 multi_block_mode: Optional[bool] = None):
     from .plugin import GPTAttentionPlugin

@@ -1,0 +1,108 @@
+"""Generates the committed golden fixtures of the oracle tests.  Run in a container that has the
+reference tree (default /root/reference) and the built checker (make -C oracle quant_check):
+
+    python tests/golden/make_golden.py
+
+Outputs (small, committed):
+  page_table_golden.json  - pointer tables produced by the reference's own Python block manager
+                            (tensorrt_llm/runtime/kv_cache_manager.py, imported by file path) for a
+                            few allocate/step scenarios, as byte offsets from the pool base.
+  quant_golden.npz        - quantise-on-write bytes from the CUDA toolkit's host conversions
+                            (cuda_fp8.h, the header the reference kernels use) for EVERY fp16 and
+                            bf16 bit pattern, int8 vectors including ties and saturation, and the
+                            reference known-answer test's inputs (srand(42), scale 0.1;
+                            cpp/tests/runtime/transposeKVKernelTest.cpp:152, :213-225) with the
+                            expectations of its castTo<> functions (:76-88).
+"""
+import ctypes
+import importlib.util
+import json
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parent.parent
+REF = Path(os.environ.get("DX_REFERENCE_DIR", "/root/reference"))
+
+
+def load_ref_manager():
+    path = REF / "tensorrt_llm" / "runtime" / "kv_cache_manager.py"
+    spec = importlib.util.spec_from_file_location("ref_kv_cache_manager", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def page_tables():
+    m = load_ref_manager()
+    scenarios = []
+    for (blocks, tpb, max_blocks, ctx_lens, steps, elts) in [
+        (16, 8, 6, [5, 8, 17], 10, 64),
+        (40, 64, 4, [1, 63, 64, 65, 130], 3, 128),
+        (12, 16, 5, [30, 31], 20, 32),
+    ]:
+        pool = torch.zeros(2 * blocks * elts, dtype=torch.int8)
+        mgr = m.KVCacheManager([pool], blocks, tpb, max_blocks, max_attention_window_size=max_blocks * tpb,
+                               sink_token_len=0)
+        for i, l in enumerate(ctx_lens):
+            mgr.add_sequence(m.GenerationSequence(seq_idx=i, batch_idx=i), l)
+        base = pool.data_ptr()
+        snaps = []
+
+        def snap():
+            arr = mgr.get_block_pointers(1)  # [pools, B, beam, 2, M]
+            a = arr[0, :, 0]
+            off = torch.where(a != 0, a - base, torch.full_like(a, -1))
+            return off.tolist()
+
+        snaps.append({"lens": list(mgr.lens), "offsets": snap()})
+        for _ in range(steps):
+            mgr.step([False] * len(ctx_lens))
+            snaps.append({"lens": list(mgr.lens), "offsets": snap()})
+        scenarios.append({"blocks": blocks, "tokens_per_block": tpb, "max_blocks_per_seq": max_blocks,
+                          "context_lens": ctx_lens, "block_bytes": elts, "snapshots": snaps})
+    (HERE / "page_table_golden.json").write_text(json.dumps(scenarios))
+
+
+def quant_vectors():
+    lib = ctypes.CDLL(str(ROOT / "oracle" / "_ref" / "libquant_check.so"))
+    u16 = np.arange(65536, dtype=np.uint16)
+    out = {}
+    for name, fn, scale in [("fp16", lib.qc_fp8_from_fp16, 42.5390625), ("bf16", lib.qc_fp8_from_bf16, 42.5390625),
+                            ("fp16_s1", lib.qc_fp8_from_fp16, 1.0), ("bf16_s1", lib.qc_fp8_from_bf16, 1.0)]:
+        res = np.zeros(65536, dtype=np.uint8)
+        fn(u16.ctypes.data_as(ctypes.c_void_p), 65536, ctypes.c_float(scale), res.ctypes.data_as(ctypes.c_void_p))
+        out[f"fp8_from_{name}"] = res
+        out[f"scale_{name}"] = np.float32(scale)
+    # int8: dense grid with exact .5 ties, saturation on both sides, and a typical scale
+    x = np.concatenate([np.arange(-140, 140, 0.25, dtype=np.float32), np.float32([1e6, -1e6, 127.5, -128.5, 0.0])])
+    r = np.zeros(x.size, dtype=np.int8)
+    lib.qc_int8_from_f32(x.ctypes.data_as(ctypes.c_void_p), x.size, ctypes.c_float(1.0), r.ctypes.data_as(ctypes.c_void_p))
+    out["int8_x"], out["int8_q"] = x, r
+    # the reference known-answer test's inputs: srand(42); 10 * rand() / RAND_MAX ; scale 0.1
+    libc = ctypes.CDLL("libc.so.6")
+    libc.srand(42)
+    n = 4096
+    rmax = 2147483647
+    kat = np.array([np.float32(10.0) * np.float32(libc.rand()) / np.float32(rmax) for _ in range(n)], dtype=np.float32)
+    k8 = np.zeros(n, dtype=np.int8)
+    kf = np.zeros(n, dtype=np.uint8)
+    lib.qc_kat_int8(kat.ctypes.data_as(ctypes.c_void_p), n, ctypes.c_float(0.1), k8.ctypes.data_as(ctypes.c_void_p))
+    lib.qc_kat_fp8(kat.ctypes.data_as(ctypes.c_void_p), n, ctypes.c_float(0.1), kf.ctypes.data_as(ctypes.c_void_p))
+    out["kat_x"], out["kat_int8"], out["kat_fp8"] = kat, k8, kf
+    # e4m3 byte -> float table
+    b = np.arange(256, dtype=np.uint8)
+    f = np.zeros(256, dtype=np.float32)
+    lib.qc_fp8_to_f32(b.ctypes.data_as(ctypes.c_void_p), 256, f.ctypes.data_as(ctypes.c_void_p))
+    out["fp8_to_f32"] = f
+    np.savez_compressed(HERE / "quant_golden.npz", **out)
+
+
+if __name__ == "__main__":
+    page_tables()
+    quant_vectors()
+    print("written:", [p.name for p in HERE.iterdir()])

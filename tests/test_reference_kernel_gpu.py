@@ -1,0 +1,61 @@
+"""Pins the oracle against the reference itself: the reference's own MMHA CUDA source, compiled for
+sm_100a from the reference tree by oracle/Makefile (oracle/_ref/libref_mmha.so), runs the same step on
+the GPU.  Bytes appended to the paged cache and their positions must be identical to the oracle's;
+the attention output must agree with the fp32 oracle within the output tolerance (the reference
+keeps the new token un-quantised in its own dot products and rounds P to 16 bits, so it is not
+bit-identical to any other implementation)."""
+import ctypes
+from pathlib import Path
+
+import pytest
+import torch
+
+from helpers import MAX_ABS_TOL, MEAN_ABS_TOL, oracle_step
+
+pytestmark = pytest.mark.gpu
+LIB = Path(__file__).resolve().parent.parent / "oracle" / "_ref" / "libref_mmha.so"
+
+
+def _run_reference(w, tiles=0):
+    cfg = w.cfg
+    lib = ctypes.CDLL(str(LIB))
+    fn = lib.ref_mmha_bf16_128 if (cfg.dtype == torch.bfloat16 and cfg.head_size == 128) else lib.ref_mmha_fp16_64
+    fn.restype = ctypes.c_int
+    out = torch.empty(cfg.batch, cfg.num_heads * cfg.head_size, dtype=cfg.dtype, device=w.qkv.device)
+    ws = torch.zeros(64 << 20, dtype=torch.uint8, device=w.qkv.device)
+    sm = torch.cuda.get_device_properties(0).multi_processor_count
+    window = w.max_blocks_per_seq * cfg.tokens_per_block
+    P = ctypes.c_void_p
+    st = fn(P(w.qkv.data_ptr()), P(out.data_ptr()), P(w.sequence_length.data_ptr()),
+            P(w.kv_cache_block_pointers.data_ptr()), cfg.batch, cfg.num_heads, cfg.num_kv_heads,
+            w.max_blocks_per_seq, cfg.tokens_per_block, window, int(w.host_past_key_value_lengths.max()),
+            ctypes.c_float(1.0), P(w.kv_orig_quant_scale.data_ptr() if w.kv_orig_quant_scale is not None else 0),
+            P(w.kv_quant_orig_scale.data_ptr() if w.kv_quant_orig_scale is not None else 0),
+            int(cfg.cache == "int8"), int(cfg.cache == "fp8"), tiles, P(ws.data_ptr()), sm,
+            P(torch.cuda.current_stream().cuda_stream))
+    assert st == 0, f"reference launcher returned {st}"
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.skipif(not LIB.exists(), reason="oracle/_ref/libref_mmha.so not built (needs the reference tree)")
+@pytest.mark.parametrize("dtype,dh,cache,heads", [
+    (torch.bfloat16, 128, "fp8", (8, 1)),
+    (torch.bfloat16, 128, "int8", (4, 4)),
+    (torch.bfloat16, 128, "int8", (8, 2)),
+    (torch.bfloat16, 128, "none", (4, 2)),
+    (torch.float16, 64, "fp8", (8, 1)),
+    (torch.float16, 64, "none", (4, 4)),
+    (torch.float16, 64, "int8", (4, 2)),
+])
+def test_oracle_matches_reference_mmha_kernel(pkg, dtype, dh, cache, heads):
+    wl = pkg.workloads
+    cfg = wl.DecodeConfig("refx", 4, heads[0], heads[1], dh, dtype, cache, 64, 30, 600, False, 2024)
+    w_cpu = wl.build_workload(cfg, "cpu")
+    w = wl.to_device(w_cpu, "cuda:0")
+    out = _run_reference(w)
+    ref, pool_ref = oracle_step(w_cpu)
+    # bit-exact: the bytes the reference kernel appended, and where
+    assert torch.equal(w.pool.cpu(), pool_ref)
+    err = (out.float().cpu() - ref).abs()
+    assert err.max().item() < MAX_ABS_TOL and err.mean().item() < MEAN_ABS_TOL, (err.max().item(), err.mean().item())
