@@ -76,14 +76,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
     return ok != 0;
 }
 
-// Bounded wait: every spin in this library has an iteration limit.  Returns false when it gave up.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity)
+// Bounded wait: every spin in this library has an iteration limit.  Returns false when it gave up,
+// either because the limit ran out or because another CTA already reported a time-out in the
+// status word (so that one stuck copy cannot add up to many serial time-outs).
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, const int32_t* status)
 {
 #pragma unroll 1
-    for (int it = 0; it < (1 << 22); ++it)
+    for (int it = 0; it < (1 << 20); ++it)
     {
         if (mbar_try_wait(bar, parity))
             return true;
+        if ((it & 255) == 255 && *reinterpret_cast<const volatile int32_t*>(status) != 0)
+            return false;
     }
     return false;
 }

@@ -283,8 +283,8 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
                     whi |= hi << (8 * i);
                     wlo |= lo << (8 * i);
                 }
-                qa[0][s][2 * half + r] = whi;
-                qa[1][s][2 * half + r] = wlo;
+                qa[0][s][2 * half + r] = (r < NR) ? whi : 0u;
+                qa[1][s][2 * half + r] = (r < NR) ? wlo : 0u;
             }
         }
     }
@@ -306,7 +306,7 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
         const uint32_t parity = (i / STAGES) & 1;
         unsigned char* kbuf = ring + s * Tr::STAGE_BYTES;
         unsigned char* vbuf = kbuf + SLAB;
-        if (!mbar_wait_bounded(&bars[s], parity))
+        if (!mbar_wait_bounded(&bars[s], parity, a.status))
         {
             timed_out = true;
             break;

@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(128) mha_decode_kernel(const AttnArgs a)
         const uint32_t parity = (i / STAGES) & 1;
         unsigned char* kbuf = ring + s * Tr::STAGE_BYTES;
         unsigned char* vbuf = kbuf + SLAB;
-        if (!mbar_wait_bounded(&bars[s], parity))
+        if (!mbar_wait_bounded(&bars[s], parity, a.status))
         {
             timed_out = true;
             break;
