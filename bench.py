@@ -255,18 +255,20 @@ def run_own_arm(args):
                                        w.kv_orig_quant_scale, w.kv_quant_orig_scale, h_out, workspace=workspace,
                                        max_attention_window=w.max_blocks_per_seq * cfg.tokens_per_block, sync=True)
 
-    for i in range(3):
-        e2e_step(i)
-    barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for i in range(e2e_steps):
-        e2e_step(i)  # synchronous: the result is in host memory when it returns
-    e1.record(stream)
-    torch.cuda.synchronize()
-    barrier()
-    e2e_ms_local = e0.elapsed_time(e1) / e2e_steps
+    e2e_ms_local = float("nan")
+    if not args.no_e2e:
+        for i in range(3):
+            e2e_step(i)
+        barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(e2e_steps):
+            e2e_step(i)  # synchronous: the result is in host memory when it returns
+        e1.record(stream)
+        torch.cuda.synchronize()
+        barrier()
+        e2e_ms_local = e0.elapsed_time(e1) / e2e_steps
     h2d = h_qkv[0].numel() * 2 + h_len[0].numel() * 4 + h_tbl[0].numel() * 8
     d2h = h_out.numel() * 2
     # the device result of the e2e path equals the resident path's
@@ -301,7 +303,7 @@ def run_own_arm(args):
             "us_per_step": ms * 1e3, "sequences_per_s": full_cfg.batch / (ms * 1e-3),
             "kv_bytes_per_step": kv_bytes_total, "tflops_algorithmic": flops_total / (ms * 1e-3) / 1e12,
             "hbm_frac_of_measured_peak": value / (peak * world), "hbm_frac_of_8TBps_nominal": value / (8000.0 * world),
-            "e2e": {"value": kv_bytes_total / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d * world,
+            "e2e": None if args.no_e2e else {"value": kv_bytes_total / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d * world,
                     "d2h_bytes_per_step": d2h * world, "us_per_step": e2e_ms * 1e3, "steps": e2e_steps},
             "gpu_launches": int(launches_total),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -334,6 +336,7 @@ def main():
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--cpu-sample", type=int, default=32, help="sequences per CPU-oracle step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
 
     if args.impl == "reference":

@@ -13,16 +13,19 @@ import torch
 from helpers import MAX_ABS_TOL, MEAN_ABS_TOL, oracle_step
 
 pytestmark = pytest.mark.gpu
+REF_MAX_ABS_TOL, REF_MEAN_ABS_TOL = 0.5, 0.05
 LIB = Path(__file__).resolve().parent.parent / "oracle" / "_ref" / "libref_mmha.so"
 
 
-def _run_reference(w, tiles=0):
+def _run_reference(w, tiles=0, sync=True, out=None, ws=None):
     cfg = w.cfg
     lib = ctypes.CDLL(str(LIB))
     fn = lib.ref_mmha_bf16_128 if (cfg.dtype == torch.bfloat16 and cfg.head_size == 128) else lib.ref_mmha_fp16_64
     fn.restype = ctypes.c_int
-    out = torch.empty(cfg.batch, cfg.num_heads * cfg.head_size, dtype=cfg.dtype, device=w.qkv.device)
-    ws = torch.zeros(64 << 20, dtype=torch.uint8, device=w.qkv.device)
+    if out is None:
+        out = torch.empty(cfg.batch, cfg.num_heads * cfg.head_size, dtype=cfg.dtype, device=w.qkv.device)
+    if ws is None:
+        ws = torch.zeros(64 << 20, dtype=torch.uint8, device=w.qkv.device)
     sm = torch.cuda.get_device_properties(0).multi_processor_count
     window = w.max_blocks_per_seq * cfg.tokens_per_block
     P = ctypes.c_void_p
@@ -34,7 +37,8 @@ def _run_reference(w, tiles=0):
             int(cfg.cache == "int8"), int(cfg.cache == "fp8"), tiles, P(ws.data_ptr()), sm,
             P(torch.cuda.current_stream().cuda_stream))
     assert st == 0, f"reference launcher returned {st}"
-    torch.cuda.synchronize()
+    if sync:
+        torch.cuda.synchronize()
     return out
 
 
@@ -57,5 +61,53 @@ def test_oracle_matches_reference_mmha_kernel(pkg, dtype, dh, cache, heads):
     ref, pool_ref = oracle_step(w_cpu)
     # bit-exact: the bytes the reference kernel appended, and where
     assert torch.equal(w.pool.cpu(), pool_ref)
+    # The reference kernel multiplies and accumulates q.k in the 16-bit activation type for 16-bit and FP8
+    # caches (no fp32 accumulation for the dot products), so with N(0,1) inputs it sits further from the
+    # fp32 oracle than this library does; its own tests use inputs of order 1e-3.  Gross agreement only.
     err = (out.float().cpu() - ref).abs()
-    assert err.max().item() < MAX_ABS_TOL and err.mean().item() < MEAN_ABS_TOL, (err.max().item(), err.mean().item())
+    print("reference-kernel deviation from the fp32 oracle:", cfg.cache, dtype, err.max().item(), err.mean().item())
+    assert err.max().item() < REF_MAX_ABS_TOL and err.mean().item() < REF_MEAN_ABS_TOL, (err.max().item(), err.mean().item())
+
+
+@pytest.mark.skipif(not LIB.exists(), reason="oracle/_ref/libref_mmha.so not built (needs the reference tree)")
+@pytest.mark.parametrize("name,tp,tiles", [("c4", 8, 0), ("c2", 1, 0), ("c5", 8, 8)])
+def test_report_reference_kernel_time(pkg, name, tp, tiles):
+    """Times the reference MMHA kernel (recompiled for sm_100a) beside this library on the same resident
+    inputs and records both in gpurun_out/ref_kernel_times.jsonl.  Asserts only agreement of results."""
+    import json
+    import os
+    wl = pkg.workloads
+    cfg = wl.shard_config(wl.CONFIGS[name], tp)
+    if name == "c2":
+        cfg = wl.scaled_config(cfg, batch=16)
+    w = wl.build_workload(cfg, "cuda:0")
+    plugin = wl.make_plugin(cfg, 0)
+    ours = wl.run_step(plugin, w)
+    theirs = _run_reference(w, tiles)
+    d = (ours.float() - theirs.float()).abs()
+    assert d.max().item() < REF_MAX_ABS_TOL and d.mean().item() < REF_MEAN_ABS_TOL
+
+    def time_it(fn, n=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n * 1e3
+
+    t_ours = time_it(lambda: wl.run_step(plugin, w))
+    rout = torch.empty_like(ours)
+    rws = torch.zeros(64 << 20, dtype=torch.uint8, device="cuda:0")
+    t_ref = time_it(lambda: _run_reference(w, tiles, sync=False, out=rout, ws=rws), n=5)
+    rec = {"config": cfg.name, "batch": cfg.batch, "ours_us": t_ours, "ref_mmha_sm100a_us": t_ref,
+           "kv_GBps_ours": w.kv_bytes / t_ours / 1e3, "kv_GBps_ref": w.kv_bytes / t_ref / 1e3,
+           "note": "same resident inputs for both; back-to-back calls, so a pool smaller than L2 is L2-warm"}
+    os.makedirs("gpurun_out", exist_ok=True)
+    with open("gpurun_out/ref_kernel_times.jsonl", "a") as f:
+        f.write(json.dumps(rec) + "\n")
+    print(rec)
+    plugin.close()
