@@ -127,8 +127,69 @@ __device__ __forceinline__ void split_hi_lo(float x, uint32_t& hi, uint32_t& lo)
     }
 }
 
-// HL: weight of the high accumulator relative to the low one for the integer path.
+// Weight of the high 8-bit part relative to the low one on the integer path.
 static constexpr int kLoWeight = 128;
+
+// Four values (already scaled into the 8-bit range) -> one word of high parts, one of low parts.
+// FP8: packed conversions, residual taken in f16x2 (exact: hi has 4 significant bits).
+// INT8: round-to-nearest through the 1.5 * 2^23 magic constant; the low byte of the biased float is
+// the two's-complement integer.
+template <int CACHE>
+__device__ __forceinline__ void split4(float x0, float x1, float x2, float x3, uint32_t& hi, uint32_t& lo)
+{
+    if constexpr (CACHE == CACHE_FP8)
+    {
+        uint16_t h01, h23, l01, l23;
+        uint32_t f01, f23, x01, x23;
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(h01) : "f"(x1), "f"(x0));
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(h23) : "f"(x3), "f"(x2));
+        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(f01) : "h"(h01));
+        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(f23) : "h"(h23));
+        asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(x01) : "f"(x1), "f"(x0));
+        asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(x23) : "f"(x3), "f"(x2));
+        asm("sub.f16x2 %0, %1, %2;" : "=r"(x01) : "r"(x01), "r"(f01));
+        asm("sub.f16x2 %0, %1, %2;" : "=r"(x23) : "r"(x23), "r"(f23));
+        asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(l01) : "r"(x01));
+        asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(l23) : "r"(x23));
+        hi = (uint32_t) h01 | ((uint32_t) h23 << 16);
+        lo = (uint32_t) l01 | ((uint32_t) l23 << 16);
+    }
+    else
+    {
+        constexpr float M = 12582912.f;
+        const float y0 = x0 + M, y1 = x1 + M, y2 = x2 + M, y3 = x3 + M;
+        const float z0 = fmaf(x0 - (y0 - M), (float) kLoWeight, M), z1 = fmaf(x1 - (y1 - M), (float) kLoWeight, M);
+        const float z2 = fmaf(x2 - (y2 - M), (float) kLoWeight, M), z3 = fmaf(x3 - (y3 - M), (float) kLoWeight, M);
+        hi = __byte_perm(__byte_perm(__float_as_uint(y0), __float_as_uint(y1), 0x0040),
+            __byte_perm(__float_as_uint(y2), __float_as_uint(y3), 0x0040), 0x5410);
+        lo = __byte_perm(__byte_perm(__float_as_uint(z0), __float_as_uint(z1), 0x0040),
+            __byte_perm(__float_as_uint(z2), __float_as_uint(z3), 0x0040), 0x5410);
+    }
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ uint2 lds64(uint32_t addr)
+{
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ void cp_async16_u32(uint32_t dst, const void* src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+__device__ __forceinline__ void cp_async16_zfill_u32(uint32_t dst, const void* src, uint32_t src_bytes)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
 
 template <typename T, int CACHE, int DH, bool H16>
 __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, const int hgroups)
@@ -137,8 +198,12 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
     using Tr = GqaTraits<DH>;
     constexpr int TG = Tr::TG, KS = Tr::KS, MT = Tr::MT, NW = Tr::NW, QV = Tr::QV;
     constexpr int SLAB = Tr::SLAB, STAGES = Tr::STAGES, NWARPS = Tr::NWARPS;
-    constexpr int NR = H16 ? 2 : 1; // head-row halves in use (rows g, and rows g + 8)
+    constexpr int NR = H16 ? 2 : 1;  // head-row halves in use (rows g, and rows g + 8)
     constexpr bool IS_FP8 = CACHE == CACHE_FP8;
+    // Score accumulator sets: only 16 heads on the integer path need the low part separately
+    // (with <= 8 heads the low parts of Q sit in rows 8..15 of the same MMA).
+    constexpr int NSA = (H16 && !IS_FP8) ? 2 : 1;
+    constexpr int NCP = (DH == 128) ? 2 : 4; // distinct per-lane destination offsets of the copies
     using Acc = typename std::conditional<IS_FP8, float, int>::type;
 
     const int chunk = blockIdx.x;
@@ -155,14 +220,14 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int G = a.num_heads / a.num_kv_heads;
-    const int nh = min(16, G - hg * 16);      // q heads handled by this CTA
-    const int head0 = hk * G + hg * 16;       // first of them
+    const int nh = min(16, G - hg * 16); // q heads handled by this CTA
+    const int head0 = hk * G + hg * 16;  // first of them
     const int tpb_log2 = a.tpb_log2, tpb_mask = (1 << tpb_log2) - 1;
 
     extern __shared__ __align__(1024) unsigned char smem[];
-    unsigned char* ring = smem + warp * (STAGES * Tr::STAGE_BYTES);
     constexpr int BAR_OFF = (Tr::RING_BYTES > Tr::MERGE_BYTES ? Tr::RING_BYTES : Tr::MERGE_BYTES);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BAR_OFF) + warp * STAGES;
+    const uint32_t ring_u32 = smem_u32(smem) + warp * (STAGES * Tr::STAGE_BYTES);
 
     if (lane == 0)
     {
@@ -177,26 +242,45 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
     const int64_t* vrow = krow + a.max_blocks_per_seq;
     const size_t head_off = (size_t) hk * ((size_t) DH << tpb_log2);
 
+    // Per-lane constant destination offsets of the 16-byte copies (copy j of a slab moves linear
+    // bytes [(lane + 32 j) * 16, +16)).
+    uint32_t cdst[NCP];
+#pragma unroll
+    for (int j = 0; j < NCP; ++j)
+        cdst[j] = swz<DH>((uint32_t) (lane + 32 * j) * 16);
+
     // Every lane copies its share of the i-th group of this warp into ring stage i % STAGES.
     auto issue = [&](int i)
     {
         const int gi = warp + NWARPS * i;
         const int t0 = chunk_start + gi * TG;
-        const int rows = min(TG, new_pos - t0); // rows already in the cache
-        unsigned char* kdst = ring + (i % STAGES) * Tr::STAGE_BYTES;
-        unsigned char* vdst = kdst + SLAB;
-        const size_t off = head_off + (size_t) (t0 & tpb_mask) * DH;
+        const int rows = new_pos - t0; // rows already in the cache (>= TG for all but the last group)
+        const uint32_t kdst = ring_u32 + (i % STAGES) * Tr::STAGE_BYTES;
+        const size_t off = head_off + (size_t) (t0 & tpb_mask) * DH + lane * 16;
         const char* kb = reinterpret_cast<const char*>(__ldg(krow + (t0 >> tpb_log2))) + off;
         const char* vb = reinterpret_cast<const char*>(__ldg(vrow + (t0 >> tpb_log2))) + off;
-        const uint32_t valid_bytes = rows > 0 ? (uint32_t) rows * DH : 0u;
-#pragma unroll
-        for (int j = 0; j < SLAB / 512; ++j)
+        if (rows >= TG)
         {
-            const uint32_t lin = (uint32_t) (lane + 32 * j) * 16;
-            const bool ok = lin < valid_bytes;
-            const uint32_t src_off = ok ? lin : 0u;
-            cp_async16_zfill(kdst + swz<DH>(lin), kb + src_off, ok ? 16u : 0u);
-            cp_async16_zfill(vdst + swz<DH>(lin), vb + src_off, ok ? 16u : 0u);
+#pragma unroll
+            for (int j = 0; j < SLAB / 512; ++j)
+            {
+                const uint32_t d = (DH == 128) ? cdst[j & 1] + (j >> 1) * 1024 : cdst[j];
+                cp_async16_u32(kdst + d, kb + j * 512);
+                cp_async16_u32(kdst + SLAB + d, vb + j * 512);
+            }
+        }
+        else
+        {
+            // last group of the sequence: rows at and behind the new token are zero-filled
+            const int valid_bytes = rows > 0 ? rows * DH : 0;
+#pragma unroll
+            for (int j = 0; j < SLAB / 512; ++j)
+            {
+                const uint32_t d = (DH == 128) ? cdst[j & 1] + (j >> 1) * 1024 : cdst[j];
+                const bool ok = (lane + 32 * j) * 16 < valid_bytes;
+                cp_async16_zfill_u32(kdst + d, ok ? kb + j * 512 : kb, ok ? 16u : 0u);
+                cp_async16_zfill_u32(kdst + SLAB + d, ok ? vb + j * 512 : vb, ok ? 16u : 0u);
+            }
         }
         cp_async_mbar_arrive_noinc(&bars[i % STAGES]);
     };
@@ -205,21 +289,22 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
     for (int i = 0; i < min(STAGES, my_groups); ++i)
         issue(i);
 
-    // ---- Q: load the head rows g (and g + 8), scale each row into the 8-bit range, split hi/lo
-    // and pack straight into A fragments.  The k index of every MMA is a fixed permutation of Dh
-    // chosen so that K fragments are plain 16-byte shared-memory loads. ----
+    // ---- Q: load the head rows, scale each row into the 8-bit range, split into high and low
+    // parts and pack straight into A fragments.  The k index of every MMA is a fixed permutation
+    // of Dh chosen so that a K fragment is one (Dh 64) or two (Dh 128) 16-byte shared loads.
+    //   <= 8 heads : one fragment set, rows 0..7 = high parts, rows 8..15 = low parts of head g
+    //   16 heads   : two fragment sets (high, low), rows = heads g and g + 8 ----
     const float deq = __ldg(a.scale_quant_orig);
     const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
     const T* qkv_b = reinterpret_cast<const T*>(a.qkv) + (size_t) b * qkv_stride;
-    uint32_t qa[2][KS][4]; // [hi/lo][k-step][a0..a3]
-    float sfac[2];         // accumulator -> score in log2 units, per head-row half
+    uint32_t qa[NR][KS][4];
+    float sfac[NR]; // accumulator -> score in log2 units, per head-row half
 #pragma unroll
-    for (int r = 0; r < 2; ++r)
+    for (int r = 0; r < NR; ++r)
     {
         float qv[QV];
         const int hl = g + 8 * r; // head within this CTA
-        const bool valid = (r < NR) && hl < nh;
-        if (valid)
+        if (hl < nh)
         {
             const T* qp = qkv_b + (size_t) (head0 + hl) * DH + t * QV;
 #pragma unroll
@@ -272,40 +357,76 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
 #pragma unroll
             for (int half = 0; half < 2; ++half)
             {
-                // elements of this thread that feed a0/a1 (half 0) or a2/a3 (half 1) of k-step s
+                // elements of this thread that feed the low-k (half 0) or high-k (half 1) registers of k-step s
                 const int base = (DH == 128) ? (16 * half + 4 * s) : (8 * s + 4 * half);
-                uint32_t whi = 0, wlo = 0;
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
+                uint32_t whi, wlo;
+                split4<CACHE>(qv[base] * qmul, qv[base + 1] * qmul, qv[base + 2] * qmul, qv[base + 3] * qmul, whi, wlo);
+                if constexpr (H16)
                 {
-                    uint32_t hi, lo;
-                    split_hi_lo<CACHE>(qv[base + i] * qmul, hi, lo);
-                    whi |= hi << (8 * i);
-                    wlo |= lo << (8 * i);
+                    qa[0][s][2 * half + r] = whi; // set 0 = high parts, register = row half r
+                    qa[1][s][2 * half + r] = wlo; // set 1 = low parts
                 }
-                qa[0][s][2 * half + r] = (r < NR) ? whi : 0u;
-                qa[1][s][2 * half + r] = (r < NR) ? wlo : 0u;
+                else
+                {
+                    qa[0][s][2 * half] = whi;     // rows 0..7
+                    qa[0][s][2 * half + 1] = wlo; // rows 8..15
+                }
             }
         }
     }
 
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    // Per-thread shared-memory offsets of the fragment loads (inside a K / V slab).
+    uint32_t koff[4], voff[8];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+        koff[nt] = swz<DH>((uint32_t) sigma_row<DH>(nt, g) * DH + t * (DH / 4));
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        voff[i] = swz<DH>((uint32_t) sigma_row<DH>(i >> 1, 2 * t + (i & 1)) * DH + g * (DH / 8));
+
+    float m[NR], l[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r)
+        m[r] = -INFINITY, l[r] = 0.f;
     float of[MT][NR][4]; // O^T fragments: [m-tile][head half][c0..c3]
+    int oi[IS_FP8 ? 1 : 2][IS_FP8 ? 1 : MT][NR][4]; // integer path: pending high / low sums
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int r = 0; r < NR; ++r)
 #pragma unroll
             for (int c = 0; c < 4; ++c)
+            {
                 of[mt][r][c] = 0.f;
+                if constexpr (!IS_FP8)
+                    oi[0][mt][r][c] = 0, oi[1][mt][r][c] = 0;
+            }
+    // integer path: move the pending integer sums into the fp32 running sums
+    auto fold = [&]()
+    {
+        if constexpr (!IS_FP8)
+        {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int r = 0; r < NR; ++r)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                    {
+                        of[mt][r][c] += (float) (oi[0][mt][r][c] * kLoWeight + oi[1][mt][r][c]);
+                        oi[0][mt][r][c] = 0;
+                        oi[1][mt][r][c] = 0;
+                    }
+        }
+    };
 
     bool timed_out = false;
     for (int i = 0; i < my_groups; ++i)
     {
         const int s = i % STAGES;
         const uint32_t parity = (i / STAGES) & 1;
-        unsigned char* kbuf = ring + s * Tr::STAGE_BYTES;
-        unsigned char* vbuf = kbuf + SLAB;
+        const uint32_t kbuf = ring_u32 + s * Tr::STAGE_BYTES;
+        const uint32_t vbuf = kbuf + SLAB;
         if (!mbar_wait_bounded(&bars[s], parity, a.status))
         {
             timed_out = true;
@@ -313,7 +434,8 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
         }
         const int gi = warp + NWARPS * i;
         const int t0 = chunk_start + gi * TG;
-        if (new_pos >= t0 && new_pos < t0 + TG)
+        const int lim = total - t0; // valid tokens in this group if < TG
+        if (new_pos < t0 + TG)
         {
             // The group ends with the new token: quantise it exactly as it is stored, put it into
             // the staged tile (rows behind it were zero-filled by the copies) and, from the first
@@ -327,9 +449,10 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
                 const T* vp = qkv_b + (size_t) (a.num_heads + a.num_kv_heads + hk) * DH + lane * 16;
                 const uint4 kq = make_cache_vec<T, CACHE, 16>(kp, sc_f, sc_t);
                 const uint4 vq = make_cache_vec<T, CACHE, 16>(vp, sc_f, sc_t);
-                const uint32_t lin = (uint32_t) r_new * DH + lane * 16;
-                *reinterpret_cast<uint4*>(kbuf + swz<DH>(lin)) = kq;
-                *reinterpret_cast<uint4*>(vbuf + swz<DH>(lin)) = vq;
+                const uint32_t lin = swz<DH>((uint32_t) r_new * DH + lane * 16);
+                unsigned char* stage = smem + warp * (STAGES * Tr::STAGE_BYTES) + s * Tr::STAGE_BYTES;
+                *reinterpret_cast<uint4*>(stage + lin) = kq;
+                *reinterpret_cast<uint4*>(stage + SLAB + lin) = vq;
                 if (hg == 0)
                 {
                     const size_t off = head_off + (size_t) (new_pos & tpb_mask) * DH + lane * 16;
@@ -342,10 +465,10 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
             __syncwarp();
         }
 
-        // ---- S = Q K^T for 16 head rows x 32 tokens ----
-        Acc sacc[2][4][4]; // [hi/lo (int8 only)][n-tile][c0..c3]
+        // ---- S = Q K^T for the head rows x 32 tokens ----
+        Acc sacc[NSA][4][4];
 #pragma unroll
-        for (int x = 0; x < 2; ++x)
+        for (int x = 0; x < NSA; ++x)
 #pragma unroll
             for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
@@ -354,14 +477,13 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt)
         {
-            const uint32_t off = (uint32_t) sigma_row<DH>(nt, g) * DH + t * (DH / 4);
             uint32_t kw[2 * KS];
             {
-                const uint4 v0 = *reinterpret_cast<const uint4*>(kbuf + swz<DH>(off));
+                const uint4 v0 = lds128(kbuf + koff[nt]);
                 kw[0] = v0.x, kw[1] = v0.y, kw[2] = v0.z, kw[3] = v0.w;
                 if constexpr (DH == 128)
                 {
-                    const uint4 v1 = *reinterpret_cast<const uint4*>(kbuf + swz<DH>(off + 16));
+                    const uint4 v1 = lds128(kbuf + (koff[nt] ^ 16u));
                     kw[4] = v1.x, kw[5] = v1.y, kw[6] = v1.z, kw[7] = v1.w;
                 }
             }
@@ -373,37 +495,64 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
                 if constexpr (IS_FP8)
                 {
                     mma_e4m3(sacc[0][nt], qa[0][ks], b0, b1);
-                    mma_e4m3(sacc[0][nt], qa[1][ks], b0, b1);
+                    if constexpr (H16)
+                        mma_e4m3(sacc[0][nt], qa[1][ks], b0, b1);
                 }
                 else
                 {
                     mma_s8(sacc[0][nt], qa[0][ks], b0, b1);
-                    mma_s8(sacc[1][nt], qa[1][ks], b0, b1);
+                    if constexpr (H16)
+                        mma_s8(sacc[1][nt], qa[1][ks], b0, b1);
                 }
             }
         }
 
-        // ---- online softmax over the 32 tokens (rows g and g + 8) ----
-        float p[4][4];
-        float mx[2] = {-INFINITY, -INFINITY};
+        // ---- online softmax over the 32 tokens ----
+        float p[4][2 * NR];
+        float mx[NR];
+#pragma unroll
+        for (int r = 0; r < NR; ++r)
+            mx[r] = -INFINITY;
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt)
         {
 #pragma unroll
             for (int c = 0; c < 2 * NR; ++c)
             {
-                const int tok = t0 + sigma_row<DH>(nt, 2 * t + (c & 1));
                 float sv;
-                if constexpr (IS_FP8)
-                    sv = sacc[0][nt][c];
+                if constexpr (H16)
+                {
+                    if constexpr (IS_FP8)
+                        sv = sacc[0][nt][c];
+                    else
+                        sv = (float) (sacc[0][nt][c] * kLoWeight + sacc[NSA - 1][nt][c]);
+                }
                 else
-                    sv = (float) (sacc[0][nt][c] * kLoWeight + sacc[1][nt][c]);
-                sv = (tok < total) ? sv * sfac[c >> 1] : -INFINITY;
-                p[nt][c] = sv;
-                mx[c >> 1] = fmaxf(mx[c >> 1], sv);
+                {
+                    if constexpr (IS_FP8)
+                        sv = sacc[0][nt][c] + sacc[0][nt][c + 2];
+                    else
+                        sv = (float) (sacc[0][nt][c] * kLoWeight + sacc[0][nt][c + 2]);
+                }
+                p[nt][c] = sv * sfac[c >> 1];
             }
         }
-        float alpha[2];
+        if (lim < TG)
+        {
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int c = 0; c < 2 * NR; ++c)
+                    if (sigma_row<DH>(nt, 2 * t + (c & 1)) >= lim)
+                        p[nt][c] = -INFINITY;
+        }
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int c = 0; c < 2 * NR; ++c)
+                mx[c >> 1] = fmaxf(mx[c >> 1], p[nt][c]);
+        float alpha[NR];
+        bool changed = false;
 #pragma unroll
         for (int r = 0; r < NR; ++r)
         {
@@ -411,6 +560,7 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
             const float m_new = fmaxf(m[r], mx[r]);
             alpha[r] = fast_exp2(m[r] - m_new);
+            changed |= m_new != m[r];
             m[r] = m_new;
             l[r] *= alpha[r];
         }
@@ -422,66 +572,64 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
 #pragma unroll
             for (int kh = 0; kh < 2; ++kh)
             {
-                uint32_t whi = 0, wlo = 0;
+                float pv[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
+                for (int q4 = 0; q4 < 4; ++q4)
                 {
-                    const int nt = 2 * kh + (i >> 1);
-                    const float pv = fast_exp2(p[nt][2 * r + (i & 1)] - m[r]);
-                    l[r] += pv;
-                    uint32_t hi, lo;
-                    split_hi_lo<CACHE>(pv * PSCALE, hi, lo);
-                    whi |= hi << (8 * i);
-                    wlo |= lo << (8 * i);
+                    pv[q4] = fast_exp2(p[2 * kh + (q4 >> 1)][2 * r + (q4 & 1)] - m[r]);
+                    l[r] += pv[q4];
                 }
-                pb[r][0][kh] = whi;
-                pb[r][1][kh] = wlo;
+                split4<CACHE>(pv[0] * PSCALE, pv[1] * PSCALE, pv[2] * PSCALE, pv[3] * PSCALE, pb[r][0][kh], pb[r][1][kh]);
             }
         }
 
-        // ---- rescale the running O^T (its columns are heads 2t, 2t+1 (+8)) ----
-        float ac[NR][2];
-#pragma unroll
-        for (int r = 0; r < NR; ++r)
+        // ---- rescale the running O^T when a row maximum moved (its columns are heads 2t, 2t+1 (+8)) ----
+        if (__any_sync(0xffffffffu, changed))
         {
-            ac[r][0] = __shfl_sync(0xffffffffu, alpha[r], 8 * t);
-            ac[r][1] = __shfl_sync(0xffffffffu, alpha[r], 8 * t + 4);
-        }
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
+            fold();
 #pragma unroll
             for (int r = 0; r < NR; ++r)
             {
-                of[mt][r][0] *= ac[r][0];
-                of[mt][r][1] *= ac[r][1];
-                of[mt][r][2] *= ac[r][0];
-                of[mt][r][3] *= ac[r][1];
+                const float a0 = __shfl_sync(0xffffffffu, alpha[r], 8 * t);
+                const float a1 = __shfl_sync(0xffffffffu, alpha[r], 8 * t + 4);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+                {
+                    of[mt][r][0] *= a0;
+                    of[mt][r][1] *= a1;
+                    of[mt][r][2] *= a0;
+                    of[mt][r][3] *= a1;
+                }
             }
+        }
+        else if ((i & 255) == 255)
+        {
+            fold(); // keeps the pending integer sums far from overflow on very long partitions
+        }
 
         // ---- O^T += V^T P^T ----
         uint32_t tr[2][NW][4]; // [k half][word][byte column] -> one A register each
-        {
-            uint32_t rv[8][NW];
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
+        for (int kh = 0; kh < 2; ++kh)
+        {
+            uint32_t rv[4][NW];
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4)
             {
-                const int row = sigma_row<DH>(i >> 1, 2 * t + (i & 1));
                 if constexpr (DH == 128)
                 {
-                    const uint4 v = *reinterpret_cast<const uint4*>(vbuf + swz<DH>((uint32_t) row * DH + g * 16));
-                    rv[i][0] = v.x, rv[i][1] = v.y, rv[i][2] = v.z, rv[i][3] = v.w;
+                    const uint4 v = lds128(vbuf + voff[4 * kh + q4]);
+                    rv[q4][0] = v.x, rv[q4][1] = v.y, rv[q4][2] = v.z, rv[q4][3] = v.w;
                 }
                 else
                 {
-                    const uint2 v = *reinterpret_cast<const uint2*>(vbuf + swz<DH>((uint32_t) row * DH + g * 8));
-                    rv[i][0] = v.x, rv[i][1] = v.y;
+                    const uint2 v = lds64(vbuf + voff[4 * kh + q4]);
+                    rv[q4][0] = v.x, rv[q4][1] = v.y;
                 }
             }
 #pragma unroll
-            for (int kh = 0; kh < 2; ++kh)
-#pragma unroll
-                for (int w = 0; w < NW; ++w)
-                    transpose4x4(rv[4 * kh][w], rv[4 * kh + 1][w], rv[4 * kh + 2][w], rv[4 * kh + 3][w], tr[kh][w]);
+            for (int w = 0; w < NW; ++w)
+                transpose4x4(rv[0][w], rv[1][w], rv[2][w], rv[3][w], tr[kh][w]);
         }
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
@@ -498,12 +646,8 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
                 }
                 else
                 {
-                    int ohi[4] = {0, 0, 0, 0}, olo[4] = {0, 0, 0, 0};
-                    mma_s8(ohi, av, pb[r][0][0], pb[r][0][1]);
-                    mma_s8(olo, av, pb[r][1][0], pb[r][1][1]);
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        of[mt][r][c] += (float) (ohi[c] * kLoWeight + olo[c]);
+                    mma_s8(oi[0][mt][r], av, pb[r][0][0], pb[r][0][1]);
+                    mma_s8(oi[1][mt][r], av, pb[r][1][0], pb[r][1][1]);
                 }
             }
         }
@@ -512,6 +656,7 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
         if (i + STAGES < my_groups)
             issue(i + STAGES);
     }
+    fold();
 
     if (timed_out && lane == 0)
         atomicExch(a.status, STATUS_TIMEOUT);
