@@ -56,7 +56,7 @@ struct dx_attn
     int cache_kind = CACHE_T;
     int tpb_log2 = 0;
     int group = 1; // q heads per kv head
-    int waves = 6; // split-K target: CTAs ~ waves * resident CTAs
+    int waves = 2; // split-K target: CTAs ~ waves * resident CTAs
     int min_chunk = 512;
     KernelInfo k_mha{}, k_gqa8{}, k_gqa16{}, k_merge{};
     int32_t* status_dev = nullptr;

@@ -1,11 +1,15 @@
 // Grouped-head (GQA / MQA) decode attention over an 8-bit paged KV cache on the tensor cores.
 //
 // One CTA per (split-K partition, kv head x 16-head slice of its q group, sequence).  The q heads
-// that share the kv head form the M dimension of S = Q K^T (m16n8k32 MMA, fp8 x fp8 -> fp32 or
-// s8 x s8 -> s32), so every cache byte is fetched from HBM once for the whole group and is fed to
-// the MMA as stored - no per-element dequantisation instruction exists on the read path; the
-// per-tensor scale is folded into the score scale and into the final normalisation.  Q and P are
-// split into a high and a low 8-bit part (two MMAs) so that they keep ~8 significant bits.
+// that share the kv head form the M dimension of S = Q K^T, so every cache byte is fetched from
+// HBM once for the whole group.  The per-tensor dequantisation scale is never applied per element:
+// it is folded into the score scale and into the final normalisation.
+//   FP8 cache : legacy fp8 mma.sync is emulated on sm_100a (conversions + f16 MMA + extra adds), so
+//               the bytes are converted in registers with packed cvt.f16x2.e4m3x2 (exact, one
+//               instruction per two bytes) and fed to m16n8k16 f16 MMAs with fp32 accumulation;
+//               Q and P stay 16-bit.
+//   INT8 cache: bytes go into m16n8k32 s8 MMAs as stored; Q and P are split into a high and a low
+//               8-bit part so that they keep ~15 / ~14 significant bits.
 // P V is computed transposed, O^T[Dh x heads] = V^T P^T, which makes the S accumulator fragments
 // directly usable as the B operand; V^T fragments are built from 16-byte shared-memory loads
 // with a 4x4 byte transpose (PRMT).
@@ -78,20 +82,42 @@ __device__ __forceinline__ void cp_async16_zfill(void* dst_smem, const void* src
                  : "memory");
 }
 
-__device__ __forceinline__ void mma_e4m3(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
-{
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
 __device__ __forceinline__ void mma_s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
 {
     asm volatile(
         "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Two e4m3 bytes (one 16-bit half of a word) -> f16x2, exact.
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2_lo(uint32_t w)
+{
+    uint32_t r;
+    asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, lo; }" : "=r"(r) : "r"(w));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2_hi(uint32_t w)
+{
+    uint32_t r;
+    asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, hi; }" : "=r"(r) : "r"(w));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi)
+{
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
 }
 
 // 4x4 byte transpose: o[j] byte i = r[i] byte j.
@@ -105,26 +131,6 @@ __device__ __forceinline__ void transpose4x4(uint32_t r0, uint32_t r1, uint32_t 
     o[1] = __byte_perm(t0, t1, 0x7632);
     o[2] = __byte_perm(t2, t3, 0x5410);
     o[3] = __byte_perm(t2, t3, 0x7632);
-}
-
-// Split x (already scaled into the 8-bit range) into a high and a low 8-bit part.
-template <int CACHE>
-__device__ __forceinline__ void split_hi_lo(float x, uint32_t& hi, uint32_t& lo)
-{
-    if constexpr (CACHE == CACHE_FP8)
-    {
-        const __nv_fp8_storage_t h = __nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
-        const __half_raw hr = __nv_cvt_fp8_to_halfraw(h, __NV_E4M3);
-        const float hf = __half2float(*reinterpret_cast<const __half*>(&hr));
-        hi = h;
-        lo = __nv_cvt_float_to_fp8(x - hf, __NV_SATFINITE, __NV_E4M3);
-    }
-    else
-    {
-        const float h = rintf(x);
-        hi = (uint32_t) (__float2int_rn(h) & 0xff);
-        lo = (uint32_t) (__float2int_rn((x - h) * 128.f) & 0xff);
-    }
 }
 
 // Weight of the high 8-bit part relative to the low one on the integer path.
@@ -297,7 +303,10 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
     const float deq = __ldg(a.scale_quant_orig);
     const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
     const T* qkv_b = reinterpret_cast<const T*>(a.qkv) + (size_t) b * qkv_stride;
-    uint32_t qa[NR][KS][4];
+    // FP8 cache: Q stays 16-bit (f16 A fragments, one k16 step per 4 channels of a thread);
+    // INT8 cache: 8-bit high/low fragments as described above.
+    constexpr int KS16 = DH / 16;
+    uint32_t qa[IS_FP8 ? 1 : NR][IS_FP8 ? KS16 : KS][4];
     float sfac[NR]; // accumulator -> score in log2 units, per head-row half
 #pragma unroll
     for (int r = 0; r < NR; ++r)
@@ -351,25 +360,44 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
             qinv = qs * (1.f / kLoWeight);
         }
         sfac[r] = qinv * deq * a.softmax_scale_log2;
+        if constexpr (IS_FP8)
+        {
+            // k16 step j of this thread covers channels 4j .. 4j+3 of its QV-channel slice:
+            // (4j, 4j+1) -> k slots (2t, 2t+1), (4j+2, 4j+3) -> k slots (2t+8, 2t+9).
 #pragma unroll
-        for (int s = 0; s < KS; ++s)
+            for (int j = 0; j < KS16; ++j)
+            {
+                qa[0][j][r] = pack_f16x2(qv[4 * j] * qmul, qv[4 * j + 1] * qmul);
+                qa[0][j][2 + r] = pack_f16x2(qv[4 * j + 2] * qmul, qv[4 * j + 3] * qmul);
+                if constexpr (!H16)
+                {
+                    qa[0][j][1] = 0u;
+                    qa[0][j][3] = 0u;
+                }
+            }
+        }
+        else
         {
 #pragma unroll
-            for (int half = 0; half < 2; ++half)
+            for (int s = 0; s < KS; ++s)
             {
-                // elements of this thread that feed the low-k (half 0) or high-k (half 1) registers of k-step s
-                const int base = (DH == 128) ? (16 * half + 4 * s) : (8 * s + 4 * half);
-                uint32_t whi, wlo;
-                split4<CACHE>(qv[base] * qmul, qv[base + 1] * qmul, qv[base + 2] * qmul, qv[base + 3] * qmul, whi, wlo);
-                if constexpr (H16)
+#pragma unroll
+                for (int half = 0; half < 2; ++half)
                 {
-                    qa[0][s][2 * half + r] = whi; // set 0 = high parts, register = row half r
-                    qa[1][s][2 * half + r] = wlo; // set 1 = low parts
-                }
-                else
-                {
-                    qa[0][s][2 * half] = whi;     // rows 0..7
-                    qa[0][s][2 * half + 1] = wlo; // rows 8..15
+                    // elements of this thread that feed the low-k (half 0) or high-k (half 1) registers of k-step s
+                    const int base = (DH == 128) ? (16 * half + 4 * s) : (8 * s + 4 * half);
+                    uint32_t whi, wlo;
+                    split4<CACHE>(qv[base] * qmul, qv[base + 1] * qmul, qv[base + 2] * qmul, qv[base + 3] * qmul, whi, wlo);
+                    if constexpr (H16)
+                    {
+                        qa[0][s][2 * half + r] = whi; // set 0 = high parts, register = row half r
+                        qa[1][s][2 * half + r] = wlo; // set 1 = low parts
+                    }
+                    else
+                    {
+                        qa[0][s][2 * half] = whi;     // rows 0..7
+                        qa[0][s][2 * half + 1] = wlo; // rows 8..15
+                    }
                 }
             }
         }
@@ -487,19 +515,20 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
                     kw[4] = v1.x, kw[5] = v1.y, kw[6] = v1.z, kw[7] = v1.w;
                 }
             }
-#pragma unroll
-            for (int ks = 0; ks < KS; ++ks)
+            if constexpr (IS_FP8)
             {
-                const uint32_t b0 = (DH == 128) ? kw[ks] : kw[2 * ks];
-                const uint32_t b1 = (DH == 128) ? kw[4 + ks] : kw[2 * ks + 1];
-                if constexpr (IS_FP8)
+                // word j of this thread's K bytes = channels 4j..4j+3 = one k16 step
+#pragma unroll
+                for (int j = 0; j < KS16; ++j)
+                    mma_f16(sacc[0][nt], qa[0][j], e4m3x2_to_f16x2_lo(kw[j]), e4m3x2_to_f16x2_hi(kw[j]));
+            }
+            else
+            {
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks)
                 {
-                    mma_e4m3(sacc[0][nt], qa[0][ks], b0, b1);
-                    if constexpr (H16)
-                        mma_e4m3(sacc[0][nt], qa[1][ks], b0, b1);
-                }
-                else
-                {
+                    const uint32_t b0 = (DH == 128) ? kw[ks] : kw[2 * ks];
+                    const uint32_t b1 = (DH == 128) ? kw[4 + ks] : kw[2 * ks + 1];
                     mma_s8(sacc[0][nt], qa[0][ks], b0, b1);
                     if constexpr (H16)
                         mma_s8(sacc[1][nt], qa[1][ks], b0, b1);
@@ -520,20 +549,12 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
             for (int c = 0; c < 2 * NR; ++c)
             {
                 float sv;
-                if constexpr (H16)
-                {
-                    if constexpr (IS_FP8)
-                        sv = sacc[0][nt][c];
-                    else
-                        sv = (float) (sacc[0][nt][c] * kLoWeight + sacc[NSA - 1][nt][c]);
-                }
+                if constexpr (IS_FP8)
+                    sv = sacc[0][nt][c]; // rows g (c = 0, 1) and g + 8 (c = 2, 3)
+                else if constexpr (H16)
+                    sv = (float) (sacc[0][nt][c] * kLoWeight + sacc[NSA - 1][nt][c]);
                 else
-                {
-                    if constexpr (IS_FP8)
-                        sv = sacc[0][nt][c] + sacc[0][nt][c + 2];
-                    else
-                        sv = (float) (sacc[0][nt][c] * kLoWeight + sacc[0][nt][c + 2]);
-                }
+                    sv = (float) (sacc[0][nt][c] * kLoWeight + sacc[0][nt][c + 2]);
                 p[nt][c] = sv * sfac[c >> 1];
             }
         }
@@ -564,8 +585,10 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
             m[r] = m_new;
             l[r] *= alpha[r];
         }
-        constexpr float PSCALE = IS_FP8 ? 256.f : 127.f;
-        uint32_t pb[NR][2][2]; // [head half][hi/lo][b0/b1]
+        // FP8 cache: P as f16 (scaled by 1024 to stay clear of f16 subnormals), pb[r][k16 step][b0/b1];
+        // INT8 cache: P split into high / low 8-bit parts, pb[r][hi/lo][b0/b1].
+        constexpr float PSCALE = IS_FP8 ? 1024.f : 127.f;
+        uint32_t pb[NR][2][2];
 #pragma unroll
         for (int r = 0; r < NR; ++r)
         {
@@ -579,7 +602,15 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
                     pv[q4] = fast_exp2(p[2 * kh + (q4 >> 1)][2 * r + (q4 & 1)] - m[r]);
                     l[r] += pv[q4];
                 }
-                split4<CACHE>(pv[0] * PSCALE, pv[1] * PSCALE, pv[2] * PSCALE, pv[3] * PSCALE, pb[r][0][kh], pb[r][1][kh]);
+                if constexpr (IS_FP8)
+                {
+                    pb[r][kh][0] = pack_f16x2(pv[0] * PSCALE, pv[1] * PSCALE);
+                    pb[r][kh][1] = pack_f16x2(pv[2] * PSCALE, pv[3] * PSCALE);
+                }
+                else
+                {
+                    split4<CACHE>(pv[0] * PSCALE, pv[1] * PSCALE, pv[2] * PSCALE, pv[3] * PSCALE, pb[r][0][kh], pb[r][1][kh]);
+                }
             }
         }
 
@@ -641,8 +672,13 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
             {
                 if constexpr (IS_FP8)
                 {
-                    mma_e4m3(of[mt][r], av, pb[r][0][0], pb[r][0][1]);
-                    mma_e4m3(of[mt][r], av, pb[r][1][0], pb[r][1][1]);
+                    // two k16 steps: tokens of k half 0 (av[0], av[1]) and of k half 1 (av[2], av[3])
+                    const uint32_t a0[4] = {e4m3x2_to_f16x2_lo(av[0]), e4m3x2_to_f16x2_lo(av[1]),
+                        e4m3x2_to_f16x2_hi(av[0]), e4m3x2_to_f16x2_hi(av[1])};
+                    const uint32_t a1[4] = {e4m3x2_to_f16x2_lo(av[2]), e4m3x2_to_f16x2_lo(av[3]),
+                        e4m3x2_to_f16x2_hi(av[2]), e4m3x2_to_f16x2_hi(av[3])};
+                    mma_f16(of[mt][r], a0, pb[r][0][0], pb[r][0][1]);
+                    mma_f16(of[mt][r], a1, pb[r][1][0], pb[r][1][1]);
                 }
                 else
                 {
@@ -693,7 +729,7 @@ __global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, co
     }
     __syncthreads();
 
-    constexpr float ONORM = IS_FP8 ? (1.f / 256.f) : (1.f / (127.f * kLoWeight));
+    constexpr float ONORM = IS_FP8 ? (1.f / 1024.f) : (1.f / (127.f * kLoWeight));
     const float ofac = deq * ONORM;
     const float* base = reinterpret_cast<const float*>(smem);
     for (int idx = threadIdx.x; idx < nh * DH; idx += blockDim.x)
