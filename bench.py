@@ -193,6 +193,8 @@ def run_own_arm(args):
     wl = pkg.workloads
     full_cfg = wl.CONFIGS[args.config]
     tp = world
+    if world == 1 and args.emulate_tp > 1:
+        tp = args.emulate_tp  # one rank's shard of a tp-way job on a single GPU (tuning aid)
     cfg = wl.shard_config(full_cfg, tp)
 
     # ---- inputs resident in HBM; rotate over replicas when one shard would fit in L2 ----
@@ -294,7 +296,7 @@ def run_own_arm(args):
             "config": {"workload": full_cfg.name, "batch": full_cfg.batch, "q_heads": full_cfg.num_heads,
                        "kv_heads": full_cfg.num_kv_heads, "head_size": full_cfg.head_size,
                        "kv_cache": full_cfg.cache, "tokens_per_block": full_cfg.tokens_per_block,
-                       "past_len": [full_cfg.len_lo, full_cfg.len_hi], "parallelism": f"tp{tp} by kv head",
+                       "past_len": [full_cfg.len_lo, full_cfg.len_hi], "parallelism": f"tp{tp} by kv head" + (" (one shard emulated on 1 GPU)" if tp != world else ""),
                        "per_gpu_heads": [cfg.num_heads, cfg.num_kv_heads], "kernel": plan["kernel"],
                        "split_k_partitions": plan["num_partitions"],
                        "tokens_per_partition": plan["tokens_per_partition"],
@@ -337,6 +339,8 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=32, help="sequences per CPU-oracle step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--emulate-tp", type=int, default=1,
+                    help="with --gpus 1: run ONE rank's shard of a tp-way job (tuning aid; value is that shard's)")
     args = ap.parse_args()
 
     if args.impl == "reference":

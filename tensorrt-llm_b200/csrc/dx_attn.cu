@@ -82,7 +82,7 @@ Plan make_plan(const dx_attn* h, int batch, int max_past_len)
         p.hgroups = (h->group + 15) / 16;
         p.heads16 = h->group > 8;
         p.rows = batch * c.num_kv_heads * p.hgroups;
-        resident = 2;
+        resident = (h->cache_kind == CACHE_FP8 && c.head_size == 128 && !p.heads16) ? 3 : 2;
     }
     else
     {

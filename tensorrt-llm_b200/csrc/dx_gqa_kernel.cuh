@@ -34,7 +34,16 @@
 namespace dx
 {
 
-template <int DH>
+// CTAs per SM the kernel is built for: 3 (with a 2-stage ring) where the register budget allows
+// it - more resident warps hide the fixed instruction latencies better than a deeper ring - else 2
+// (3-stage ring).
+template <int CACHE, int DH, bool H16>
+constexpr int gqa_min_blocks()
+{
+    return (CACHE == CACHE_FP8 && DH == 128 && !H16) ? 3 : 2;
+}
+
+template <int DH, int MINB>
 struct GqaTraits
 {
     static constexpr int TG = 32;           // tokens per stage (per warp)
@@ -44,7 +53,7 @@ struct GqaTraits
     static constexpr int QV = DH / 4;       // q elements per thread per head row
     static constexpr int SLAB = TG * DH;    // bytes of K (or V) per stage
     static constexpr int STAGE_BYTES = 2 * SLAB;
-    static constexpr int STAGES = 3;
+    static constexpr int STAGES = (MINB >= 3 && DH == 128) ? 2 : 3;
     static constexpr int NWARPS = 4;
     static constexpr int RING_BYTES = NWARPS * STAGES * STAGE_BYTES;
     static constexpr int MERGE_BYTES = NWARPS * (16 * DH + 32) * 4;
@@ -198,10 +207,10 @@ __device__ __forceinline__ void cp_async16_zfill_u32(uint32_t dst, const void* s
 }
 
 template <typename T, int CACHE, int DH, bool H16>
-__global__ void __launch_bounds__(128, 2) gqa_decode_kernel(const AttnArgs a, const int hgroups)
+__global__ void __launch_bounds__(128, gqa_min_blocks<CACHE, DH, H16>()) gqa_decode_kernel(const AttnArgs a, const int hgroups)
 {
     static_assert(CACHE == CACHE_INT8 || CACHE == CACHE_FP8, "8-bit caches only");
-    using Tr = GqaTraits<DH>;
+    using Tr = GqaTraits<DH, gqa_min_blocks<CACHE, DH, H16>()>;
     constexpr int TG = Tr::TG, KS = Tr::KS, MT = Tr::MT, NW = Tr::NW, QV = Tr::QV;
     constexpr int SLAB = Tr::SLAB, STAGES = Tr::STAGES, NWARPS = Tr::NWARPS;
     constexpr int NR = H16 ? 2 : 1;  // head-row halves in use (rows g, and rows g + 8)
