@@ -140,6 +140,24 @@ int dx_attn_enqueue_generation(dx_attn_t* handle, const dx_attn_generation_param
 int dx_attn_enqueue_generation_host(
     dx_attn_t* handle, const dx_attn_generation_params* params, void* cuda_stream, int32_t sync);
 
+/* No counterpart in the reference.  Same step as dx_attn_enqueue_generation for callers that cannot
+ * hand over a workspace: hosts whose scratch request was fixed before the live batch was known, code
+ * running while the device allocator is frozen or simply absent (cudaMalloc is off limits there).
+ * The split-K partial results go to a fixed DX_STATIC_SCRATCH_BYTES array inside the library's device
+ * image instead of params->workspace (which is ignored); every GPU that loads the library holds that
+ * array until the process exits.  The call allocates nothing and calls no allocating routine.
+ *  - A batch whose partials need more than DX_STATIC_SCRATCH_BYTES is refused with DX_ERR_WORKSPACE
+ *    before anything is launched (dx_attn_workspace_size() tells the need).
+ *  - The first call on a device looks the array's device address up (cudaGetSymbolAddress); make that
+ *    first call before any stream capture.
+ *  - All calls on a device share the one array and it keeps the previous call's contents.  Nothing in
+ *    it has to start at zero, but two calls that overlap on the GPU (different streams, no ordering)
+ *    race on it: serialise them. */
+#define DX_STATIC_SCRATCH_BYTES (8u << 20)
+int dx_attn_enqueue_generation_static_scratch(
+    dx_attn_t* handle, const dx_attn_generation_params* params, void* cuda_stream);
+size_t dx_attn_static_scratch_bytes(void);
+
 /* Host-side check of a block-pointer table against the pool it must point into; launches nothing.
  * Stands in for the bounds checking the reference does not have (its kernels trust the table). */
 int dx_attn_validate(const dx_attn_t* handle, const int64_t* host_block_pointers,

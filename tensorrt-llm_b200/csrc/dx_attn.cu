@@ -9,6 +9,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <new>
 
 #include "../../include/decode_attn.h"
@@ -148,6 +149,42 @@ KernelInfo merge_kernel_info(int dtype, int dh)
     return k;
 }
 } // namespace dx
+
+// ---------------------------------------------------------------------------------------------
+// Fixed split-K scratch for dx_attn_enqueue_generation_static_scratch: lives in the library's
+// device image, so every GPU that loads the library holds DX_STATIC_SCRATCH_BYTES of it until the
+// process exits.  In host code the name below is only a stand-in for the symbol, not an address a
+// kernel could use; the device address is asked for once per device with cudaGetSymbolAddress.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_scratch[DX_STATIC_SCRATCH_BYTES];
+
+namespace
+{
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+void* g_scratch_addr[kMaxDevices] = {};
+
+// Device address of g_static_scratch on `device`, which must be the current device.
+int static_scratch_address(dx_attn* h, int device, void** out)
+{
+    if (device < 0 || device >= kMaxDevices)
+        return DX_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (!g_scratch_addr[device])
+    {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p)
+        {
+            h->last_cuda_error = (int) e;
+            return DX_ERR_CUDA;
+        }
+        g_scratch_addr[device] = p;
+    }
+    *out = g_scratch_addr[device];
+    return DX_OK;
+}
+} // namespace
 
 extern "C" {
 
@@ -508,6 +545,46 @@ int dx_attn_device_status(dx_attn_t* h)
             return st;
     }
     return v == 0 ? DX_OK : (v == STATUS_TIMEOUT ? DX_ERR_TIMEOUT : DX_ERR_CUDA);
+}
+
+size_t dx_attn_static_scratch_bytes(void)
+{
+    return DX_STATIC_SCRATCH_BYTES;
+}
+
+int dx_attn_enqueue_generation_static_scratch(
+    dx_attn_t* h, const dx_attn_generation_params* params, void* cuda_stream)
+{
+    if (!h || !params || params->struct_size != sizeof(dx_attn_generation_params))
+        return DX_ERR_BAD_ARG;
+    if (params->num_requests <= 0)
+        return params->num_requests == 0 ? DX_OK : DX_ERR_BAD_ARG;
+    // Size check first, on the host: the partials of this batch must fit the fixed array.
+    int max_past = params->past_kv_length;
+    if (params->host_past_key_value_lengths)
+    {
+        max_past = 0;
+        for (int i = 0; i < params->num_requests; ++i)
+            max_past = std::max(max_past, params->host_past_key_value_lengths[i]);
+    }
+    if (max_past < 0)
+        return DX_ERR_BAD_ARG;
+    const Plan plan = make_plan(h, params->num_requests, max_past);
+    if (plan.workspace() > (size_t) DX_STATIC_SCRATCH_BYTES)
+        return DX_ERR_WORKSPACE;
+    int st = check_cuda(h, cudaSetDevice(h->cfg.device));
+    if (st != DX_OK)
+        return st;
+    void* scratch = nullptr;
+    st = static_scratch_address(h, h->cfg.device, &scratch); // first call on a device: symbol look-up
+    if (st != DX_OK)
+        return st;
+    // Nothing in the array has to start at zero: every partition the merge reads is written by
+    // this call's attention kernel first.
+    dx_attn_generation_params p = *params;
+    p.workspace = scratch;
+    p.workspace_bytes = DX_STATIC_SCRATCH_BYTES;
+    return dx_attn_enqueue_generation(h, &p, cuda_stream);
 }
 
 int dx_attn_last_cuda_error(const dx_attn_t* h)

@@ -63,6 +63,7 @@ EXPORTED_SYMBOLS = [
     "dx_abi_version", "dx_strerror", "dx_attn_create", "dx_attn_destroy", "dx_attn_workspace_size",
     "dx_attn_enqueue_generation", "dx_attn_enqueue_generation_host", "dx_attn_validate", "dx_attn_plan",
     "dx_attn_device_status", "dx_attn_last_cuda_error", "dx_attn_launch_count",
+    "dx_attn_enqueue_generation_static_scratch", "dx_attn_static_scratch_bytes",
 ]
 
 
@@ -94,6 +95,10 @@ def load_library() -> ctypes.CDLL:
     lib.dx_attn_enqueue_generation_host.restype = ctypes.c_int
     lib.dx_attn_enqueue_generation_host.argtypes = [ctypes.c_void_p, ctypes.POINTER(_GenParams), ctypes.c_void_p,
                                                     ctypes.c_int32]
+    lib.dx_attn_enqueue_generation_static_scratch.restype = ctypes.c_int
+    lib.dx_attn_enqueue_generation_static_scratch.argtypes = [ctypes.c_void_p, ctypes.POINTER(_GenParams),
+                                                              ctypes.c_void_p]
+    lib.dx_attn_static_scratch_bytes.restype = ctypes.c_size_t
     lib.dx_attn_validate.restype = ctypes.c_int
     lib.dx_attn_validate.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
                                      ctypes.c_int32, ctypes.c_void_p, ctypes.c_size_t]
