@@ -57,9 +57,11 @@ struct dx_attn
     int cache_kind = CACHE_T;
     int tpb_log2 = 0;
     int group = 1; // q heads per kv head
-    int waves = 2; // split-K target: CTAs ~ waves * resident CTAs
-    int min_chunk = 512;
-    KernelInfo k_mha{}, k_gqa8{}, k_gqa16{}, k_merge{};
+    int waves = 8;               // bound on the partitions a call may need: waves * SMs * 3 CTAs (workspace sizing)
+    int min_chunk = 256;         // smallest partition bound, tokens
+    int fixed_cost_tokens = 400; // per-CTA fixed cost (prologue, pipeline fill, epilogue) in tokens of streaming time
+    KernelInfo k_mha{}, k_gqa[2]{}, k_merge{}; // k_gqa[16 heads per CTA?]
+    int force_chunk = 0;     // > 0: partition bound forced (tuning)
     int32_t* status_dev = nullptr;
     int last_cuda_error = 0;
     std::atomic<int64_t> launches{0};
@@ -71,38 +73,75 @@ struct dx_attn
 namespace
 {
 
-Plan make_plan(const dx_attn* h, int batch, int max_past_len)
+// Partitions of one sequence of `total` tokens for a partition bound of `target` tokens.
+inline long parts_of(long total, long target)
+{
+    return (total + target - 1) / target;
+}
+
+// Launch plan.  With multi_block_mode the partition bound T is chosen from the (host) lengths so
+// that the CTAs fill k whole waves of resident CTAs, for the k in 1..4 (or no split at all) that
+// minimises  waves * (fixed cost + tokens per CTA);  the kernels then cut every sequence into equal
+// partitions of at most T tokens (partition_of).  host_past may be null: all sequences are then
+// taken to have max_past_len tokens.
+Plan make_plan(const dx_attn* h, int batch, int max_past_len, const int32_t* host_past = nullptr)
 {
     Plan p;
     const dx_attn_config& c = h->cfg;
     const bool grouped = h->group > 1 && h->cache_kind != CACHE_T && c.tokens_per_block >= 32;
     p.kind = grouped ? KIND_GQA : KIND_MHA;
-    int resident = 2;
+    int resident = 2, rows_per_seq = c.num_heads;
     if (grouped)
     {
         p.hgroups = (h->group + 15) / 16;
         p.heads16 = h->group > 8;
-        p.rows = batch * c.num_kv_heads * p.hgroups;
+        rows_per_seq = c.num_kv_heads * p.hgroups;
         resident = (h->cache_kind == CACHE_FP8 && c.head_size == 128 && !p.heads16) ? 3 : 2;
     }
     else
     {
-        p.rows = batch * c.num_heads;
         resident = 3;
     }
-    const int total = max_past_len + 1;
-    int n = 1;
+    p.rows = batch * rows_per_seq;
+    const long max_total = (long) max_past_len + 1;
+    long target = (long) align_up((size_t) max_total, 128);
     if (c.multi_block_mode)
     {
-        const long target = (long) h->sm_count * resident * h->waves;
-        n = (int) ((target + p.rows - 1) / std::max(1, p.rows));
-        n = std::min(n, (total + h->min_chunk - 1) / h->min_chunk);
-        n = std::max(n, 1);
+        const long t_min = std::max<long>(128, h->min_chunk);
+        // Cost model, in tokens of one CTA's streaming time (fitted to measurements on B200):
+        //     cost(T) = waves(T) * fixed + T / 2
+        // waves(T) = CTAs / resident CTA slots, rounded up: every wave pays the per-CTA fixed cost
+        // (prologue, pipeline fill, epilogue) once; T / 2 is the expected idle tail while the last
+        // CTAs finish.  The streaming term (total tokens / slots) does not depend on T.
+        const long slots = (long) h->sm_count * resident;
+        const double fixed = (double) h->fixed_cost_tokens;
+        const long t_max = (long) align_up((size_t) max_total, 128);
+        double best = 1e300;
+        for (long t = std::min(t_min, t_max); t <= t_max;)
+        {
+            long cnt = 0;
+            for (int i = 0; i < batch; ++i)
+                cnt += parts_of(host_past ? (long) host_past[i] + 1 : max_total, t);
+            cnt *= rows_per_seq;
+            const double waves = std::max(1.0, std::ceil((double) cnt / (double) slots - 0.05));
+            const double cost = waves * fixed + 0.5 * (double) std::min(t, max_total);
+            const bool allowed = t == t_max || cnt <= (long) h->waves * slots; // keeps workspace_bound() valid
+            if (allowed && cost < best)
+            {
+                best = cost;
+                target = t;
+            }
+            if (t == t_max)
+                break;
+            // candidate bounds: every 128 tokens up to 2K, then coarser (about 6 % steps)
+            const long step = t < 2048 ? 128 : align_up((size_t) (t / 16), 128);
+            t = std::min(t + step, t_max);
+        }
+        if (h->force_chunk > 0)
+            target = std::min<long>((long) align_up((size_t) h->force_chunk, 128), (long) align_up((size_t) max_total, 128));
     }
-    int chunk = (total + n - 1) / n;
-    chunk = (int) align_up((size_t) chunk, 128);
-    p.chunk_tokens = chunk;
-    p.nsplit = (total + chunk - 1) / chunk;
+    p.chunk_tokens = (int) target;
+    p.nsplit = (int) parts_of(max_total, target);
     if (p.nsplit > 1)
     {
         const size_t qrows = (size_t) batch * c.num_heads;
@@ -110,6 +149,25 @@ Plan make_plan(const dx_attn* h, int batch, int max_past_len)
         p.part_ml_bytes = align_up(qrows * p.nsplit * sizeof(float2), 128);
     }
     return p;
+}
+
+// Upper bound of Plan::workspace() over every length vector with lengths <= max_past_len.
+size_t workspace_bound(const dx_attn* h, int batch, int max_past_len)
+{
+    const dx_attn_config& c = h->cfg;
+    if (!c.multi_block_mode)
+        return 0;
+    const Plan shape = make_plan(h, batch, max_past_len); // for kind / rows only
+    const long rows_per_seq = std::max(1, shape.rows / std::max(1, batch));
+    const long resident = 3;
+    const long max_total = (long) max_past_len + 1;
+    const long t_min = std::max<long>(128, h->min_chunk);
+    long nsplit = std::min(parts_of(max_total, t_min), std::max<long>(1, h->waves * h->sm_count * resident / rows_per_seq));
+    nsplit = std::max<long>(nsplit, shape.nsplit);
+    if (nsplit <= 1)
+        return 0;
+    const size_t qrows = (size_t) batch * c.num_heads;
+    return align_up(qrows * nsplit * c.head_size * sizeof(float), 128) + align_up(qrows * nsplit * sizeof(float2), 128);
 }
 
 int check_cuda(dx_attn* h, cudaError_t e)
@@ -242,6 +300,10 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
         h->waves = std::max(1, atoi(w));
     if (const char* w = getenv("DX_ATTN_MIN_CHUNK"))
         h->min_chunk = std::max(128, atoi(w));
+    if (const char* w = getenv("DX_ATTN_FIXED_COST"))
+        h->fixed_cost_tokens = std::max(0, atoi(w));
+    if (const char* w = getenv("DX_ATTN_FORCE_CHUNK"))
+        h->force_chunk = atoi(w);
 
     int st = check_cuda(h, cudaSetDevice(c.device));
     if (st == DX_OK)
@@ -255,18 +317,16 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
         h->k_merge = merge_kernel_info(c.type_id, c.head_size);
         if (h->cache_kind != CACHE_T)
         {
-            h->k_gqa8 = gqa_kernel_info(c.type_id, h->cache_kind, c.head_size, false);
-            h->k_gqa16 = gqa_kernel_info(c.type_id, h->cache_kind, c.head_size, true);
+            for (int h16 = 0; h16 < 2; ++h16)
+                h->k_gqa[h16] = gqa_kernel_info(c.type_id, h->cache_kind, c.head_size, h16 != 0);
         }
         if (!h->k_mha.fn || !h->k_merge.fn)
             st = DX_ERR_UNSUPPORTED;
     }
     if (st == DX_OK)
         st = set_smem(h, h->k_mha);
-    if (st == DX_OK)
-        st = set_smem(h, h->k_gqa8);
-    if (st == DX_OK)
-        st = set_smem(h, h->k_gqa16);
+    for (int i = 0; i < 2 && st == DX_OK; ++i)
+        st = set_smem(h, h->k_gqa[i]);
     if (st == DX_OK)
         st = check_cuda(h, cudaMalloc(reinterpret_cast<void**>(&h->status_dev), 256));
     if (st == DX_OK)
@@ -298,11 +358,7 @@ size_t dx_attn_workspace_size(const dx_attn_t* h, int32_t batch, int32_t max_pas
 {
     if (!h || batch <= 0 || max_past_len < 0 || !h->cfg.multi_block_mode)
         return 0;
-    // The partition count depends on the batch actually enqueued; cover every batch up to `batch`.
-    size_t need = 0;
-    for (int b = 1; b <= batch; ++b)
-        need = std::max(need, make_plan(h, b, max_past_len).workspace());
-    return need;
+    return workspace_bound(h, batch, max_past_len);
 }
 
 int dx_attn_plan(const dx_attn_t* h, int32_t batch, int32_t max_past_len, int32_t* num_partitions,
@@ -360,7 +416,7 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     if (p.cyclic_attention_window_size < max_past + 1 || p.max_attention_window < max_past + 1)
         return DX_ERR_UNSUPPORTED; // sliding-window / cyclic cache is not implemented
 
-    const Plan plan = make_plan(h, p.num_requests, max_past);
+    const Plan plan = make_plan(h, p.num_requests, max_past, p.host_past_key_value_lengths);
     if (plan.kind == KIND_MHA && c.tokens_per_block < 16)
         return DX_ERR_UNSUPPORTED;
     if (plan.nsplit > 1)
@@ -398,7 +454,7 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
 
     if (plan.kind == KIND_GQA)
     {
-        const KernelInfo& k = plan.heads16 ? h->k_gqa16 : h->k_gqa8;
+        const KernelInfo& k = h->k_gqa[plan.heads16 ? 1 : 0];
         if (!k.fn)
             return DX_ERR_UNSUPPORTED;
         int hgroups = plan.hgroups;
@@ -420,7 +476,19 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     {
         void* args[] = {&a};
         const int rows = p.num_requests * c.num_heads;
-        st = check_cuda(h, cudaLaunchKernel(h->k_merge.fn, dim3((rows + 3) / 4), dim3(128), args, 0, stream));
+        // Programmatic dependent launch: the merge grid is scheduled while the attention grid drains and
+        // blocks in griddepcontrol.wait until that grid has completed (hides the launch gap).
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((rows + 3) / 4);
+        cfg.blockDim = dim3(128);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        st = check_cuda(h, cudaLaunchKernelExC(&cfg, h->k_merge.fn, args));
         if (st != DX_OK)
             return st;
         h->launches.fetch_add(1);
@@ -569,7 +637,7 @@ int dx_attn_enqueue_generation_static_scratch(
     }
     if (max_past < 0)
         return DX_ERR_BAD_ARG;
-    const Plan plan = make_plan(h, params->num_requests, max_past);
+    const Plan plan = make_plan(h, params->num_requests, max_past, params->host_past_key_value_lengths);
     if (plan.workspace() > (size_t) DX_STATIC_SCRATCH_BYTES)
         return DX_ERR_WORKSPACE;
     int st = check_cuda(h, cudaSetDevice(h->cfg.device));

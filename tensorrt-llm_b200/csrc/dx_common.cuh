@@ -35,12 +35,24 @@ struct AttnArgs
     int32_t num_kv_heads;
     int32_t max_blocks_per_seq;
     int32_t tpb_log2;
-    int32_t chunk_tokens; // tokens per split-K partition (multiple of the kernel's token group)
+    int32_t chunk_tokens; // upper bound of tokens per split-K partition (multiple of 128), see partition_of()
     int32_t nsplit;       // grid.x; 1 => kernels write the final output themselves
     float softmax_scale_log2; // log2(e) / (sqrt(Dh) * q_scaling)
 };
 
 static constexpr int32_t STATUS_TIMEOUT = 5;
+
+// Split-K partitioning of one sequence: `total` tokens are cut into the fewest partitions of at
+// most `target` tokens, and those partitions are made equal (rounded up to 128 tokens) so that no
+// CTA is left with a sliver.  Attention kernels and the merge kernel derive the same numbers.
+__host__ __device__ __forceinline__ void partition_of(
+    int total, int target, int part, int& start, int& len, int& nparts)
+{
+    nparts = (total + target - 1) / target;
+    const int size = (((total + nparts - 1) / nparts) + 127) & ~127;
+    start = part * size;
+    len = part < nparts ? (total - start < size ? total - start : size) : 0;
+}
 
 // ----------------------------------------------------------------------------------------------
 // PTX wrappers

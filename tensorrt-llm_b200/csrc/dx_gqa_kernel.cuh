@@ -225,13 +225,14 @@ __global__ void __launch_bounds__(128, gqa_min_blocks<CACHE, DH, H16>()) gqa_dec
     const int hk = blockIdx.y / hgroups, hg = blockIdx.y % hgroups;
     const int b = blockIdx.z;
     const int total = a.seq_len[b];
-    const int chunk_start = chunk * a.chunk_tokens;
-    if (chunk_start >= total)
-        return;
-    const int ctoks = min(a.chunk_tokens, total - chunk_start);
+    int chunk_start, ctoks, nparts;
+    partition_of(total, a.chunk_tokens, chunk, chunk_start, ctoks, nparts);
+    if (chunk >= nparts)
+        return; // ragged batch: this sequence uses fewer partitions
     const int n_groups = (ctoks + TG - 1) / TG;
     const int new_pos = total - 1;
 
+    griddep_launch_dependents(); // the merge kernel may be scheduled; it waits for this grid to finish
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int G = a.num_heads / a.num_kv_heads;
@@ -239,7 +240,7 @@ __global__ void __launch_bounds__(128, gqa_min_blocks<CACHE, DH, H16>()) gqa_dec
     const int head0 = hk * G + hg * 16;  // first of them
     const int tpb_log2 = a.tpb_log2, tpb_mask = (1 << tpb_log2) - 1;
 
-    extern __shared__ __align__(1024) unsigned char smem[];
+    extern __shared__ __align__(128) unsigned char smem[];
     constexpr int BAR_OFF = (Tr::RING_BYTES > Tr::MERGE_BYTES ? Tr::RING_BYTES : Tr::MERGE_BYTES);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BAR_OFF) + warp * STAGES;
     const uint32_t ring_u32 = smem_u32(smem) + warp * (STAGES * Tr::STAGE_BYTES);

@@ -23,7 +23,8 @@ __global__ void __launch_bounds__(128) lse_merge_kernel(const AttnArgs a)
         return;
     const int b = row / a.num_heads;
     const int total = a.seq_len[b];
-    const int n = (total + a.chunk_tokens - 1) / a.chunk_tokens; // partitions this sequence used
+    griddep_wait(); // launched with programmatic stream serialisation: the partials are complete after this
+    const int n = (total + a.chunk_tokens - 1) / a.chunk_tokens; // partitions this sequence used (partition_of)
 
     const float2* ml = a.part_ml + (size_t) row * a.nsplit;
     float M = -INFINITY;

@@ -99,14 +99,15 @@ __global__ void __launch_bounds__(128) mha_decode_kernel(const AttnArgs a)
     const int h = blockIdx.y;
     const int b = blockIdx.z;
     const int total = a.seq_len[b]; // tokens to attend to, new token included
-    const int chunk_start = chunk * a.chunk_tokens;
-    if (chunk_start >= total)
-        return;                                       // ragged batch: this partition is empty
-    const int ctoks = min(a.chunk_tokens, total - chunk_start);
+    int chunk_start, ctoks, nparts;
+    partition_of(total, a.chunk_tokens, chunk, chunk_start, ctoks, nparts);
+    if (chunk >= nparts)
+        return;                                       // ragged batch: this sequence uses fewer partitions
     const int n_groups = (ctoks + TG - 1) / TG;
     const int new_pos = total - 1;                    // cache index of the new token
-    const bool has_new = new_pos >= chunk_start && new_pos < chunk_start + a.chunk_tokens;
+    const bool has_new = chunk == nparts - 1;          // the last partition ends with the new token
 
+    griddep_launch_dependents(); // the merge kernel may be scheduled; it waits for this grid to finish
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane / LPR, sl = lane % LPR;
     const int G = a.num_heads / a.num_kv_heads;

@@ -256,6 +256,44 @@ class GPTAttentionPlugin:
             raise DecodeAttnError(st, "dx_attn_enqueue_generation")
         return out
 
+    def bind_generation(self, qkv: torch.Tensor, sequence_length: torch.Tensor,
+                        host_past_key_value_lengths: torch.Tensor, kv_cache_block_pointers: torch.Tensor,
+                        kv_orig_quant_scale: Optional[torch.Tensor] = None,
+                        kv_quant_orig_scale: Optional[torch.Tensor] = None, *, out: torch.Tensor,
+                        workspace: Optional[torch.Tensor] = None, max_attention_window: Optional[int] = None,
+                        stream: Optional[torch.cuda.Stream] = None, host: bool = False, sync: bool = True):
+        """Pre-marshals one step's arguments and returns a zero-argument callable that only makes the C
+        call (a C++ caller has no marshalling cost; this keeps Python's out of timed loops).  The tensors
+        must stay alive and unchanged in place while the callable is used.  host=True binds the
+        host-buffer entry point instead."""
+        hp = host_past_key_value_lengths.to(torch.int32).contiguous()
+        max_past = int(hp.max()) if hp.numel() else 0
+        dev = torch.device("cuda", self.device)
+        if workspace is None:
+            workspace = self._ensure_workspace(qkv.shape[0], max_past, dev)
+        p, _ = self._params(qkv, sequence_length, hp, kv_cache_block_pointers, kv_orig_quant_scale,
+                            kv_quant_orig_scale, out, workspace, max_attention_window)
+        s = stream if stream is not None else torch.cuda.current_stream(dev)
+        sp = ctypes.c_void_p(s.cuda_stream)
+        pref = ctypes.byref(p)
+        keep = (p, hp, workspace, qkv, sequence_length, kv_cache_block_pointers, out)
+        h = self._h
+        if host:
+            fn, flag = self.lib.dx_attn_enqueue_generation_host, int(sync)
+
+            def call(_keep=keep):
+                st = fn(h, pref, sp, flag)
+                if st != DX_OK:
+                    raise DecodeAttnError(st, "dx_attn_enqueue_generation_host")
+        else:
+            fn = self.lib.dx_attn_enqueue_generation
+
+            def call(_keep=keep):
+                st = fn(h, pref, sp)
+                if st != DX_OK:
+                    raise DecodeAttnError(st, "dx_attn_enqueue_generation")
+        return call
+
     def enqueue_generation_host(self, qkv: torch.Tensor, sequence_length: torch.Tensor,
                                 host_past_key_value_lengths: torch.Tensor, kv_cache_block_pointers: torch.Tensor,
                                 kv_orig_quant_scale: Optional[torch.Tensor], kv_quant_orig_scale: Optional[torch.Tensor],

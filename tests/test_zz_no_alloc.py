@@ -80,28 +80,30 @@ def test_static_scratch_matches_workspace_entry_point(pkg):
 def test_static_scratch_refuses_what_does_not_fit(pkg):
     wl, P = pkg.workloads, pkg.plugin
     lib = pkg.load_library()
-    # many q heads and few rows: the partials need more than the fixed array; nothing may be launched
-    cfg = wl.DecodeConfig("toolarge", 128, 64, 1, 128, torch.bfloat16, "int8", 64, 8000, 9000, True, 5)
+    # 49 short sequences and one very long one: the long one is cut into many partitions and the
+    # dense [rows, partitions] partial buffer outgrows the fixed array; nothing may be launched
+    cfg = wl.DecodeConfig("toolarge", 50, 64, 8, 128, torch.bfloat16, "fp8", 64, 128, 60000, True, 5)
     plugin = wl.make_plugin(cfg, 0)
     try:
-        lens = torch.full((cfg.batch,), 9000, dtype=torch.int32)
-        need = plugin.get_workspace_size(cfg.batch, 9000)
-        if need <= lib.dx_attn_static_scratch_bytes():
-            pytest.skip("plan fits the static scratch on this device")
+        lens = torch.tensor([128] * 49 + [60000], dtype=torch.int32)
+        blocks = (60000 + 1 + 63) // 64
         dummy = torch.zeros(16, dtype=torch.uint8, device="cuda:0")
         p = P._GenParams()
         p.struct_size = ctypes.sizeof(P._GenParams)
         p.attention_input = dummy.data_ptr()
         p.sequence_lengths = dummy.data_ptr()
         p.host_past_key_value_lengths = lens.data_ptr()
-        p.beam_width, p.num_requests, p.max_blocks_per_sequence = 1, cfg.batch, 141
-        p.max_attention_window = p.cyclic_attention_window_size = 141 * 64
+        p.beam_width, p.num_requests, p.max_blocks_per_sequence = 1, cfg.batch, blocks
+        p.max_attention_window = p.cyclic_attention_window_size = blocks * 64
         p.block_pointers = dummy.data_ptr()
         p.kv_scale_orig_quant = p.kv_scale_quant_orig = dummy.data_ptr()
         p.context_buf = dummy.data_ptr()
         n0 = plugin.launch_count()
         st = lib.dx_attn_enqueue_generation_static_scratch(plugin._h, ctypes.byref(p), None)
-        assert st == P.DX_ERR_WORKSPACE
+        assert st == P.DX_ERR_WORKSPACE, st
         assert plugin.launch_count() == n0
+        # the regular entry point asks for the same memory through its workspace argument
+        assert lib.dx_attn_enqueue_generation(plugin._h, ctypes.byref(p), None) == P.DX_ERR_WORKSPACE
+        assert plugin.get_workspace_size(cfg.batch, 60000) > lib.dx_attn_static_scratch_bytes()
     finally:
         plugin.close()
