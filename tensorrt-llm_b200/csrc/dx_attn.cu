@@ -313,7 +313,7 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
             h, cudaDeviceGetAttribute(&h->max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, c.device));
     if (st == DX_OK)
     {
-        h->k_mha = mha_kernel_info(c.type_id, h->cache_kind, c.head_size);
+        h->k_mha = mha_kernel_info(c.type_id, h->cache_kind, c.head_size, c.tokens_per_block);
         h->k_merge = merge_kernel_info(c.type_id, c.head_size);
         if (h->cache_kind != CACHE_T)
         {

@@ -26,10 +26,17 @@ __global__ void __launch_bounds__(128) lse_merge_kernel(const AttnArgs a)
     griddep_wait(); // launched with programmatic stream serialisation: the partials are complete after this
     const int n = (total + a.chunk_tokens - 1) / a.chunk_tokens; // partitions this sequence used (partition_of)
 
+    // (m, l) of up to 32 partitions per pass, one per lane: all loads of a pass are in flight together.
     const float2* ml = a.part_ml + (size_t) row * a.nsplit;
     float M = -INFINITY;
-    for (int c = 0; c < n; ++c)
-        M = fmaxf(M, ml[c].x);
+    for (int c0 = 0; c0 < n; c0 += 32)
+    {
+        const float mc = (c0 + lane < n) ? ml[c0 + lane].x : -INFINITY;
+        M = fmaxf(M, mc);
+    }
+#pragma unroll
+    for (int x = 16; x >= 1; x >>= 1)
+        M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, x));
 
     float L = 0.f;
     float o[VPL];
@@ -37,26 +44,52 @@ __global__ void __launch_bounds__(128) lse_merge_kernel(const AttnArgs a)
     for (int i = 0; i < VPL; ++i)
         o[i] = 0.f;
     const float* po = a.part_o + (size_t) row * a.nsplit * DH + lane * VPL;
-    for (int c = 0; c < n; ++c)
+    for (int c0 = 0; c0 < n; c0 += 32)
     {
-        const float2 v = ml[c];
-        const float f = fast_exp2(v.x - M);
-        L = fmaf(v.y, f, L);
-        if constexpr (VPL == 4)
+        // lane j holds the weight of partition c0 + j
+        float f = 0.f, lw = 0.f;
+        if (c0 + lane < n)
         {
-            const float4 p = *reinterpret_cast<const float4*>(po + (size_t) c * DH);
-            o[0] = fmaf(p.x, f, o[0]);
-            o[1] = fmaf(p.y, f, o[1]);
-            o[2] = fmaf(p.z, f, o[2]);
-            o[3] = fmaf(p.w, f, o[3]);
+            const float2 v = ml[c0 + lane];
+            f = fast_exp2(v.x - M);
+            lw = v.y * f;
         }
-        else
+        L += lw;
+        const int cnt = min(32, n - c0);
+        for (int j0 = 0; j0 < cnt; j0 += 8)
         {
-            const float2 p = *reinterpret_cast<const float2*>(po + (size_t) c * DH);
-            o[0] = fmaf(p.x, f, o[0]);
-            o[1] = fmaf(p.y, f, o[1]);
+            // 8 independent row loads, then the weighted sums
+            float v[8][VPL];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+            {
+                const int c = min(c0 + j0 + j, n - 1); // clamped: weight of a padded slot is 0
+                if constexpr (VPL == 4)
+                {
+                    const float4 q = *reinterpret_cast<const float4*>(po + (size_t) c * DH);
+                    v[j][0] = q.x, v[j][1] = q.y, v[j][2] = q.z, v[j][3] = q.w;
+                }
+                else
+                {
+                    const float2 q = *reinterpret_cast<const float2*>(po + (size_t) c * DH);
+                    v[j][0] = q.x, v[j][1] = q.y;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+            {
+                float fj = __shfl_sync(0xffffffffu, f, (j0 + j) & 31);
+                if (j0 + j >= cnt)
+                    fj = 0.f;
+#pragma unroll
+                for (int i = 0; i < VPL; ++i)
+                    o[i] = fmaf(v[j][i], fj, o[i]);
+            }
         }
     }
+#pragma unroll
+    for (int x = 16; x >= 1; x >>= 1)
+        L += __shfl_xor_sync(0xffffffffu, L, x);
     const float inv = 1.f / L;
     T* dst = reinterpret_cast<T*>(a.out) + (size_t) row * DH + lane * VPL;
     if constexpr (VPL == 4)

@@ -1,5 +1,6 @@
 // Instantiations of the CUDA-core multi-head decode kernel.
 #include "dx_launch.h"
+#include "dx_mha_int8_kernel.cuh"
 #include "dx_mha_kernel.cuh"
 
 namespace dx
@@ -31,8 +32,22 @@ static KernelInfo by_cache_dh(int cache, int dh)
     return KernelInfo{};
 }
 
-KernelInfo mha_kernel_info(int dtype, int cache, int dh)
+template <typename T, int DH>
+static KernelInfo mk_int8()
 {
+    KernelInfo k;
+    k.fn = reinterpret_cast<const void*>(&mha_int8_decode_kernel<T, DH>);
+    k.smem = MhaInt8Traits<DH>::SMEM_BYTES;
+    return k;
+}
+
+KernelInfo mha_kernel_info(int dtype, int cache, int dh, int tokens_per_block)
+{
+    // INT8 caches take the integer (dp4a) kernel when a token group fits a cache block.
+    if (cache == CACHE_INT8 && dh == 128 && tokens_per_block >= MhaInt8Traits<128>::TG)
+        return dtype == 0 ? mk_int8<__half, 128>() : mk_int8<__nv_bfloat16, 128>();
+    if (cache == CACHE_INT8 && dh == 64 && tokens_per_block >= MhaInt8Traits<64>::TG)
+        return dtype == 0 ? mk_int8<__half, 64>() : mk_int8<__nv_bfloat16, 64>();
     return dtype == 0 ? by_cache_dh<__half>(cache, dh) : by_cache_dh<__nv_bfloat16>(cache, dh);
 }
 } // namespace dx
