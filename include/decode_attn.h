@@ -158,6 +158,16 @@ int dx_attn_enqueue_generation_static_scratch(
     dx_attn_t* handle, const dx_attn_generation_params* params, void* cuda_stream);
 size_t dx_attn_static_scratch_bytes(void);
 
+/* Context-phase KV append: stores the K and V of whole prompts, k_src / v_src = device T
+ * [batch, num_kv_heads, seq_len, head_size], into the paged cache with the same quantise-on-write as the
+ * decode step; tokens at or beyond sequence_lengths[b] are skipped.  Replaces invokeTranspose4dBatchMajor
+ * (cpp/tensorrt_llm/kernels/unfusedAttentionKernels.cu:1638-1666), same argument meaning.
+ * attention_window_size < seq_len (cyclic cache) is not implemented: DX_ERR_UNSUPPORTED. */
+int dx_attn_append_context(dx_attn_t* handle, const void* k_src, const void* v_src,
+    const int32_t* sequence_lengths, int32_t batch, int32_t seq_len, int32_t attention_window_size,
+    const int64_t* block_pointers, int32_t max_blocks_per_sequence, const float* kv_scale_orig_quant,
+    void* cuda_stream);
+
 /* Host-side check of a block-pointer table against the pool it must point into; launches nothing.
  * Stands in for the bounds checking the reference does not have (its kernels trust the table). */
 int dx_attn_validate(const dx_attn_t* handle, const int64_t* host_block_pointers,

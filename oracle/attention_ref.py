@@ -73,3 +73,28 @@ def decode_attention_reference(qkv: torch.Tensor, sequence_lengths: torch.Tensor
         o = torch.matmul(p, V)  # [Hkv, G, Dh]
         out[b] = o.reshape(H * Dh)
     return out
+
+
+def append_context_reference(k: torch.Tensor, v: torch.Tensor, sequence_lengths: torch.Tensor, pool: torch.Tensor,
+                             offset_table: torch.Tensor, *, tokens_per_block: int, cache_mode: int,
+                             kv_scale_orig_quant: float = 1.0) -> None:
+    """Context-phase KV write, restated from transpose4dBatchMajorKVCache
+    (cpp/tensorrt_llm/kernels/unfusedAttentionKernels.cu:1565-1636): for every sequence b, head h and token
+    t < sequence_lengths[b], the (quantised) K[b, h, t, :] goes to block offset_table[b, 0, t // tpb] at local
+    index (h * tpb + t % tpb) * Dh (kvCacheUtils.h:144-152), V likewise through row 1.
+    k, v: T [B, Hkv, seq_len, Dh] on CPU; pool: uint8, mutated in place."""
+    B, Hkv, L, Dh = k.shape
+    esz = 2 if cache_mode == CACHE_T else 1
+    row = Dh * esz
+    blk = Hkv * tokens_per_block * row
+    pool_blocks = pool.view(-1, Hkv, tokens_per_block, row)
+    kq = quantize_kv(k, kv_scale_orig_quant, cache_mode)  # [B, Hkv, L, row]
+    vq = quantize_kv(v, kv_scale_orig_quant, cache_mode)
+    for b in range(B):
+        n = min(int(sequence_lengths[b]), L)
+        for t0 in range(0, n, tokens_per_block):
+            t1 = min(n, t0 + tokens_per_block)
+            ko, vo = int(offset_table[b, 0, t0 // tokens_per_block]), int(offset_table[b, 1, t0 // tokens_per_block])
+            assert ko >= 0 and vo >= 0 and ko % blk == 0 and vo % blk == 0
+            pool_blocks[ko // blk, :, : t1 - t0, :] = kq[b, :, t0:t1]
+            pool_blocks[vo // blk, :, : t1 - t0, :] = vq[b, :, t0:t1]

@@ -13,6 +13,7 @@
 #include <new>
 
 #include "../../include/decode_attn.h"
+#include "dx_append_kernel.cuh"
 #include "dx_launch.h"
 #include "dx_merge_kernel.cuh"
 
@@ -60,7 +61,7 @@ struct dx_attn
     int waves = 8;               // bound on the partitions a call may need: waves * SMs * 3 CTAs (workspace sizing)
     int min_chunk = 256;         // smallest partition bound, tokens
     int fixed_cost_tokens = 400; // per-CTA fixed cost (prologue, pipeline fill, epilogue) in tokens of streaming time
-    KernelInfo k_mha{}, k_gqa[2]{}, k_merge{}; // k_gqa[16 heads per CTA?]
+    KernelInfo k_mha{}, k_gqa[2]{}, k_merge{}, k_append{}; // k_gqa[16 heads per CTA?]
     int force_chunk = 0;     // > 0: partition bound forced (tuning)
     int32_t* status_dev = nullptr;
     int last_cuda_error = 0;
@@ -315,6 +316,7 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
     {
         h->k_mha = mha_kernel_info(c.type_id, h->cache_kind, c.head_size, c.tokens_per_block);
         h->k_merge = merge_kernel_info(c.type_id, c.head_size);
+        h->k_append = append_kernel_info(c.type_id, h->cache_kind, c.head_size);
         if (h->cache_kind != CACHE_T)
         {
             for (int h16 = 0; h16 < 2; ++h16)
@@ -653,6 +655,51 @@ int dx_attn_enqueue_generation_static_scratch(
     p.workspace = scratch;
     p.workspace_bytes = DX_STATIC_SCRATCH_BYTES;
     return dx_attn_enqueue_generation(h, &p, cuda_stream);
+}
+
+int dx_attn_append_context(dx_attn_t* h, const void* k_src, const void* v_src, const int32_t* sequence_lengths,
+    int32_t batch, int32_t seq_len, int32_t attention_window_size, const int64_t* block_pointers,
+    int32_t max_blocks_per_sequence, const float* kv_scale_orig_quant, void* cuda_stream)
+{
+    if (!h || batch < 0 || seq_len < 0 || max_blocks_per_sequence <= 0)
+        return DX_ERR_BAD_ARG;
+    if (batch == 0 || seq_len == 0)
+        return DX_OK;
+    if (!k_src || !v_src || !sequence_lengths || !block_pointers)
+        return DX_ERR_BAD_ARG;
+    if ((((uintptr_t) k_src | (uintptr_t) v_src) & 15) || ((uintptr_t) block_pointers & 7))
+        return DX_ERR_BAD_ARG;
+    const dx_attn_config& c = h->cfg;
+    if (h->cache_kind != CACHE_T && !kv_scale_orig_quant)
+        return DX_ERR_BAD_ARG;
+    if (attention_window_size < seq_len)
+        return DX_ERR_UNSUPPORTED; // cyclic cache (dropping the oldest tokens) is not implemented
+    if ((int64_t) seq_len > (int64_t) max_blocks_per_sequence * c.tokens_per_block)
+        return DX_ERR_BAD_ARG;
+    if (!h->k_append.fn)
+        return DX_ERR_UNSUPPORTED;
+    AppendArgs a{};
+    a.k_src = k_src;
+    a.v_src = v_src;
+    a.seq_len = sequence_lengths;
+    a.block_ptrs = block_pointers;
+    a.scale_orig_quant = kv_scale_orig_quant;
+    a.batch = batch;
+    a.num_kv_heads = c.num_kv_heads;
+    a.src_seq_len = seq_len;
+    a.max_blocks_per_seq = max_blocks_per_sequence;
+    a.tpb_log2 = h->tpb_log2;
+    int st = check_cuda(h, cudaSetDevice(c.device));
+    if (st != DX_OK)
+        return st;
+    const int esz = h->cache_kind == CACHE_T ? 2 : 1;
+    const long threads = (long) seq_len * (c.head_size * esz / 16);
+    void* args[] = {&a};
+    dim3 grid((unsigned) ((threads + 255) / 256), batch, c.num_kv_heads);
+    st = check_cuda(h, cudaLaunchKernel(h->k_append.fn, grid, dim3(256), args, 0, reinterpret_cast<cudaStream_t>(cuda_stream)));
+    if (st == DX_OK)
+        h->launches.fetch_add(1);
+    return st;
 }
 
 int dx_attn_last_cuda_error(const dx_attn_t* h)

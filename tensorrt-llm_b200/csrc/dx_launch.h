@@ -14,4 +14,5 @@ struct KernelInfo
 KernelInfo mha_kernel_info(int dtype, int cache, int dh, int tokens_per_block);
 KernelInfo gqa_kernel_info(int dtype, int cache, int dh, bool heads16);
 KernelInfo merge_kernel_info(int dtype, int dh);
+KernelInfo append_kernel_info(int dtype, int cache, int dh);
 } // namespace dx

@@ -1,5 +1,6 @@
 // Instantiations of the CUDA-core multi-head decode kernel.
 #include "dx_launch.h"
+#include "dx_append_kernel.cuh"
 #include "dx_mha_int8_kernel.cuh"
 #include "dx_mha_kernel.cuh"
 
@@ -49,5 +50,26 @@ KernelInfo mha_kernel_info(int dtype, int cache, int dh, int tokens_per_block)
     if (cache == CACHE_INT8 && dh == 64 && tokens_per_block >= MhaInt8Traits<64>::TG)
         return dtype == 0 ? mk_int8<__half, 64>() : mk_int8<__nv_bfloat16, 64>();
     return dtype == 0 ? by_cache_dh<__half>(cache, dh) : by_cache_dh<__nv_bfloat16>(cache, dh);
+}
+template <typename T>
+static KernelInfo append_by(int cache, int dh)
+{
+    KernelInfo k;
+#define DX_APPEND_CASE(C, D)                                                                       \
+    if (cache == C && dh == D)                                                                     \
+        k.fn = reinterpret_cast<const void*>(&kv_append_context_kernel<T, C, D>);
+    DX_APPEND_CASE(CACHE_T, 64)
+    DX_APPEND_CASE(CACHE_T, 128)
+    DX_APPEND_CASE(CACHE_INT8, 64)
+    DX_APPEND_CASE(CACHE_INT8, 128)
+    DX_APPEND_CASE(CACHE_FP8, 64)
+    DX_APPEND_CASE(CACHE_FP8, 128)
+#undef DX_APPEND_CASE
+    return k;
+}
+
+KernelInfo append_kernel_info(int dtype, int cache, int dh)
+{
+    return dtype == 0 ? append_by<__half>(cache, dh) : append_by<__nv_bfloat16>(cache, dh);
 }
 } // namespace dx
