@@ -74,7 +74,22 @@ typedef struct dx_attn_config
     int32_t tokens_per_block;    /* power of two, 16..256                                              */
     int32_t type_id;             /* DX_DTYPE_FP16 / DX_DTYPE_BF16                                      */
     int32_t device;              /* CUDA device ordinal this handle launches on                        */
+    /* --- optional tail (struct_size tells whether it is present; absent = all zero) ---
+     * In-step pre-processing of the packed QKV row, as the reference kernels do it
+     * (decoderMaskedMultiheadAttentionTemplate.h:1587-1712): bias add, then rotary embedding on q and k.
+     * Values of position_embedding_type / rotary_embedding_scale_type are the reference's
+     * (cpp/tensorrt_llm/kernels/gptKernels.h:41-58): 0 learned-absolute (nothing to do), 1 RoPE GPT-J,
+     * 2 RoPE GPT-NeoX; scale type 0 none, 1 linear, 2 dynamic.  ALiBi / relative: DX_ERR_UNSUPPORTED. */
+    int32_t position_embedding_type;
+    int32_t rotary_embedding_dim;
+    float rotary_embedding_base;
+    int32_t rotary_embedding_scale_type;
+    float rotary_embedding_scale;
+    int32_t rotary_embedding_max_positions;
+    int32_t qkv_bias_enabled;    /* 1: calls may pass dx_attn_generation_params.qkv_bias (sizes the workspace) */
 } dx_attn_config;
+/* size of dx_attn_config without the optional tail (accepted by dx_attn_create) */
+#define DX_ATTN_CONFIG_SIZE_V1 60u
 
 /* Per-call arguments.  Field names and meaning follow
  * GPTAttentionPluginCommon::EnqueueGenerationParams
@@ -113,7 +128,11 @@ typedef struct dx_attn_generation_params
     void* workspace;                  /* device, >= dx_attn_workspace_size(); 128-byte aligned      */
     size_t workspace_bytes;
     const int32_t* cache_indir; /* must be NULL (beam search not implemented)                      */
+    /* optional tail: device, T [(num_heads + 2*num_kv_heads) * head_size] or NULL (plugin input qkv_bias) */
+    const void* qkv_bias;
 } dx_attn_generation_params;
+/* size of dx_attn_generation_params without the optional tail (accepted by the enqueue calls) */
+#define DX_ATTN_GENERATION_PARAMS_SIZE_V1 (sizeof(dx_attn_generation_params) - sizeof(void*))
 
 typedef struct dx_attn dx_attn_t;
 
@@ -124,7 +143,8 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out);
 void dx_attn_destroy(dx_attn_t* handle);
 
 /* Replaces GPTAttentionPluginCommon::getWorkspaceSizeForGeneration (gptAttentionCommon.cpp:585-626).
- * Upper bound for any call with num_requests <= batch; 0 when multi_block_mode is off. */
+ * Upper bound for any call with num_requests <= batch; 0 when multi_block_mode is off and no in-step
+ * pre-processing (bias / rotary embedding) is configured. */
 size_t dx_attn_workspace_size(const dx_attn_t* handle, int32_t batch, int32_t max_past_len);
 
 /* Replaces GPTAttentionPluginCommon::enqueueGeneration (gptAttentionCommon.cpp:1159-1364). */

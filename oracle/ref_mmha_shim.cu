@@ -56,7 +56,9 @@ extern "C" int REF_CAT(REF_FN(ref_mmha), REF_DH)(const void* qkv, void* out, con
     int64_t* block_pointers_dev, int32_t batch, int32_t num_heads, int32_t num_kv_heads, int32_t max_blocks_per_seq,
     int32_t tokens_per_block, int32_t max_attention_window, int32_t past_kv_length, float q_scaling,
     const float* kv_scale_orig_quant_dev, const float* kv_scale_quant_orig_dev, int32_t int8_kv, int32_t fp8_kv,
-    int32_t tiles, void* workspace, int32_t sm_count, cudaStream_t stream)
+    int32_t tiles, void* workspace, int32_t sm_count, cudaStream_t stream, const void* qkv_bias,
+    int32_t position_embedding_type, int32_t rotary_embedding_dim, float rotary_embedding_base,
+    int32_t rotary_embedding_scale_type, float rotary_embedding_scale, int32_t rotary_embedding_max_positions)
 {
     const int Dh = REF_DH;
     const size_t elem = (int8_kv || fp8_kv) ? 1 : sizeof(RefT);
@@ -90,7 +92,18 @@ extern "C" int REF_CAT(REF_FN(ref_mmha), REF_DH)(const void* qkv, void* out, con
     p.num_heads = num_heads;
     p.num_kv_heads = num_kv_heads;
     p.hidden_size_per_head = Dh;
-    p.position_embedding_type = PositionEmbeddingType::kLEARNED_ABSOLUTE;
+    p.position_embedding_type = static_cast<PositionEmbeddingType>(position_embedding_type);
+    p.rotary_embedding_dim = rotary_embedding_dim;
+    p.rotary_embedding_base = rotary_embedding_base;
+    p.rotary_embedding_scale_type = static_cast<RotaryScalingType>(rotary_embedding_scale_type);
+    p.rotary_embedding_scale = rotary_embedding_scale;
+    p.rotary_embedding_max_positions = rotary_embedding_max_positions;
+    if (qkv_bias)
+    {
+        p.q_bias = reinterpret_cast<const RefT*>(qkv_bias);
+        p.k_bias = p.q_bias + hq;
+        p.v_bias = p.q_bias + hq + hkv;
+    }
     p.inv_sqrt_dh = 1.F / (sqrtf((float) Dh) * q_scaling);
     p.multi_processor_count = sm_count;
     p.multi_block_mode = tiles > 1;

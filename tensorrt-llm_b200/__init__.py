@@ -4,8 +4,8 @@ of TensorRT-LLM's GPT attention plugin).
 The directory name contains a hyphen, so import it through ``__graft_entry__.load_package()``
 (registers it as ``tensorrt_llm_b200``) or put an importlib spec on it yourself.
 """
-from .plugin import (DX_OK, DecodeAttnError, GPTAttentionPlugin, QuantMode, gpt_attention, library_path,  # noqa: F401
-                     load_library)
+from .plugin import (DX_OK, DecodeAttnError, GPTAttentionPlugin, PositionEmbeddingType, QuantMode,  # noqa: F401
+                     RotaryScalingType, gpt_attention, library_path, load_library)
 from . import workloads  # noqa: F401
 
 __all__ = ["GPTAttentionPlugin", "QuantMode", "gpt_attention", "DecodeAttnError", "load_library", "library_path",

@@ -16,6 +16,7 @@
 #include "dx_append_kernel.cuh"
 #include "dx_launch.h"
 #include "dx_merge_kernel.cuh"
+#include "dx_prep_kernel.cuh"
 
 using namespace dx;
 
@@ -63,6 +64,7 @@ struct dx_attn
     int fixed_cost_tokens = 400; // per-CTA fixed cost (prologue, pipeline fill, epilogue) in tokens of streaming time
     KernelInfo k_mha{}, k_gqa[2]{}, k_merge{}, k_append{}; // k_gqa[16 heads per CTA?]
     int force_chunk = 0;     // > 0: partition bound forced (tuning)
+    bool prep = false; // bias / rotary embedding configured: QKV is pre-processed into the workspace
     int32_t* status_dev = nullptr;
     int last_cuda_error = 0;
     std::atomic<int64_t> launches{0};
@@ -73,6 +75,19 @@ struct dx_attn
 
 namespace
 {
+
+// Accepts both layouts of dx_attn_generation_params (with and without the optional tail).
+bool read_params(const dx_attn_generation_params* in, dx_attn_generation_params& out)
+{
+    if (!in)
+        return false;
+    if (in->struct_size != sizeof(dx_attn_generation_params) && in->struct_size != DX_ATTN_GENERATION_PARAMS_SIZE_V1)
+        return false;
+    memset(&out, 0, sizeof(out));
+    memcpy(&out, in, in->struct_size);
+    out.struct_size = sizeof(dx_attn_generation_params);
+    return true;
+}
 
 // Partitions of one sequence of `total` tokens for a partition bound of `target` tokens.
 inline long parts_of(long total, long target)
@@ -169,6 +184,15 @@ size_t workspace_bound(const dx_attn* h, int batch, int max_past_len)
         return 0;
     const size_t qrows = (size_t) batch * c.num_heads;
     return align_up(qrows * nsplit * c.head_size * sizeof(float), 128) + align_up(qrows * nsplit * sizeof(float2), 128);
+}
+
+// Bytes of the pre-processed QKV copy at the start of the workspace (0 when nothing is configured).
+size_t prep_bytes(const dx_attn* h, int batch)
+{
+    if (!h->prep)
+        return 0;
+    const dx_attn_config& c = h->cfg;
+    return align_up((size_t) batch * (c.num_heads + 2 * c.num_kv_heads) * c.head_size * 2, 128);
 }
 
 int check_cuda(dx_attn* h, cudaError_t e)
@@ -272,9 +296,26 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
     if (!config || !out)
         return DX_ERR_BAD_ARG;
     *out = nullptr;
-    if (config->struct_size != sizeof(dx_attn_config))
+    if (config->struct_size != sizeof(dx_attn_config) && config->struct_size != DX_ATTN_CONFIG_SIZE_V1)
         return DX_ERR_BAD_ARG;
-    const dx_attn_config& c = *config;
+    dx_attn_config full;
+    memset(&full, 0, sizeof(full));
+    memcpy(&full, config, config->struct_size);
+    full.struct_size = sizeof(dx_attn_config);
+    const dx_attn_config& c = full;
+    if (c.position_embedding_type < 0 || c.position_embedding_type > POS_ROPE_GPT_NEOX)
+        return DX_ERR_UNSUPPORTED; // ALiBi / relative position bias are not implemented
+    if (c.position_embedding_type != POS_LEARNED_ABSOLUTE)
+    {
+        if (c.rotary_embedding_dim <= 0 || (c.rotary_embedding_dim & 3) || c.rotary_embedding_dim > c.head_size
+            || !(c.rotary_embedding_base > 0.f) || c.rotary_embedding_scale_type < ROT_SCALE_NONE
+            || c.rotary_embedding_scale_type > ROT_SCALE_DYNAMIC)
+            return DX_ERR_BAD_ARG;
+        if (c.rotary_embedding_scale_type != ROT_SCALE_NONE && !(c.rotary_embedding_scale > 0.f))
+            return DX_ERR_BAD_ARG;
+        if (c.rotary_embedding_scale_type == ROT_SCALE_DYNAMIC && c.rotary_embedding_max_positions <= 0)
+            return DX_ERR_BAD_ARG;
+    }
     if (c.num_heads <= 0 || c.num_kv_heads <= 0 || c.num_heads % c.num_kv_heads != 0)
         return DX_ERR_BAD_ARG;
     if (!(c.q_scaling > 0.f) || c.tokens_per_block <= 0 || (c.tokens_per_block & (c.tokens_per_block - 1)))
@@ -293,6 +334,7 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
     if (!h)
         return DX_ERR_BAD_ARG;
     h->cfg = c;
+    h->prep = c.position_embedding_type != POS_LEARNED_ABSOLUTE || c.qkv_bias_enabled != 0;
     h->cache_kind = q == DX_QUANT_INT8_KV_CACHE ? CACHE_INT8 : (q == DX_QUANT_FP8_KV_CACHE ? CACHE_FP8 : CACHE_T);
     h->group = c.num_heads / c.num_kv_heads;
     while ((1 << h->tpb_log2) < c.tokens_per_block)
@@ -358,9 +400,9 @@ void dx_attn_destroy(dx_attn_t* h)
 
 size_t dx_attn_workspace_size(const dx_attn_t* h, int32_t batch, int32_t max_past_len)
 {
-    if (!h || batch <= 0 || max_past_len < 0 || !h->cfg.multi_block_mode)
+    if (!h || batch <= 0 || max_past_len < 0)
         return 0;
-    return workspace_bound(h, batch, max_past_len);
+    return prep_bytes(h, batch) + workspace_bound(h, batch, max_past_len);
 }
 
 int dx_attn_plan(const dx_attn_t* h, int32_t batch, int32_t max_past_len, int32_t* num_partitions,
@@ -380,14 +422,16 @@ int dx_attn_plan(const dx_attn_t* h, int32_t batch, int32_t max_past_len, int32_
 
 int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* params, void* cuda_stream)
 {
-    if (!h || !params || params->struct_size != sizeof(dx_attn_generation_params))
+    dx_attn_generation_params p;
+    if (!h || !read_params(params, p))
         return DX_ERR_BAD_ARG;
-    const dx_attn_generation_params& p = *params;
     const dx_attn_config& c = h->cfg;
     if (p.num_requests < 0 || p.max_blocks_per_sequence <= 0)
         return DX_ERR_BAD_ARG;
     if (p.num_requests == 0)
         return DX_OK; // empty batch: nothing to do, nothing launched
+    if (p.qkv_bias && (!c.qkv_bias_enabled || ((uintptr_t) p.qkv_bias & 1)))
+        return DX_ERR_BAD_ARG; // a bias needs qkv_bias_enabled at create time (it sizes the workspace)
     if (!p.attention_input || !p.sequence_lengths || !p.block_pointers || !p.context_buf)
         return DX_ERR_BAD_ARG;
     if (((uintptr_t) p.attention_input | (uintptr_t) p.context_buf) & 15)
@@ -421,24 +465,25 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     const Plan plan = make_plan(h, p.num_requests, max_past, p.host_past_key_value_lengths);
     if (plan.kind == KIND_MHA && c.tokens_per_block < 16)
         return DX_ERR_UNSUPPORTED;
-    if (plan.nsplit > 1)
+    const size_t prep = prep_bytes(h, p.num_requests);
+    if (plan.nsplit > 1 || prep)
     {
         if (!p.workspace || ((uintptr_t) p.workspace & 127))
             return p.workspace ? DX_ERR_BAD_ARG : DX_ERR_WORKSPACE;
-        if (p.workspace_bytes < plan.workspace())
+        if (p.workspace_bytes < prep + plan.workspace())
             return DX_ERR_WORKSPACE;
     }
+    char* const ws_partials = reinterpret_cast<char*>(p.workspace) + prep;
 
     AttnArgs a{};
-    a.qkv = p.attention_input;
+    a.qkv = prep ? p.workspace : p.attention_input;
     a.out = p.context_buf;
     a.seq_len = p.sequence_lengths;
     a.block_ptrs = p.block_pointers;
     a.scale_orig_quant = p.kv_scale_orig_quant;
     a.scale_quant_orig = p.kv_scale_quant_orig;
-    a.part_o = plan.nsplit > 1 ? reinterpret_cast<float*>(p.workspace) : nullptr;
-    a.part_ml = plan.nsplit > 1 ? reinterpret_cast<float2*>(reinterpret_cast<char*>(p.workspace) + plan.part_o_bytes)
-                                : nullptr;
+    a.part_o = plan.nsplit > 1 ? reinterpret_cast<float*>(ws_partials) : nullptr;
+    a.part_ml = plan.nsplit > 1 ? reinterpret_cast<float2*>(ws_partials + plan.part_o_bytes) : nullptr;
     a.status = h->status_dev;
     a.batch = p.num_requests;
     a.num_heads = c.num_heads;
@@ -453,6 +498,34 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     int st = check_cuda(h, cudaSetDevice(c.device));
     if (st != DX_OK)
         return st;
+
+    if (prep)
+    {
+        // bias + rotary embedding of the new token's q / k (bias only for v) into the workspace copy
+        PrepArgs pa{};
+        pa.qkv = p.attention_input;
+        pa.bias = p.qkv_bias;
+        pa.out = p.workspace;
+        pa.seq_len = p.sequence_lengths;
+        pa.batch = p.num_requests;
+        pa.num_heads = c.num_heads;
+        pa.num_kv_heads = c.num_kv_heads;
+        pa.head_size = c.head_size;
+        pa.pos_type = c.position_embedding_type;
+        pa.rot_dim = c.rotary_embedding_dim;
+        pa.rot_scale_type = c.rotary_embedding_scale_type;
+        pa.rot_max_positions = c.rotary_embedding_max_positions;
+        pa.rot_base = c.rotary_embedding_base;
+        pa.rot_scale = c.rotary_embedding_scale;
+        const long pairs = (long) p.num_requests * (c.num_heads + 2 * c.num_kv_heads) * (c.head_size / 2);
+        void* pargs[] = {&pa};
+        const void* fn = c.type_id == DX_DTYPE_FP16 ? reinterpret_cast<const void*>(&qkv_bias_rope_kernel<__half>)
+                                                    : reinterpret_cast<const void*>(&qkv_bias_rope_kernel<__nv_bfloat16>);
+        st = check_cuda(h, cudaLaunchKernel(fn, dim3((unsigned) ((pairs + 255) / 256)), dim3(256), pargs, 0, stream));
+        if (st != DX_OK)
+            return st;
+        h->launches.fetch_add(1);
+    }
 
     if (plan.kind == KIND_GQA)
     {
@@ -501,9 +574,9 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
 int dx_attn_enqueue_generation_host(
     dx_attn_t* h, const dx_attn_generation_params* params, void* cuda_stream, int32_t sync)
 {
-    if (!h || !params || params->struct_size != sizeof(dx_attn_generation_params))
+    dx_attn_generation_params p;
+    if (!h || !read_params(params, p))
         return DX_ERR_BAD_ARG;
-    dx_attn_generation_params p = *params;
     const dx_attn_config& c = h->cfg;
     if (p.num_requests < 0 || p.max_blocks_per_sequence <= 0)
         return DX_ERR_BAD_ARG;
@@ -625,8 +698,10 @@ size_t dx_attn_static_scratch_bytes(void)
 int dx_attn_enqueue_generation_static_scratch(
     dx_attn_t* h, const dx_attn_generation_params* params, void* cuda_stream)
 {
-    if (!h || !params || params->struct_size != sizeof(dx_attn_generation_params))
+    dx_attn_generation_params full;
+    if (!h || !read_params(params, full))
         return DX_ERR_BAD_ARG;
+    params = &full;
     if (params->num_requests <= 0)
         return params->num_requests == 0 ? DX_OK : DX_ERR_BAD_ARG;
     // Size check first, on the host: the partials of this batch must fit the fixed array.
@@ -640,7 +715,7 @@ int dx_attn_enqueue_generation_static_scratch(
     if (max_past < 0)
         return DX_ERR_BAD_ARG;
     const Plan plan = make_plan(h, params->num_requests, max_past, params->host_past_key_value_lengths);
-    if (plan.workspace() > (size_t) DX_STATIC_SCRATCH_BYTES)
+    if (prep_bytes(h, params->num_requests) + plan.workspace() > (size_t) DX_STATIC_SCRATCH_BYTES)
         return DX_ERR_WORKSPACE;
     int st = check_cuda(h, cudaSetDevice(h->cfg.device));
     if (st != DX_OK)

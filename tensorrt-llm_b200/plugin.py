@@ -23,6 +23,20 @@ DX_DTYPE_FP16, DX_DTYPE_BF16 = 0, 1
 _LIB: Optional[ctypes.CDLL] = None
 
 
+class PositionEmbeddingType:
+    """Values of tensorrt_llm::kernels::PositionEmbeddingType (cpp/tensorrt_llm/kernels/gptKernels.h:41-51)."""
+    learned_absolute = 0
+    rope_gptj = 1
+    rope_gpt_neox = 2
+
+
+class RotaryScalingType:
+    """Values of tensorrt_llm::kernels::RotaryScalingType (cpp/tensorrt_llm/kernels/gptKernels.h:53-58)."""
+    none = 0
+    linear = 1
+    dynamic = 2
+
+
 class QuantMode:
     """Bit values of tensorrt_llm.quantization.mode.QuantMode that concern the KV cache
     (tensorrt_llm/quantization/mode.py:47-49)."""
@@ -43,7 +57,11 @@ class _Config(ctypes.Structure):
                 ("tp_size", ctypes.c_int32), ("tp_rank", ctypes.c_int32), ("multi_block_mode", ctypes.c_int32),
                 ("enable_xqa", ctypes.c_int32), ("kv_cache_quant_mode", ctypes.c_int32),
                 ("paged_kv_cache", ctypes.c_int32), ("tokens_per_block", ctypes.c_int32),
-                ("type_id", ctypes.c_int32), ("device", ctypes.c_int32)]
+                ("type_id", ctypes.c_int32), ("device", ctypes.c_int32),
+                ("position_embedding_type", ctypes.c_int32), ("rotary_embedding_dim", ctypes.c_int32),
+                ("rotary_embedding_base", ctypes.c_float), ("rotary_embedding_scale_type", ctypes.c_int32),
+                ("rotary_embedding_scale", ctypes.c_float), ("rotary_embedding_max_positions", ctypes.c_int32),
+                ("qkv_bias_enabled", ctypes.c_int32)]
 
 
 class _GenParams(ctypes.Structure):
@@ -56,7 +74,7 @@ class _GenParams(ctypes.Structure):
                 ("host_block_pointers", ctypes.c_void_p), ("kv_scale_orig_quant", ctypes.c_void_p),
                 ("kv_scale_quant_orig", ctypes.c_void_p), ("context_buf", ctypes.c_void_p),
                 ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
-                ("cache_indir", ctypes.c_void_p)]
+                ("cache_indir", ctypes.c_void_p), ("qkv_bias", ctypes.c_void_p)]
 
 
 EXPORTED_SYMBOLS = [
@@ -135,7 +153,11 @@ class GPTAttentionPlugin:
     def __init__(self, *, num_heads: int, num_kv_heads: int, head_size: int, q_scaling: float = 1.0,
                  tp_size: int = 1, tp_rank: int = 0, multi_block_mode: bool = False, enable_xqa: bool = True,
                  kv_cache_quant_mode: int = QuantMode.NONE, paged_kv_cache: bool = True, tokens_per_block: int = 64,
-                 type_id: torch.dtype = torch.float16, layer_idx: int = 0, device: int = 0):
+                 type_id: torch.dtype = torch.float16, layer_idx: int = 0, device: int = 0,
+                 position_embedding_type: int = PositionEmbeddingType.learned_absolute,
+                 rotary_embedding_dim: int = 0, rotary_embedding_base: float = 10000.0,
+                 rotary_embedding_scale_type: int = RotaryScalingType.none, rotary_embedding_scale: float = 1.0,
+                 rotary_embedding_max_positions: int = 1024, qkv_bias: bool = False):
         if type_id not in (torch.float16, torch.bfloat16):
             raise DecodeAttnError(DX_ERR_UNSUPPORTED, "type_id")
         self.lib = load_library()
@@ -146,7 +168,10 @@ class GPTAttentionPlugin:
         self.device = device
         cfg = _Config(ctypes.sizeof(_Config), layer_idx, num_heads, num_kv_heads, head_size, q_scaling, tp_size,
                       tp_rank, int(multi_block_mode), int(enable_xqa), kv_cache_quant_mode, int(paged_kv_cache),
-                      tokens_per_block, DX_DTYPE_FP16 if type_id == torch.float16 else DX_DTYPE_BF16, device)
+                      tokens_per_block, DX_DTYPE_FP16 if type_id == torch.float16 else DX_DTYPE_BF16, device,
+                      position_embedding_type, rotary_embedding_dim, rotary_embedding_base,
+                      rotary_embedding_scale_type, rotary_embedding_scale, rotary_embedding_max_positions,
+                      int(qkv_bias))
         handle = ctypes.c_void_p()
         st = self.lib.dx_attn_create(ctypes.byref(cfg), ctypes.byref(handle))
         if st != DX_OK:
@@ -192,7 +217,8 @@ class GPTAttentionPlugin:
 
     def _params(self, qkv, sequence_length, host_past_key_value_lengths, kv_cache_block_pointers,
                 kv_orig_quant_scale, kv_quant_orig_scale, out, workspace, max_attention_window,
-                host_kv_cache_block_pointers=None, cache_indirection=None, beam_width=1, sink_token_length=0):
+                host_kv_cache_block_pointers=None, cache_indirection=None, beam_width=1, sink_token_length=0,
+                qkv_bias=None):
         B = qkv.shape[0]
         M = kv_cache_block_pointers.shape[-1]
         hp = host_past_key_value_lengths
@@ -218,6 +244,7 @@ class GPTAttentionPlugin:
         p.workspace = _ptr(workspace)
         p.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
         p.cache_indir = _ptr(cache_indirection)
+        p.qkv_bias = _ptr(qkv_bias)
         return p, max_past
 
     def _ensure_workspace(self, batch: int, max_past: int, device) -> Optional[torch.Tensor]:
@@ -236,7 +263,8 @@ class GPTAttentionPlugin:
                            workspace: Optional[torch.Tensor] = None, max_attention_window: Optional[int] = None,
                            host_kv_cache_block_pointers: Optional[torch.Tensor] = None,
                            cache_indirection: Optional[torch.Tensor] = None, beam_width: int = 1,
-                           sink_token_length: int = 0, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+                           sink_token_length: int = 0, qkv_bias: Optional[torch.Tensor] = None,
+                           stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
         """qkv: T [B, (H+2Hkv)*Dh] (device); sequence_length: int32 [B] (device, includes the new token);
         host_past_key_value_lengths: int32 [B] (host); kv_cache_block_pointers: int64 [B, 2, M] (device).
         Appends the new token to the cache and returns the attention output T [B, H*Dh].  Asynchronous."""
@@ -253,7 +281,7 @@ class GPTAttentionPlugin:
             workspace = self._ensure_workspace(B, max_past, qkv.device)
         p, _ = self._params(qkv, sequence_length, hp, kv_cache_block_pointers, kv_orig_quant_scale,
                             kv_quant_orig_scale, out, workspace, max_attention_window,
-                            host_kv_cache_block_pointers, cache_indirection, beam_width, sink_token_length)
+                            host_kv_cache_block_pointers, cache_indirection, beam_width, sink_token_length, qkv_bias)
         s = stream if stream is not None else torch.cuda.current_stream(qkv.device)
         st = self.lib.dx_attn_enqueue_generation(self._h, ctypes.byref(p), ctypes.c_void_p(s.cuda_stream))
         if st != DX_OK:

@@ -17,8 +17,9 @@ REF_MAX_ABS_TOL, REF_MEAN_ABS_TOL = 0.5, 0.05
 LIB = Path(__file__).resolve().parent.parent / "oracle" / "_ref" / "libref_mmha.so"
 
 
-def _run_reference(w, tiles=0, sync=True, out=None, ws=None):
+def _run_reference(w, tiles=0, sync=True, out=None, ws=None, qkv_bias=None, rope=None):
     cfg = w.cfg
+    rope = rope or {}
     lib = ctypes.CDLL(str(LIB))
     fn = lib.ref_mmha_bf16_128 if (cfg.dtype == torch.bfloat16 and cfg.head_size == 128) else lib.ref_mmha_fp16_64
     fn.restype = ctypes.c_int
@@ -35,7 +36,10 @@ def _run_reference(w, tiles=0, sync=True, out=None, ws=None):
             ctypes.c_float(1.0), P(w.kv_orig_quant_scale.data_ptr() if w.kv_orig_quant_scale is not None else 0),
             P(w.kv_quant_orig_scale.data_ptr() if w.kv_quant_orig_scale is not None else 0),
             int(cfg.cache == "int8"), int(cfg.cache == "fp8"), tiles, P(ws.data_ptr()), sm,
-            P(torch.cuda.current_stream().cuda_stream))
+            P(torch.cuda.current_stream().cuda_stream), P(qkv_bias.data_ptr() if qkv_bias is not None else 0),
+            int(rope.get("position_embedding_type", 0)), int(rope.get("rotary_embedding_dim", 0)),
+            ctypes.c_float(rope.get("rotary_embedding_base", 10000.0)), int(rope.get("rotary_embedding_scale_type", 0)),
+            ctypes.c_float(rope.get("rotary_embedding_scale", 1.0)), int(rope.get("rotary_embedding_max_positions", 1024)))
     assert st == 0, f"reference launcher returned {st}"
     if sync:
         torch.cuda.synchronize()
