@@ -31,7 +31,7 @@ template <typename T>
 struct EnqueueGenerationParams
 {
     T const* attention_input = nullptr;
-    T const* qkv_bias = nullptr; // must be nullptr: bias is applied by the caller
+    T const* qkv_bias = nullptr; // needs setQkvBiasEnabled(true) before initialize()
     int32_t input_seq_length = 1;
     int32_t const* sequence_lengths = nullptr;
     int32_t past_kv_length = 0;
@@ -78,6 +78,24 @@ public:
         mConfig.device = device;
     }
 
+    // Rotary position embedding / bias applied inside the step (call before initialize()); values are the
+    // reference's PositionEmbeddingType / RotaryScalingType (cpp/tensorrt_llm/kernels/gptKernels.h:41-58).
+    void setPositionEmbedding(int position_embedding_type, int rotary_embedding_dim, float rotary_embedding_base,
+        int rotary_embedding_scale_type, float rotary_embedding_scale, int rotary_embedding_max_positions)
+    {
+        mConfig.position_embedding_type = position_embedding_type;
+        mConfig.rotary_embedding_dim = rotary_embedding_dim;
+        mConfig.rotary_embedding_base = rotary_embedding_base;
+        mConfig.rotary_embedding_scale_type = rotary_embedding_scale_type;
+        mConfig.rotary_embedding_scale = rotary_embedding_scale;
+        mConfig.rotary_embedding_max_positions = rotary_embedding_max_positions;
+    }
+
+    void setQkvBiasEnabled(bool enabled)
+    {
+        mConfig.qkv_bias_enabled = enabled;
+    }
+
     GPTAttentionCommon(GPTAttentionCommon const&) = delete;
     GPTAttentionCommon& operator=(GPTAttentionCommon const&) = delete;
 
@@ -113,7 +131,7 @@ public:
     {
         if (!mHandle)
             return DX_ERR_BAD_ARG;
-        if (params.qkv_bias || params.alibi_slopes || params.key_value_cache || params.input_seq_length != 1)
+        if (params.alibi_slopes || params.key_value_cache || params.input_seq_length != 1)
             return DX_ERR_UNSUPPORTED;
         dx_attn_generation_params p{};
         p.struct_size = sizeof(p);
@@ -134,6 +152,7 @@ public:
         p.workspace = params.workspace;
         p.workspace_bytes = params.workspace_bytes;
         p.cache_indir = params.cache_indir;
+        p.qkv_bias = params.qkv_bias;
         return dx_attn_enqueue_generation(mHandle, &p, stream);
     }
 
