@@ -86,7 +86,8 @@ EXPORTED_SYMBOLS = [
 
 
 def library_path() -> Path:
-    return Path(__file__).resolve().parent / "libdecode_attn.so"
+    override = os.environ.get("DX_DECODE_ATTN_LIB")  # alternative build of the same library (tuning)
+    return Path(override) if override else Path(__file__).resolve().parent / "libdecode_attn.so"
 
 
 def load_library() -> ctypes.CDLL:
