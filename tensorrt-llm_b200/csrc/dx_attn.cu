@@ -26,7 +26,8 @@ namespace
 enum KernelKind : int
 {
     KIND_MHA = 0, // CUDA-core kernel, one CTA per q head
-    KIND_GQA = 1  // tensor-core kernel, one CTA per kv head (x 16-head slice)
+    KIND_GQA = 1, // tensor-core kernel, one CTA per kv head (x 16-head slice)
+    KIND_WIDE = 2 // tcgen05 kernel, one CTA per kv head (x 128-head slice), FP8 cache, more than 16 heads per kv head
 };
 
 struct Plan
@@ -62,7 +63,8 @@ struct dx_attn
     int waves = 8;               // bound on the partitions a call may need: waves * SMs * 3 CTAs (workspace sizing)
     int min_chunk = 256;         // smallest partition bound, tokens
     int fixed_cost_tokens = 400; // per-CTA fixed cost (prologue, pipeline fill, epilogue) in tokens of streaming time
-    KernelInfo k_mha{}, k_gqa[2]{}, k_merge{}, k_append{}; // k_gqa[16 heads per CTA?]
+    KernelInfo k_mha{}, k_gqa[2]{}, k_wide{}, k_merge{}, k_append{}; // k_gqa[16 heads per CTA?]
+    bool wide = false;       // wide-group kernel usable for this configuration
     int force_chunk = 0;     // > 0: partition bound forced (tuning)
     bool prep = false; // bias / rotary embedding configured: QKV is pre-processed into the workspace
     int32_t* status_dev = nullptr;
@@ -107,7 +109,14 @@ Plan make_plan(const dx_attn* h, int batch, int max_past_len, const int32_t* hos
     const bool grouped = h->group > 1 && h->cache_kind != CACHE_T && c.tokens_per_block >= 32;
     p.kind = grouped ? KIND_GQA : KIND_MHA;
     int resident = 2, rows_per_seq = c.num_heads;
-    if (grouped)
+    if (grouped && h->wide)
+    {
+        p.kind = KIND_WIDE;
+        p.hgroups = (h->group + 127) / 128;
+        rows_per_seq = c.num_kv_heads * p.hgroups;
+        resident = c.head_size == 64 ? 3 : 2;
+    }
+    else if (grouped)
     {
         p.hgroups = (h->group + 15) / 16;
         p.heads16 = h->group > 8;
@@ -371,6 +380,15 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
         st = set_smem(h, h->k_mha);
     for (int i = 0; i < 2 && st == DX_OK; ++i)
         st = set_smem(h, h->k_gqa[i]);
+    if (st == DX_OK && h->cache_kind == CACHE_FP8 && h->group > 16 && c.tokens_per_block >= 64)
+    {
+        const char* w = getenv("DX_ATTN_WIDE"); // "0": keep such groups on the 16-head-slice kernel
+        if (!w || atoi(w) != 0)
+        {
+            h->k_wide = wide_kernel_info(c.type_id, c.head_size);
+            h->wide = h->k_wide.fn != nullptr && set_smem(h, h->k_wide) == DX_OK;
+        }
+    }
     if (st == DX_OK)
         st = check_cuda(h, cudaMalloc(reinterpret_cast<void**>(&h->status_dev), 256));
     if (st == DX_OK)
@@ -527,7 +545,14 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
         h->launches.fetch_add(1);
     }
 
-    if (plan.kind == KIND_GQA)
+    if (plan.kind == KIND_WIDE)
+    {
+        int hgroups = plan.hgroups;
+        void* args[] = {&a, &hgroups};
+        dim3 grid(plan.nsplit, c.num_kv_heads * plan.hgroups, p.num_requests);
+        st = check_cuda(h, cudaLaunchKernel(h->k_wide.fn, grid, dim3(128), args, (size_t) h->k_wide.smem, stream));
+    }
+    else if (plan.kind == KIND_GQA)
     {
         const KernelInfo& k = h->k_gqa[plan.heads16 ? 1 : 0];
         if (!k.fn)

@@ -13,6 +13,7 @@ struct KernelInfo
 // dtype: 0 fp16, 1 bf16.  cache: CacheKind.  dh: 64 or 128.
 KernelInfo mha_kernel_info(int dtype, int cache, int dh, int tokens_per_block);
 KernelInfo gqa_kernel_info(int dtype, int cache, int dh, bool heads16);
+KernelInfo wide_kernel_info(int dtype, int dh); // FP8 cache only
 KernelInfo merge_kernel_info(int dtype, int dh);
 KernelInfo append_kernel_info(int dtype, int cache, int dh);
 } // namespace dx
