@@ -27,6 +27,7 @@ enum KernelKind : int
 {
     KIND_MHA = 0, // CUDA-core kernel, one CTA per q head
     KIND_GQA = 1, // tensor-core kernel, one CTA per kv head (x 16-head slice)
+    KIND_TOK = 3, // tcgen05 kernel, token-major, one CTA per kv head, FP8 cache, Dh 128, up to 16 heads per kv head
     KIND_WIDE = 2 // tcgen05 kernel, one CTA per kv head (x 128-head slice), FP8 cache, more than 16 heads per kv head
 };
 
@@ -63,8 +64,9 @@ struct dx_attn
     int waves = 8;               // bound on the partitions a call may need: waves * SMs * 3 CTAs (workspace sizing)
     int min_chunk = 256;         // smallest partition bound, tokens
     int fixed_cost_tokens = 400; // per-CTA fixed cost (prologue, pipeline fill, epilogue) in tokens of streaming time
-    KernelInfo k_mha{}, k_gqa[2]{}, k_wide{}, k_merge{}, k_append{}; // k_gqa[16 heads per CTA?]
+    KernelInfo k_mha{}, k_gqa[2]{}, k_wide{}, k_tok{}, k_merge{}, k_append{}; // k_gqa[16 heads per CTA?]
     bool wide = false;       // wide-group kernel usable for this configuration
+    bool tok = false;        // token-major tcgen05 kernel usable for this configuration
     int force_chunk = 0;     // > 0: partition bound forced (tuning)
     bool prep = false; // bias / rotary embedding configured: QKV is pre-processed into the workspace
     int32_t* status_dev = nullptr;
@@ -115,6 +117,13 @@ Plan make_plan(const dx_attn* h, int batch, int max_past_len, const int32_t* hos
         p.hgroups = (h->group + 127) / 128;
         rows_per_seq = c.num_kv_heads * p.hgroups;
         resident = c.head_size == 64 ? 3 : 2;
+    }
+    else if (grouped && h->tok)
+    {
+        p.kind = KIND_TOK;
+        p.hgroups = 1;
+        rows_per_seq = c.num_kv_heads;
+        resident = h->k_tok.resident;
     }
     else if (grouped)
     {
@@ -389,6 +398,16 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
             h->wide = h->k_wide.fn != nullptr && set_smem(h, h->k_wide) == DX_OK;
         }
     }
+    if (st == DX_OK && h->cache_kind == CACHE_FP8 && h->group > 1 && h->group <= 16 && c.head_size == 128
+        && c.tokens_per_block >= 32)
+    {
+        const char* w = getenv("DX_ATTN_TOK");
+        if (w && atoi(w) != 0)
+        {
+            h->k_tok = tok_kernel_info(c.type_id, c.head_size, h->group);
+            h->tok = h->k_tok.fn != nullptr && set_smem(h, h->k_tok) == DX_OK;
+        }
+    }
     if (st == DX_OK)
         st = check_cuda(h, cudaMalloc(reinterpret_cast<void**>(&h->status_dev), 256));
     if (st == DX_OK)
@@ -551,6 +570,12 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
         void* args[] = {&a, &hgroups};
         dim3 grid(plan.nsplit, c.num_kv_heads * plan.hgroups, p.num_requests);
         st = check_cuda(h, cudaLaunchKernel(h->k_wide.fn, grid, dim3(128), args, (size_t) h->k_wide.smem, stream));
+    }
+    else if (plan.kind == KIND_TOK)
+    {
+        void* args[] = {&a};
+        dim3 grid(plan.nsplit, c.num_kv_heads, p.num_requests);
+        st = check_cuda(h, cudaLaunchKernel(h->k_tok.fn, grid, dim3(128), args, (size_t) h->k_tok.smem, stream));
     }
     else if (plan.kind == KIND_GQA)
     {

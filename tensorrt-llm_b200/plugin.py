@@ -201,7 +201,7 @@ class GPTAttentionPlugin:
         if st != DX_OK:
             raise DecodeAttnError(st, "dx_attn_plan")
         return {"num_partitions": n.value, "tokens_per_partition": c.value,
-                "kernel": {0: "mha_cuda_core", 1: "gqa_tensor_core", 2: "wide_group_tcgen05"}.get(k.value, "?")}
+                "kernel": {0: "mha_cuda_core", 1: "gqa_tensor_core", 2: "wide_group_tcgen05", 3: "token_major_tcgen05"}.get(k.value, "?")}
 
     def launch_count(self) -> int:
         return int(self.lib.dx_attn_launch_count(self._h))
