@@ -79,7 +79,8 @@ typedef struct dx_attn_config
      * (decoderMaskedMultiheadAttentionTemplate.h:1587-1712): bias add, then rotary embedding on q and k.
      * Values of position_embedding_type / rotary_embedding_scale_type are the reference's
      * (cpp/tensorrt_llm/kernels/gptKernels.h:41-58): 0 learned-absolute (nothing to do), 1 RoPE GPT-J,
-     * 2 RoPE GPT-NeoX; scale type 0 none, 1 linear, 2 dynamic.  ALiBi / relative: DX_ERR_UNSUPPORTED. */
+     * 2 RoPE GPT-NeoX, 3 ALiBi, 4 ALiBi with scale (both: slopes per call, dx_attn_generation_params.alibi_slopes);
+ * scale type 0 none, 1 linear, 2 dynamic.  Relative position bias: DX_ERR_UNSUPPORTED. */
     int32_t position_embedding_type;
     int32_t rotary_embedding_dim;
     float rotary_embedding_base;
@@ -110,12 +111,18 @@ typedef struct dx_attn_generation_params
     /* max over the batch of the past length (the plugin computes it from the host array,
      * gptAttentionPlugin.cpp:558-563).  Ignored when host_past_key_value_lengths != NULL. */
     int32_t past_kv_length;
-    int32_t beam_width;                   /* must be 1                                              */
+    int32_t beam_width;                   /* > 1: every per-sequence array has num_requests * beam_width rows
+                                           * (the reference's batch_beam, gptAttentionCommon.cpp:1186);
+                                           * cache_indir and context_lengths must be given          */
     int32_t num_requests;                 /* batch                                                  */
     int32_t max_blocks_per_sequence;      /* M: row length of the pointer table                     */
-    int32_t max_attention_window;         /* cache capacity in tokens; must be >= past length + 1   */
-    int32_t cyclic_attention_window_size; /* must be >= past length + 1 (no wrap implemented)       */
-    int32_t sink_token_length;            /* must be 0                                              */
+    int32_t max_attention_window;         /* cache capacity in tokens (row length of cache_indir)   */
+    int32_t cyclic_attention_window_size; /* sliding window W: a sequence with more than W past tokens attends to
+                                           * the W cache slots (and the new token), which then overwrites the
+                                           * oldest non-sink slot (kvCacheUtils.h:109-117); needs a table without
+                                           * the spare block, (M-1)*tokens_per_block < W                       */
+    int32_t sink_token_length;            /* tokens that are never overwritten; a multiple of tokens_per_block
+                                           * (other values need the reference's position shift: unsupported)   */
     /* device, int64 [num_requests, 2, M]: KVBlockArray::data for this layer - K row then V row of
      * device pointers per sequence (cpp/tensorrt_llm/kernels/kvCacheUtils.h:36-153). */
     const int64_t* block_pointers;
@@ -127,12 +134,22 @@ typedef struct dx_attn_generation_params
     void* context_buf;                /* device, T [num_requests, num_heads * head_size]: output   */
     void* workspace;                  /* device, >= dx_attn_workspace_size(); 128-byte aligned      */
     size_t workspace_bytes;
-    const int32_t* cache_indir; /* must be NULL (beam search not implemented)                      */
-    /* optional tail: device, T [(num_heads + 2*num_kv_heads) * head_size] or NULL (plugin input qkv_bias) */
+    /* device, int32 [num_requests * beam_width, max_attention_window] or NULL: for beam search, the beam whose cache holds
+     * slot t of this sequence (decoderMaskedMultiheadAttentionTemplate.h:2063-2078) */
+    const int32_t* cache_indir;
+    /* optional tail 1: device, T [(num_heads + 2*num_kv_heads) * head_size] or NULL (plugin input qkv_bias) */
     const void* qkv_bias;
+    /* optional tail 2 */
+    /* device, int32 [num_requests * beam_width]: prompt length of every sequence; with beams, slots below it are read
+     * from beam 0 of the request (decoderMaskedMultiheadAttentionTemplate.h:1497-1498) */
+    const int32_t* context_lengths;
+    /* device, T [num_heads] or NULL: ALiBi slopes of this rank's heads; score += slope * (slot - past length)
+     * (decoderMaskedMultiheadAttentionTemplate.h:1890-1895, :2026).  Needs position_embedding_type 3 or 4. */
+    const void* alibi_slopes;
 } dx_attn_generation_params;
-/* size of dx_attn_generation_params without the optional tail (accepted by the enqueue calls) */
-#define DX_ATTN_GENERATION_PARAMS_SIZE_V1 (sizeof(dx_attn_generation_params) - sizeof(void*))
+/* sizes of dx_attn_generation_params without the optional tails (all three are accepted by the enqueue calls) */
+#define DX_ATTN_GENERATION_PARAMS_SIZE_V1 (sizeof(dx_attn_generation_params) - 3 * sizeof(void*))
+#define DX_ATTN_GENERATION_PARAMS_SIZE_V2 (sizeof(dx_attn_generation_params) - 2 * sizeof(void*))
 
 typedef struct dx_attn dx_attn_t;
 

@@ -52,18 +52,30 @@ using namespace tensorrt_llm::kernels;
  * workspace layout (caller allocates, 128-byte aligned sub-buffers, same order as the plugin):
  *   partial_out [tiles,B,H,Dh] T | partial_sum [B*H*tiles] f32 | partial_max [B*H*tiles] f32 | block_counter [B*H] i32
  * tiles == 0 disables multi-block mode. */
-extern "C" int REF_CAT(REF_FN(ref_mmha), REF_DH)(const void* qkv, void* out, const int32_t* sequence_length_dev,
+struct RefExtras
+{
+    int32_t beam_width = 1;
+    const int32_t* cache_indir = nullptr;   // [batch, max_attention_window]
+    const int32_t* input_lengths = nullptr; // [batch]
+    int32_t cyclic_attention_window_size = 0; // 0: same as max_attention_window
+    int32_t sink_token_length = 0;
+    const void* linear_bias_slopes = nullptr; // T [num_heads]
+};
+
+static int ref_mmha_impl(const void* qkv, void* out, const int32_t* sequence_length_dev,
     int64_t* block_pointers_dev, int32_t batch, int32_t num_heads, int32_t num_kv_heads, int32_t max_blocks_per_seq,
     int32_t tokens_per_block, int32_t max_attention_window, int32_t past_kv_length, float q_scaling,
     const float* kv_scale_orig_quant_dev, const float* kv_scale_quant_orig_dev, int32_t int8_kv, int32_t fp8_kv,
     int32_t tiles, void* workspace, int32_t sm_count, cudaStream_t stream, const void* qkv_bias,
     int32_t position_embedding_type, int32_t rotary_embedding_dim, float rotary_embedding_base,
-    int32_t rotary_embedding_scale_type, float rotary_embedding_scale, int32_t rotary_embedding_max_positions)
+    int32_t rotary_embedding_scale_type, float rotary_embedding_scale, int32_t rotary_embedding_max_positions,
+    const RefExtras& x)
 {
     const int Dh = REF_DH;
     const size_t elem = (int8_kv || fp8_kv) ? 1 : sizeof(RefT);
-    KVBlockArray kv(batch, max_blocks_per_seq, tokens_per_block, (int32_t) (num_kv_heads * Dh * elem),
-        max_attention_window, /*sink*/ 0, false);
+    const int32_t cyclic = x.cyclic_attention_window_size > 0 ? x.cyclic_attention_window_size : max_attention_window;
+    KVBlockArray kv(batch, max_blocks_per_seq, tokens_per_block, (int32_t) (num_kv_heads * Dh * elem), cyclic,
+        x.sink_token_length, false);
     kv.data = block_pointers_dev;
     KVLinearBuffer shift_k;
 
@@ -83,10 +95,13 @@ extern "C" int REF_CAT(REF_FN(ref_mmha), REF_DH)(const void* qkv, void* out, con
     }
     p.stride = hq + 2 * hkv;
     p.batch_size = batch;
-    p.beam_width = 1;
+    p.beam_width = x.beam_width;
+    p.cache_indir = x.beam_width > 1 ? x.cache_indir : nullptr;
+    p.input_lengths = x.input_lengths;
+    p.linear_bias_slopes = reinterpret_cast<const RefT*>(x.linear_bias_slopes);
     p.max_attention_window_size = max_attention_window;
-    p.cyclic_attention_window_size = max_attention_window;
-    p.sink_token_length = 0;
+    p.cyclic_attention_window_size = cyclic;
+    p.sink_token_length = x.sink_token_length;
     p.length_per_sample = sequence_length_dev;
     p.timestep = past_kv_length;
     p.num_heads = num_heads;
@@ -135,4 +150,43 @@ extern "C" int REF_CAT(REF_FN(ref_mmha), REF_DH)(const void* qkv, void* out, con
         return -1;
     }
     return (int) cudaGetLastError();
+}
+
+extern "C" int REF_CAT(REF_FN(ref_mmha), REF_DH)(const void* qkv, void* out, const int32_t* sequence_length_dev,
+    int64_t* block_pointers_dev, int32_t batch, int32_t num_heads, int32_t num_kv_heads, int32_t max_blocks_per_seq,
+    int32_t tokens_per_block, int32_t max_attention_window, int32_t past_kv_length, float q_scaling,
+    const float* kv_scale_orig_quant_dev, const float* kv_scale_quant_orig_dev, int32_t int8_kv, int32_t fp8_kv,
+    int32_t tiles, void* workspace, int32_t sm_count, cudaStream_t stream, const void* qkv_bias,
+    int32_t position_embedding_type, int32_t rotary_embedding_dim, float rotary_embedding_base,
+    int32_t rotary_embedding_scale_type, float rotary_embedding_scale, int32_t rotary_embedding_max_positions)
+{
+    return ref_mmha_impl(qkv, out, sequence_length_dev, block_pointers_dev, batch, num_heads, num_kv_heads,
+        max_blocks_per_seq, tokens_per_block, max_attention_window, past_kv_length, q_scaling, kv_scale_orig_quant_dev,
+        kv_scale_quant_orig_dev, int8_kv, fp8_kv, tiles, workspace, sm_count, stream, qkv_bias, position_embedding_type,
+        rotary_embedding_dim, rotary_embedding_base, rotary_embedding_scale_type, rotary_embedding_scale,
+        rotary_embedding_max_positions, RefExtras{});
+}
+
+/* Same call with the remaining enqueueGeneration features: beam search (batch counts beams; cache_indir
+ * [batch, max_attention_window], input_lengths [batch]), cyclic window, sink tokens, ALiBi slopes (T [num_heads]).
+ * Single-block mode only; position shift off. */
+extern "C" int REF_CAT(REF_FN(ref_mmha_ext), REF_DH)(const void* qkv, void* out, const int32_t* sequence_length_dev,
+    int64_t* block_pointers_dev, int32_t batch, int32_t num_heads, int32_t num_kv_heads, int32_t max_blocks_per_seq,
+    int32_t tokens_per_block, int32_t max_attention_window, int32_t past_kv_length, float q_scaling,
+    const float* kv_scale_orig_quant_dev, const float* kv_scale_quant_orig_dev, int32_t int8_kv, int32_t fp8_kv,
+    int32_t sm_count, cudaStream_t stream, int32_t beam_width, const int32_t* cache_indir,
+    const int32_t* input_lengths, int32_t cyclic_attention_window_size, int32_t sink_token_length,
+    const void* linear_bias_slopes)
+{
+    RefExtras x;
+    x.beam_width = beam_width;
+    x.cache_indir = cache_indir;
+    x.input_lengths = input_lengths;
+    x.cyclic_attention_window_size = cyclic_attention_window_size;
+    x.sink_token_length = sink_token_length;
+    x.linear_bias_slopes = linear_bias_slopes;
+    return ref_mmha_impl(qkv, out, sequence_length_dev, block_pointers_dev, batch, num_heads, num_kv_heads,
+        max_blocks_per_seq, tokens_per_block, max_attention_window, past_kv_length, q_scaling, kv_scale_orig_quant_dev,
+        kv_scale_quant_orig_dev, int8_kv, fp8_kv, 0, nullptr, sm_count, stream, nullptr,
+        linear_bias_slopes ? 3 : 0, 0, 10000.f, 0, 1.f, 0, x);
 }

@@ -67,6 +67,7 @@ struct dx_attn
     KernelInfo k_mha{}, k_gqa[2]{}, k_wide{}, k_tok{}, k_merge{}, k_append{}; // k_gqa[16 heads per CTA?]
     bool wide = false;       // wide-group kernel usable for this configuration
     bool tok = false;        // token-major tcgen05 kernel usable for this configuration
+    GeneralKernels k_general{}; // beams / cyclic window / sinks / ALiBi
     int force_chunk = 0;     // > 0: partition bound forced (tuning)
     bool prep = false; // bias / rotary embedding configured: QKV is pre-processed into the workspace
     int32_t* status_dev = nullptr;
@@ -85,7 +86,8 @@ bool read_params(const dx_attn_generation_params* in, dx_attn_generation_params&
 {
     if (!in)
         return false;
-    if (in->struct_size != sizeof(dx_attn_generation_params) && in->struct_size != DX_ATTN_GENERATION_PARAMS_SIZE_V1)
+    if (in->struct_size != sizeof(dx_attn_generation_params) && in->struct_size != DX_ATTN_GENERATION_PARAMS_SIZE_V1
+        && in->struct_size != DX_ATTN_GENERATION_PARAMS_SIZE_V2)
         return false;
     memset(&out, 0, sizeof(out));
     memcpy(&out, in, in->struct_size);
@@ -287,6 +289,117 @@ int static_scratch_address(dx_attn* h, int device, void** out)
 }
 } // namespace
 
+namespace
+{
+
+// Launches the optional bias / rotary pre-processing of the new token into the start of the workspace.
+int launch_prep(dx_attn* h, const dx_attn_generation_params& p, int nseq, cudaStream_t stream)
+{
+    const dx_attn_config& c = h->cfg;
+    PrepArgs pa{};
+    pa.qkv = p.attention_input;
+    pa.bias = p.qkv_bias;
+    pa.out = p.workspace;
+    pa.seq_len = p.sequence_lengths;
+    pa.batch = nseq;
+    pa.num_heads = c.num_heads;
+    pa.num_kv_heads = c.num_kv_heads;
+    pa.head_size = c.head_size;
+    pa.pos_type = c.position_embedding_type <= POS_ROPE_GPT_NEOX ? c.position_embedding_type : POS_LEARNED_ABSOLUTE;
+    pa.rot_dim = c.rotary_embedding_dim;
+    pa.rot_scale_type = c.rotary_embedding_scale_type;
+    pa.rot_max_positions = c.rotary_embedding_max_positions;
+    pa.rot_base = c.rotary_embedding_base;
+    pa.rot_scale = c.rotary_embedding_scale;
+    const long pairs = (long) nseq * (c.num_heads + 2 * c.num_kv_heads) * (c.head_size / 2);
+    void* pargs[] = {&pa};
+    const void* fn = c.type_id == DX_DTYPE_FP16 ? reinterpret_cast<const void*>(&qkv_bias_rope_kernel<__half>)
+                                                : reinterpret_cast<const void*>(&qkv_bias_rope_kernel<__nv_bfloat16>);
+    const int st = check_cuda(h, cudaLaunchKernel(fn, dim3((unsigned) ((pairs + 255) / 256)), dim3(256), pargs, 0, stream));
+    if (st == DX_OK)
+        h->launches.fetch_add(1);
+    return st;
+}
+
+// Beam search / cyclic window / sink tokens / ALiBi: one CTA per (sequence, q head) reads the cache as it is,
+// then a second kernel appends the new token at its (cyclic) slot.
+int enqueue_general(dx_attn* h, const dx_attn_generation_params& p, int max_past, void* cuda_stream)
+{
+    const dx_attn_config& c = h->cfg;
+    const int tpb = c.tokens_per_block;
+    const int W = p.cyclic_attention_window_size, sink = p.sink_token_length;
+    const int nseq = p.num_requests * p.beam_width; // the reference's batch_beam (gptAttentionCommon.cpp:1186)
+    if (!h->k_general.attn)
+        return DX_ERR_UNSUPPORTED;
+    if (p.max_attention_window < W || sink >= W)
+        return DX_ERR_BAD_ARG;
+    if (sink % tpb != 0)
+        return DX_ERR_UNSUPPORTED; // a partly filled sink block needs the reference's position shift
+    // KVBlockArray (kvCacheUtils.h:74-90): a table with a spare block keeps W + tokens_per_block slots cycling
+    const bool one_more_block = (int64_t) (p.max_blocks_per_sequence - 1) * tpb >= W;
+    const int cyclic_len = one_more_block ? W + tpb - sink : W - sink;
+    if (max_past > W && one_more_block)
+        return DX_ERR_UNSUPPORTED; // the walked slots 0..W-1 are the live window only without the spare block
+    const int64_t slots_used = std::min<int64_t>((int64_t) max_past + 1, (int64_t) sink + cyclic_len);
+    if (slots_used > (int64_t) p.max_blocks_per_sequence * tpb)
+        return DX_ERR_BAD_ARG; // the table cannot hold that many tokens
+    if (p.beam_width > 1)
+    {
+        if (!p.cache_indir || !p.context_lengths)
+            return DX_ERR_BAD_ARG;
+        if (((uintptr_t) p.cache_indir | (uintptr_t) p.context_lengths) & 3)
+            return DX_ERR_BAD_ARG;
+    }
+    const size_t prep = prep_bytes(h, nseq);
+    if (prep)
+    {
+        if (!p.workspace || ((uintptr_t) p.workspace & 127))
+            return p.workspace ? DX_ERR_BAD_ARG : DX_ERR_WORKSPACE;
+        if (p.workspace_bytes < prep)
+            return DX_ERR_WORKSPACE;
+    }
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+    int st = check_cuda(h, cudaSetDevice(c.device));
+    if (st == DX_OK && prep)
+        st = launch_prep(h, p, nseq, stream);
+    if (st != DX_OK)
+        return st;
+
+    GeneralArgs g{};
+    g.qkv = prep ? p.workspace : p.attention_input;
+    g.out = p.context_buf;
+    g.seq_len = p.sequence_lengths;
+    g.block_ptrs = p.block_pointers;
+    g.scale_orig_quant = p.kv_scale_orig_quant;
+    g.scale_quant_orig = p.kv_scale_quant_orig;
+    g.cache_indir = p.beam_width > 1 ? p.cache_indir : nullptr;
+    g.context_lengths = p.context_lengths;
+    g.alibi_slopes = c.position_embedding_type >= POS_ALIBI ? p.alibi_slopes : nullptr;
+    g.num_heads = c.num_heads;
+    g.num_kv_heads = c.num_kv_heads;
+    g.max_blocks_per_seq = p.max_blocks_per_sequence;
+    g.tpb_log2 = h->tpb_log2;
+    g.beam_width = p.beam_width;
+    g.max_attention_window = p.max_attention_window;
+    g.cyclic_window = W;
+    g.cyclic_len = cyclic_len;
+    g.sink = sink;
+    g.softmax_scale_log2 = 1.4426950408889634f / (sqrtf((float) c.head_size) * c.q_scaling);
+    void* args[] = {&g};
+    st = check_cuda(h, cudaLaunchKernel(h->k_general.attn, dim3(c.num_heads, nseq), dim3(128), args,
+                           (size_t) h->k_general.smem, stream));
+    if (st != DX_OK)
+        return st;
+    h->launches.fetch_add(1);
+    st = check_cuda(h, cudaLaunchKernel(h->k_general.append, dim3(c.num_kv_heads, nseq), dim3(32), args, 0, stream));
+    if (st != DX_OK)
+        return st;
+    h->launches.fetch_add(1);
+    return DX_OK;
+}
+
+} // namespace
+
 extern "C" {
 
 int dx_abi_version(void)
@@ -321,9 +434,9 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
     memcpy(&full, config, config->struct_size);
     full.struct_size = sizeof(dx_attn_config);
     const dx_attn_config& c = full;
-    if (c.position_embedding_type < 0 || c.position_embedding_type > POS_ROPE_GPT_NEOX)
-        return DX_ERR_UNSUPPORTED; // ALiBi / relative position bias are not implemented
-    if (c.position_embedding_type != POS_LEARNED_ABSOLUTE)
+    if (c.position_embedding_type < 0 || c.position_embedding_type > POS_ALIBI_WITH_SCALE)
+        return DX_ERR_UNSUPPORTED; // relative position bias is not implemented
+    if (c.position_embedding_type == POS_ROPE_GPTJ || c.position_embedding_type == POS_ROPE_GPT_NEOX)
     {
         if (c.rotary_embedding_dim <= 0 || (c.rotary_embedding_dim & 3) || c.rotary_embedding_dim > c.head_size
             || !(c.rotary_embedding_base > 0.f) || c.rotary_embedding_scale_type < ROT_SCALE_NONE
@@ -352,7 +465,8 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
     if (!h)
         return DX_ERR_BAD_ARG;
     h->cfg = c;
-    h->prep = c.position_embedding_type != POS_LEARNED_ABSOLUTE || c.qkv_bias_enabled != 0;
+    h->prep = c.position_embedding_type == POS_ROPE_GPTJ || c.position_embedding_type == POS_ROPE_GPT_NEOX
+        || c.qkv_bias_enabled != 0;
     h->cache_kind = q == DX_QUANT_INT8_KV_CACHE ? CACHE_INT8 : (q == DX_QUANT_FP8_KV_CACHE ? CACHE_FP8 : CACHE_T);
     h->group = c.num_heads / c.num_kv_heads;
     while ((1 << h->tpb_log2) < c.tokens_per_block)
@@ -377,6 +491,7 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
         h->k_mha = mha_kernel_info(c.type_id, h->cache_kind, c.head_size, c.tokens_per_block);
         h->k_merge = merge_kernel_info(c.type_id, c.head_size);
         h->k_append = append_kernel_info(c.type_id, h->cache_kind, c.head_size);
+        h->k_general = general_kernel_info(c.type_id, h->cache_kind, c.head_size);
         if (h->cache_kind != CACHE_T)
         {
             for (int h16 = 0; h16 < 2; ++h16)
@@ -477,14 +592,17 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
         return DX_ERR_BAD_ARG;
     if (h->cache_kind != CACHE_T && (!p.kv_scale_orig_quant || !p.kv_scale_quant_orig))
         return DX_ERR_BAD_ARG;
-    if (p.beam_width != 1 || p.cache_indir != nullptr || p.sink_token_length != 0)
-        return DX_ERR_UNSUPPORTED;
+    if (p.beam_width < 1 || p.sink_token_length < 0 || p.cyclic_attention_window_size < 1)
+        return DX_ERR_BAD_ARG;
+    const bool alibi = c.position_embedding_type >= POS_ALIBI && p.alibi_slopes != nullptr;
+    if (p.alibi_slopes != nullptr && c.position_embedding_type < POS_ALIBI)
+        return DX_ERR_BAD_ARG; // slopes need an ALiBi position embedding type at create time
 
     int max_past = p.past_kv_length;
     if (p.host_past_key_value_lengths)
     {
         max_past = 0;
-        for (int i = 0; i < p.num_requests; ++i)
+        for (int i = 0; i < p.num_requests * p.beam_width; ++i) // one entry per sequence (request x beam)
         {
             const int v = p.host_past_key_value_lengths[i];
             if (v < 0)
@@ -494,10 +612,13 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     }
     if (max_past < 0)
         return DX_ERR_BAD_ARG;
+    // Beam search, a window shorter than some sequence, sink tokens and ALiBi go to the feature-complete kernel.
+    const bool general = p.beam_width > 1 || p.sink_token_length > 0 || alibi
+        || p.cyclic_attention_window_size < max_past + 1 || p.max_attention_window < max_past + 1;
+    if (general)
+        return enqueue_general(h, p, max_past, cuda_stream);
     if ((int64_t) max_past + 1 > (int64_t) p.max_blocks_per_sequence * c.tokens_per_block)
         return DX_ERR_BAD_ARG; // the table cannot hold that many tokens
-    if (p.cyclic_attention_window_size < max_past + 1 || p.max_attention_window < max_past + 1)
-        return DX_ERR_UNSUPPORTED; // sliding-window / cyclic cache is not implemented
 
     const Plan plan = make_plan(h, p.num_requests, max_past, p.host_past_key_value_lengths);
     if (plan.kind == KIND_MHA && c.tokens_per_block < 16)
@@ -539,29 +660,9 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     if (prep)
     {
         // bias + rotary embedding of the new token's q / k (bias only for v) into the workspace copy
-        PrepArgs pa{};
-        pa.qkv = p.attention_input;
-        pa.bias = p.qkv_bias;
-        pa.out = p.workspace;
-        pa.seq_len = p.sequence_lengths;
-        pa.batch = p.num_requests;
-        pa.num_heads = c.num_heads;
-        pa.num_kv_heads = c.num_kv_heads;
-        pa.head_size = c.head_size;
-        pa.pos_type = c.position_embedding_type;
-        pa.rot_dim = c.rotary_embedding_dim;
-        pa.rot_scale_type = c.rotary_embedding_scale_type;
-        pa.rot_max_positions = c.rotary_embedding_max_positions;
-        pa.rot_base = c.rotary_embedding_base;
-        pa.rot_scale = c.rotary_embedding_scale;
-        const long pairs = (long) p.num_requests * (c.num_heads + 2 * c.num_kv_heads) * (c.head_size / 2);
-        void* pargs[] = {&pa};
-        const void* fn = c.type_id == DX_DTYPE_FP16 ? reinterpret_cast<const void*>(&qkv_bias_rope_kernel<__half>)
-                                                    : reinterpret_cast<const void*>(&qkv_bias_rope_kernel<__nv_bfloat16>);
-        st = check_cuda(h, cudaLaunchKernel(fn, dim3((unsigned) ((pairs + 255) / 256)), dim3(256), pargs, 0, stream));
+        st = launch_prep(h, p, p.num_requests, stream);
         if (st != DX_OK)
             return st;
-        h->launches.fetch_add(1);
     }
 
     if (plan.kind == KIND_WIDE)

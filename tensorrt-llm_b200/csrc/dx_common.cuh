@@ -40,6 +40,35 @@ struct AttnArgs
     float softmax_scale_log2; // log2(e) / (sqrt(Dh) * q_scaling)
 };
 
+// Arguments of the feature-complete path (beam search, cyclic window, sink tokens, ALiBi).
+struct GeneralArgs
+{
+    const void* qkv;   // T [B, (H + 2 Hkv) Dh]
+    void* out;         // T [B, H Dh]
+    const int32_t* seq_len;      // [B] including the new token
+    const int64_t* block_ptrs;   // [B, 2, M]
+    const float* scale_orig_quant;
+    const float* scale_quant_orig;
+    const int32_t* cache_indir;     // [B, max_attention_window] or null (B counts beams)
+    const int32_t* context_lengths; // [B] or null
+    const void* alibi_slopes;       // T [H] or null
+    int32_t num_heads;
+    int32_t num_kv_heads;
+    int32_t max_blocks_per_seq;
+    int32_t tpb_log2;
+    int32_t beam_width;
+    int32_t max_attention_window;
+    int32_t cyclic_window; // slots the kernel may walk
+    int32_t cyclic_len;    // period of the non-sink part of the cache
+    int32_t sink;
+    float softmax_scale_log2;
+};
+
+__host__ __device__ __forceinline__ int cyclic_slot(int tok, int sink, int cyclic_len)
+{
+    return tok < sink ? tok : sink + (tok - sink) % cyclic_len;
+}
+
 static constexpr int32_t STATUS_TIMEOUT = 5;
 
 // Split-K partitioning of one sequence: `total` tokens are cut into the fewest partitions of at

@@ -1,0 +1,187 @@
+// Feature-complete generation-phase attention: beam search through the cache indirection table, cyclic
+// (sliding-window) cache with sink tokens, ALiBi.  One CTA per (sequence, q head); plain 16-byte loads per
+// lane, fp32 FMA, online softmax per lane group, merge through shared memory.  Calls that use none of these
+// features never come here: they run on the streaming kernels.
+//
+// What is restated (cpp/tensorrt_llm/kernels/decoderMaskedMultiheadAttention/decoderMaskedMultiheadAttentionTemplate.h,
+// position shift off):
+//   kv_loop_length = min(tlength, cyclic window): the kernel walks cache SLOTS 0 .. kv_loop_length-1        (:1493, :1897-1945)
+//   slot of the new token = tok < sink ? tok : sink + (tok - sink) % cyclic_len                  (kvCacheUtils.h:109-117)
+//   beams: slot s comes from sequence batch*beam_width + (s < context length ? 0 : cache_indir[bb][s]);
+//          a wrapped cache takes every slot through the table                                     (:1497-1498, :2063-2078)
+//   ALiBi: score += slope[head] * (s - tlength), nothing for the new token                              (:1797, :2026)
+// The new token is read "as stored" (quantised, then dequantised) and written to the cache by
+// kv_append_token_kernel, launched behind this kernel: every CTA sees the old content of the slot that is
+// about to be overwritten, as the reference's one-CTA-per-head kernel does for its own head.
+#pragma once
+
+#include "dx_common.cuh"
+#include "dx_mha_kernel.cuh" // MhaTraits lane mapping, dequant_vec, make_cache_vec
+
+namespace dx
+{
+
+template <typename T, int CACHE, int DH>
+__global__ void __launch_bounds__(128) general_decode_kernel(const GeneralArgs a)
+{
+    using Tr = MhaTraits<CACHE, DH>;
+    constexpr int LPR = Tr::LPR, TPW = Tr::TPW, EPL = Tr::EPL, ROW_BYTES = Tr::ROW_BYTES;
+    constexpr int U = 2;              // token passes in flight per warp
+    constexpr int NSTATE = 4 * TPW;   // lane groups of the CTA, each with its own running softmax
+    constexpr float LOG2E = 1.4426950408889634f;
+
+    const int h = blockIdx.x, bb = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane / LPR, sl = lane % LPR;
+    const int G = a.num_heads / a.num_kv_heads;
+    const int hk = h / G;
+    const int tpb_log2 = a.tpb_log2, tpb_mask = (1 << tpb_log2) - 1;
+
+    const int tlength = a.seq_len[bb] - 1;
+    const int kv_len = min(tlength, a.cyclic_window);
+    const bool beams = a.cache_indir != nullptr && a.beam_width > 1;
+    const int seq0 = beams ? (bb / a.beam_width) * a.beam_width : bb;
+    const int ctx0 = !beams ? kv_len : (tlength > a.cyclic_window ? 0 : (a.context_lengths ? a.context_lengths[bb] : 0));
+    const int32_t* indir = beams ? a.cache_indir + (size_t) bb * a.max_attention_window : nullptr;
+
+    const float deq = (CACHE == CACHE_T) ? 1.f : __ldg(a.scale_quant_orig);
+    const float sscale = deq * a.softmax_scale_log2;
+    float slope = 0.f;
+    if (a.alibi_slopes != nullptr)
+        slope = TypeOps<T>::to_float(reinterpret_cast<const T*>(a.alibi_slopes)[h]) * LOG2E;
+
+    const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
+    const T* qkv_b = reinterpret_cast<const T*>(a.qkv) + (size_t) bb * qkv_stride;
+    float q[EPL];
+    {
+        const T* qp = qkv_b + (size_t) h * DH + sl * EPL;
+#pragma unroll
+        for (int i = 0; i < EPL; i += 2)
+        {
+            const float2 v = TypeOps<T>::unpack2(*reinterpret_cast<const uint32_t*>(qp + i));
+            q[i] = v.x;
+            q[i + 1] = v.y;
+        }
+    }
+
+    float m = -INFINITY, l = 0.f, o[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i)
+        o[i] = 0.f;
+
+    auto accumulate = [&](const uint4& kraw, const uint4& vraw, float bias, bool valid)
+    {
+        float kf[EPL], vf[EPL];
+        dequant_vec<T, CACHE, EPL>(kraw, kf);
+        dequant_vec<T, CACHE, EPL>(vraw, vf);
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i)
+            d = fmaf(q[i], kf[i], d);
+#pragma unroll
+        for (int x = LPR / 2; x >= 1; x >>= 1)
+            d += __shfl_xor_sync(0xffffffffu, d, x);
+        if (valid)
+        {
+            const float s = fmaf(d, sscale, bias);
+            const float mn = fmaxf(m, s);
+            const float alpha = fast_exp2(m - mn), p = fast_exp2(s - mn);
+            m = mn;
+            l = fmaf(l, alpha, p);
+#pragma unroll
+            for (int i = 0; i < EPL; ++i)
+                o[i] = fmaf(o[i], alpha, p * vf[i]);
+        }
+    };
+
+    const size_t head_off = (size_t) hk * ((size_t) ROW_BYTES << tpb_log2) + sl * 16;
+    const int step = 4 * TPW * U;
+    for (int base = 0; base < kv_len; base += step)
+    {
+        uint4 kraw[U], vraw[U];
+        int slot[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+        {
+            slot[u] = base + (warp * U + u) * TPW + sub;
+            const int s = min(slot[u], kv_len - 1);
+            const int seq = seq0 + ((beams && s >= ctx0) ? __ldg(indir + s) : 0);
+            const int64_t* rowp = a.block_ptrs + (int64_t) seq * 2 * a.max_blocks_per_seq + (s >> tpb_log2);
+            const size_t off = head_off + (size_t) (s & tpb_mask) * ROW_BYTES;
+            kraw[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(__ldg(rowp)) + off);
+            vraw[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(__ldg(rowp + a.max_blocks_per_seq)) + off);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            accumulate(kraw[u], vraw[u], slope * (float) (slot[u] - tlength), slot[u] < kv_len);
+    }
+    // the new token, as it will be stored: one lane group of warp 0 (every lane runs the shuffles)
+    {
+        const float sc_f = (CACHE == CACHE_T) ? 1.f : __ldg(a.scale_orig_quant);
+        const T sc_t = TypeOps<T>::from_float(sc_f);
+        const T* kp = qkv_b + (size_t) (a.num_heads + hk) * DH + sl * EPL;
+        const T* vp = qkv_b + (size_t) (a.num_heads + a.num_kv_heads + hk) * DH + sl * EPL;
+        const uint4 kq = make_cache_vec<T, CACHE, EPL>(kp, sc_f, sc_t);
+        const uint4 vq = make_cache_vec<T, CACHE, EPL>(vp, sc_f, sc_t);
+        if (warp == 0)
+            accumulate(kq, vq, 0.f, sub == 0);
+    }
+
+    // ---- merge the NSTATE running states ----
+    extern __shared__ __align__(16) unsigned char smem_g[];
+    float* st_o = reinterpret_cast<float*>(smem_g); // [NSTATE][DH]
+    float* st_m = st_o + NSTATE * DH;                // [NSTATE]
+    float* st_l = st_m + NSTATE;                     // [NSTATE]
+    const int state = warp * TPW + sub;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i)
+        st_o[state * DH + sl * EPL + i] = o[i];
+    if (sl == 0)
+    {
+        st_m[state] = m;
+        st_l[state] = l;
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < DH; d += blockDim.x)
+    {
+        float M = -INFINITY;
+        for (int s = 0; s < NSTATE; ++s)
+            M = fmaxf(M, st_m[s]);
+        float L = 0.f, acc = 0.f;
+        for (int s = 0; s < NSTATE; ++s)
+        {
+            const float f = fast_exp2(st_m[s] - M); // empty states: m = -inf -> 0
+            L = fmaf(st_l[s], f, L);
+            acc = fmaf(st_o[s * DH + d], f, acc);
+        }
+        reinterpret_cast<T*>(a.out)[((size_t) bb * a.num_heads + h) * DH + d] = TypeOps<T>::from_float(acc * deq / L);
+    }
+}
+
+// Writes the new token's K and V rows (quantised as the reference stores them) at its cyclic slot.
+// Grid (Hkv, B), one warp.
+template <typename T, int CACHE, int DH>
+__global__ void __launch_bounds__(32) kv_append_token_kernel(const GeneralArgs a)
+{
+    using Tr = MhaTraits<CACHE, DH>;
+    constexpr int LPR = Tr::LPR, EPL = Tr::EPL, ROW_BYTES = Tr::ROW_BYTES;
+    const int hk = blockIdx.x, bb = blockIdx.y, lane = threadIdx.x;
+    if (lane >= LPR)
+        return;
+    const int tlength = a.seq_len[bb] - 1;
+    const int slot = cyclic_slot(tlength, a.sink, a.cyclic_len);
+    const int tpb_log2 = a.tpb_log2, tpb_mask = (1 << tpb_log2) - 1;
+    const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
+    const T* qkv_b = reinterpret_cast<const T*>(a.qkv) + (size_t) bb * qkv_stride;
+    const float sc_f = (CACHE == CACHE_T) ? 1.f : __ldg(a.scale_orig_quant);
+    const T sc_t = TypeOps<T>::from_float(sc_f);
+    const uint4 kq = make_cache_vec<T, CACHE, EPL>(qkv_b + (size_t) (a.num_heads + hk) * DH + lane * EPL, sc_f, sc_t);
+    const uint4 vq = make_cache_vec<T, CACHE, EPL>(
+        qkv_b + (size_t) (a.num_heads + a.num_kv_heads + hk) * DH + lane * EPL, sc_f, sc_t);
+    const int64_t* rowp = a.block_ptrs + (int64_t) bb * 2 * a.max_blocks_per_seq + (slot >> tpb_log2);
+    const size_t off = (size_t) hk * ((size_t) ROW_BYTES << tpb_log2) + (size_t) (slot & tpb_mask) * ROW_BYTES + lane * 16;
+    *reinterpret_cast<uint4*>(reinterpret_cast<char*>(__ldg(rowp)) + off) = kq;
+    *reinterpret_cast<uint4*>(reinterpret_cast<char*>(__ldg(rowp + a.max_blocks_per_seq)) + off) = vq;
+}
+
+} // namespace dx

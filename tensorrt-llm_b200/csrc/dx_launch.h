@@ -16,6 +16,13 @@ KernelInfo mha_kernel_info(int dtype, int cache, int dh, int tokens_per_block);
 KernelInfo gqa_kernel_info(int dtype, int cache, int dh, bool heads16);
 KernelInfo wide_kernel_info(int dtype, int dh); // FP8 cache only
 KernelInfo tok_kernel_info(int dtype, int dh, int group); // FP8 cache, Dh 128, group <= 16
+struct GeneralKernels
+{
+    const void* attn = nullptr;   // general_decode_kernel: grid (H, B), 128 threads, `smem` dynamic bytes
+    const void* append = nullptr; // kv_append_token_kernel: grid (Hkv, B), 32 threads
+    int smem = 0;
+};
+GeneralKernels general_kernel_info(int dtype, int cache, int dh);
 KernelInfo merge_kernel_info(int dtype, int dh);
 KernelInfo append_kernel_info(int dtype, int cache, int dh);
 } // namespace dx

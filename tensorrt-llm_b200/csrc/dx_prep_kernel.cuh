@@ -22,7 +22,9 @@ enum : int
 {
     POS_LEARNED_ABSOLUTE = 0,
     POS_ROPE_GPTJ = 1,
-    POS_ROPE_GPT_NEOX = 2
+    POS_ROPE_GPT_NEOX = 2,
+    POS_ALIBI = 3,           // no change of q / k; slopes are added to the scores
+    POS_ALIBI_WITH_SCALE = 4
 };
 
 enum : int

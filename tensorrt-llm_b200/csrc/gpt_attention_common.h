@@ -39,7 +39,7 @@ struct EnqueueGenerationParams
     int32_t const* context_lengths = nullptr;
     float const* kv_scale_orig_quant = nullptr;
     float const* kv_scale_quant_orig = nullptr;
-    T const* alibi_slopes = nullptr; // must be nullptr
+    T const* alibi_slopes = nullptr; // needs an ALiBi position embedding type (setPositionEmbedding)
     T* context_buf = nullptr;
     void* key_value_cache = nullptr; // contiguous cache: not supported, must be nullptr
     void* block_pointers = nullptr;
@@ -131,8 +131,8 @@ public:
     {
         if (!mHandle)
             return DX_ERR_BAD_ARG;
-        if (params.alibi_slopes || params.key_value_cache || params.input_seq_length != 1)
-            return DX_ERR_UNSUPPORTED;
+        if (params.key_value_cache || params.input_seq_length != 1)
+            return DX_ERR_UNSUPPORTED; // contiguous cache, multi-token (Medusa) queries
         dx_attn_generation_params p{};
         p.struct_size = sizeof(p);
         p.attention_input = params.attention_input;
@@ -153,6 +153,8 @@ public:
         p.workspace_bytes = params.workspace_bytes;
         p.cache_indir = params.cache_indir;
         p.qkv_bias = params.qkv_bias;
+        p.context_lengths = params.context_lengths;
+        p.alibi_slopes = params.alibi_slopes;
         return dx_attn_enqueue_generation(mHandle, &p, stream);
     }
 

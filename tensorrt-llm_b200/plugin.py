@@ -28,6 +28,8 @@ class PositionEmbeddingType:
     learned_absolute = 0
     rope_gptj = 1
     rope_gpt_neox = 2
+    alibi = 3
+    alibi_with_scale = 4
 
 
 class RotaryScalingType:
@@ -74,7 +76,8 @@ class _GenParams(ctypes.Structure):
                 ("host_block_pointers", ctypes.c_void_p), ("kv_scale_orig_quant", ctypes.c_void_p),
                 ("kv_scale_quant_orig", ctypes.c_void_p), ("context_buf", ctypes.c_void_p),
                 ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
-                ("cache_indir", ctypes.c_void_p), ("qkv_bias", ctypes.c_void_p)]
+                ("cache_indir", ctypes.c_void_p), ("qkv_bias", ctypes.c_void_p),
+                ("context_lengths", ctypes.c_void_p), ("alibi_slopes", ctypes.c_void_p)]
 
 
 EXPORTED_SYMBOLS = [
@@ -219,7 +222,7 @@ class GPTAttentionPlugin:
     def _params(self, qkv, sequence_length, host_past_key_value_lengths, kv_cache_block_pointers,
                 kv_orig_quant_scale, kv_quant_orig_scale, out, workspace, max_attention_window,
                 host_kv_cache_block_pointers=None, cache_indirection=None, beam_width=1, sink_token_length=0,
-                qkv_bias=None):
+                qkv_bias=None, cyclic_attention_window_size=None, context_lengths=None, alibi_slopes=None):
         B = qkv.shape[0]
         M = kv_cache_block_pointers.shape[-1]
         hp = host_past_key_value_lengths
@@ -232,10 +235,10 @@ class GPTAttentionPlugin:
         p.host_past_key_value_lengths = _ptr(hp)
         p.past_kv_length = max_past
         p.beam_width = beam_width
-        p.num_requests = B
+        p.num_requests = B // max(1, beam_width)
         p.max_blocks_per_sequence = M
         p.max_attention_window = window
-        p.cyclic_attention_window_size = window
+        p.cyclic_attention_window_size = window if cyclic_attention_window_size is None else cyclic_attention_window_size
         p.sink_token_length = sink_token_length
         p.block_pointers = _ptr(kv_cache_block_pointers)
         p.host_block_pointers = _ptr(host_kv_cache_block_pointers)
@@ -246,6 +249,8 @@ class GPTAttentionPlugin:
         p.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
         p.cache_indir = _ptr(cache_indirection)
         p.qkv_bias = _ptr(qkv_bias)
+        p.context_lengths = _ptr(context_lengths)
+        p.alibi_slopes = _ptr(alibi_slopes)
         return p, max_past
 
     def _ensure_workspace(self, batch: int, max_past: int, device) -> Optional[torch.Tensor]:
@@ -265,10 +270,16 @@ class GPTAttentionPlugin:
                            host_kv_cache_block_pointers: Optional[torch.Tensor] = None,
                            cache_indirection: Optional[torch.Tensor] = None, beam_width: int = 1,
                            sink_token_length: int = 0, qkv_bias: Optional[torch.Tensor] = None,
+                           cyclic_attention_window_size: Optional[int] = None,
+                           context_lengths: Optional[torch.Tensor] = None,
+                           alibi_slopes: Optional[torch.Tensor] = None,
                            stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
         """qkv: T [B, (H+2Hkv)*Dh] (device); sequence_length: int32 [B] (device, includes the new token);
         host_past_key_value_lengths: int32 [B] (host); kv_cache_block_pointers: int64 [B, 2, M] (device).
-        Appends the new token to the cache and returns the attention output T [B, H*Dh].  Asynchronous."""
+        Appends the new token to the cache and returns the attention output T [B, H*Dh].  Asynchronous.
+        Beam search: B = batch * beam_width, cache_indirection int32 [B, max_attention_window] and
+        context_lengths int32 [B] on the device.  Sliding window: cyclic_attention_window_size (and
+        sink_token_length).  ALiBi: alibi_slopes T [H] on the device (plugin built with an ALiBi type)."""
         if not qkv.is_cuda:
             raise DecodeAttnError(DX_ERR_BAD_ARG, "enqueue_generation needs device tensors (no CPU path exists)")
         if qkv.dtype != self.dtype:
@@ -282,7 +293,8 @@ class GPTAttentionPlugin:
             workspace = self._ensure_workspace(B, max_past, qkv.device)
         p, _ = self._params(qkv, sequence_length, hp, kv_cache_block_pointers, kv_orig_quant_scale,
                             kv_quant_orig_scale, out, workspace, max_attention_window,
-                            host_kv_cache_block_pointers, cache_indirection, beam_width, sink_token_length, qkv_bias)
+                            host_kv_cache_block_pointers, cache_indirection, beam_width, sink_token_length, qkv_bias,
+                            cyclic_attention_window_size, context_lengths, alibi_slopes)
         s = stream if stream is not None else torch.cuda.current_stream(qkv.device)
         st = self.lib.dx_attn_enqueue_generation(self._h, ctypes.byref(p), ctypes.c_void_p(s.cuda_stream))
         if st != DX_OK:

@@ -52,10 +52,12 @@ def test_good_call_launches_and_bad_calls_do_not(setup):
         (dict(num_requests=-1), P.DX_ERR_BAD_ARG),
         (dict(max_blocks_per_sequence=0), P.DX_ERR_BAD_ARG),
         (dict(max_blocks_per_sequence=2), P.DX_ERR_BAD_ARG),                      # table cannot hold the tokens
-        (dict(beam_width=4), P.DX_ERR_UNSUPPORTED),
-        (dict(cache_indir=w.qkv.data_ptr()), P.DX_ERR_UNSUPPORTED),
-        (dict(sink_token_length=4), P.DX_ERR_UNSUPPORTED),
-        (dict(cyclic_attention_window_size=512), P.DX_ERR_UNSUPPORTED),          # sliding window
+        (dict(beam_width=0), P.DX_ERR_BAD_ARG),
+        (dict(beam_width=3), P.DX_ERR_BAD_ARG),                                   # beams without an indirection table
+        (dict(sink_token_length=4), P.DX_ERR_UNSUPPORTED),                        # sink ends inside a block
+        (dict(cyclic_attention_window_size=512), P.DX_ERR_UNSUPPORTED),          # wrapped window, table with spare blocks
+        (dict(cyclic_attention_window_size=0), P.DX_ERR_BAD_ARG),
+        (dict(alibi_slopes=w.qkv.data_ptr()), P.DX_ERR_BAD_ARG),                  # slopes without an ALiBi plugin
         (dict(struct_size=8), P.DX_ERR_BAD_ARG),
     ]
     for over, want in bad:
