@@ -118,7 +118,7 @@ Plan make_plan(const dx_attn* h, int batch, int max_past_len, const int32_t* hos
         p.kind = KIND_WIDE;
         p.hgroups = (h->group + 127) / 128;
         rows_per_seq = c.num_kv_heads * p.hgroups;
-        resident = c.head_size == 64 ? 3 : 2;
+        resident = h->k_wide.resident;
     }
     else if (grouped && h->tok)
     {

@@ -156,6 +156,18 @@ __device__ __forceinline__ void cp_async16(void* dst_smem, const void* src_gmem)
 }
 
 // Makes the executing thread's prior cp.async operations arrive on the mbarrier when they land.
+// 16-byte asynchronous copy global -> shared (shared address as a 32-bit window offset); the zfill form
+// copies src_bytes (0 or 16) and zero-fills the rest.
+__device__ __forceinline__ void cp_async16_u32(uint32_t dst, const void* src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+__device__ __forceinline__ void cp_async16_zfill_u32(uint32_t dst, const void* src, uint32_t src_bytes)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+
 __device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t* bar)
 {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");

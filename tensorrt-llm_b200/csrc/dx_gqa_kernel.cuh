@@ -196,16 +196,6 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr)
     return v;
 }
 
-__device__ __forceinline__ void cp_async16_u32(uint32_t dst, const void* src)
-{
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-
-__device__ __forceinline__ void cp_async16_zfill_u32(uint32_t dst, const void* src, uint32_t src_bytes)
-{
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-
 template <typename T, int CACHE, int DH, bool H16>
 __global__ void __launch_bounds__(128, gqa_min_blocks<CACHE, DH, H16>()) gqa_decode_kernel(const AttnArgs a, const int hgroups)
 {

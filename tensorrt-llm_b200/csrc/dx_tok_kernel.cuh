@@ -23,7 +23,7 @@
 #ifndef DX_TOK_STAGES
 #define DX_TOK_STAGES 2
 #endif
-#include "dx_wide_kernel.cuh" // hw_swz, umma_desc, umma_f8, umma_commit
+#include "dx_tcgen05.cuh"
 
 
 namespace dx
@@ -70,53 +70,6 @@ __device__ __forceinline__ void split4_lo16(float x0, float x1, float x2, float 
     asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(l23) : "r"(x23));
     hi = (uint32_t) h01 | ((uint32_t) h23 << 16);
     lo = (uint32_t) l01 | ((uint32_t) l23 << 16);
-}
-
-// One row (32 lanes x NC columns) of fp32 accumulators: tensor memory -> registers and back.
-template <int NC>
-__device__ __forceinline__ void tmem_ld_row(uint32_t addr, float (&v)[NC])
-{
-    static_assert(NC == 16 || NC == 32, "16 or 32 columns");
-    if constexpr (NC == 32)
-    {
-        tmem_ld32(addr, v);
-    }
-    else
-    {
-        uint32_t r[16];
-        __syncwarp();
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-              "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-            : "r"(addr));
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-            v[i] = __uint_as_float(r[i]);
-    }
-}
-
-template <int NC>
-__device__ __forceinline__ void tmem_st_row(uint32_t addr, const float (&v)[NC])
-{
-    static_assert(NC == 16 || NC == 32, "16 or 32 columns");
-    __syncwarp();
-#pragma unroll
-    for (int c = 0; c < NC; c += 16)
-    {
-        asm volatile(
-            "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(
-                addr + c),
-            "r"(__float_as_uint(v[c])), "r"(__float_as_uint(v[c + 1])), "r"(__float_as_uint(v[c + 2])),
-            "r"(__float_as_uint(v[c + 3])), "r"(__float_as_uint(v[c + 4])), "r"(__float_as_uint(v[c + 5])),
-            "r"(__float_as_uint(v[c + 6])), "r"(__float_as_uint(v[c + 7])), "r"(__float_as_uint(v[c + 8])),
-            "r"(__float_as_uint(v[c + 9])), "r"(__float_as_uint(v[c + 10])), "r"(__float_as_uint(v[c + 11])),
-            "r"(__float_as_uint(v[c + 12])), "r"(__float_as_uint(v[c + 13])), "r"(__float_as_uint(v[c + 14])),
-            "r"(__float_as_uint(v[c + 15]))
-            : "memory");
-    }
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
 template <typename T, int GP>

@@ -19,6 +19,7 @@ static KernelInfo mk()
     KernelInfo k;
     k.fn = reinterpret_cast<const void*>(&wide_decode_kernel<T, DH>);
     k.smem = WideTraits<DH>::SMEM_BYTES;
+    k.resident = WideTraits<DH>::MIN_BLOCKS;
     return k;
 }
 
