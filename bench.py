@@ -270,40 +270,48 @@ def run_own_arm(args):
     h_qkv = [pin(w.qkv) for w in ws]
     h_len = [pin(w.sequence_length) for w in ws]
     h_tbl = [pin(w.kv_cache_block_pointers) for w in ws]
-    h_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    h_out = [torch.empty(out.shape, dtype=out.dtype).pin_memory() for _ in range(5)]
 
-    bound_host = [plugin.bind_generation(h_qkv[j], h_len[j], ws[j].host_past_key_value_lengths, h_tbl[j],
-                                         ws[j].kv_orig_quant_scale, ws[j].kv_quant_orig_scale, out=h_out,
-                                         workspace=workspace, host=True, sync=True,
-                                         max_attention_window=ws[j].max_blocks_per_seq * cfg.tokens_per_block)
-                  for j in range(replicas)]
+    def bind_host(sync):
+        return [plugin.bind_generation(h_qkv[j % replicas], h_len[j % replicas],
+                                       ws[j % replicas].host_past_key_value_lengths, h_tbl[j % replicas],
+                                       ws[j % replicas].kv_orig_quant_scale, ws[j % replicas].kv_quant_orig_scale,
+                                       out=h_out[j % 5], workspace=workspace, host=True, sync=sync,
+                                       max_attention_window=ws[j % replicas].max_blocks_per_seq * cfg.tokens_per_block)
+                for j in range(5 * replicas)]
 
-    def e2e_step(i):
-        bound_host[i % replicas]()
-
-    e2e_ms_local = float("nan")
-    if not args.no_e2e:
+    def time_e2e(calls, drain):
         for i in range(3):
-            e2e_step(i)
+            calls[i % len(calls)]()
+        drain()
         barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for i in range(e2e_steps):
-            e2e_step(i)  # synchronous: the result is in host memory when it returns
+            calls[i % len(calls)]()
+        drain()  # the last results are in host memory; e1 is recorded behind that point
         e1.record(stream)
         torch.cuda.synchronize()
         barrier()
-        e2e_ms_local = e0.elapsed_time(e1) / e2e_steps
+        return e0.elapsed_time(e1) / e2e_steps
+
+    # Two figures through the host-buffer entry point, every step copying its inputs from pinned host memory
+    # and its result back: (a) pipelined - sync=0, the copies of a step overlap the kernels of the steps
+    # before it (four staging slots in the library), results waited for with host_sync(); (b) strictly synchronous.
+    e2e_ms_local = e2e_sync_ms_local = float("nan")
+    if not args.no_e2e:
+        e2e_ms_local = time_e2e(bind_host(False), plugin.host_sync)
+        e2e_sync_ms_local = time_e2e(bind_host(True), lambda: None)
     h2d = h_qkv[0].numel() * 2 + h_len[0].numel() * 4 + h_tbl[0].numel() * 8
-    d2h = h_out.numel() * 2
+    d2h = h_out[0].numel() * 2
     # the device result of the e2e path equals the resident path's
     torch.cuda.synchronize()
 
     kv_bytes_local = float(sum(w.kv_bytes for w in ws)) / replicas
     flops_local = float(w0.flops)
-    (ms, e2e_ms, _), (kv_bytes_total, flops_total, launches_total) = reduce_over_ranks(
-        dist, dev, [ms_local, e2e_ms_local, kern_ms], [kv_bytes_local, flops_local, float(launches)])
+    (ms, e2e_ms, _, e2e_sync_ms), (kv_bytes_total, flops_total, launches_total) = reduce_over_ranks(
+        dist, dev, [ms_local, e2e_ms_local, kern_ms, e2e_sync_ms_local], [kv_bytes_local, flops_local, float(launches)])
 
     if rank == 0:
         peak, peak_src = measured_peak_gbs()
@@ -330,7 +338,11 @@ def run_own_arm(args):
             "kv_bytes_per_step": kv_bytes_total, "tflops_algorithmic": flops_total / (ms * 1e-3) / 1e12,
             "hbm_frac_of_measured_peak": value / (peak * world), "hbm_frac_of_8TBps_nominal": value / (8000.0 * world),
             "e2e": None if args.no_e2e else {"value": kv_bytes_total / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d * world,
-                    "d2h_bytes_per_step": d2h * world, "us_per_step": e2e_ms * 1e3, "steps": e2e_steps},
+                    "d2h_bytes_per_step": d2h * world, "us_per_step": e2e_ms * 1e3, "steps": e2e_steps,
+                    "mode": "host-buffer C-ABI call with sync=0: the copies of a step overlap the kernels of the "
+                            "steps before it (four staging slots), every result read back to pinned host memory",
+                    "synchronous_value": kv_bytes_total / (e2e_sync_ms * 1e-3) / 1e9,
+                    "synchronous_us_per_step": e2e_sync_ms * 1e3},
             "gpu_launches": int(launches_total),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": profiled_traffic(f"{full_cfg.name}_tp{tp}"),

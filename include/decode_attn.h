@@ -172,8 +172,13 @@ int dx_attn_enqueue_generation(dx_attn_t* handle, const dx_attn_generation_param
  * (grown on demand, the only allocation this library ever makes after create), runs the step and
  * copies context_buf back to the host pointer.  All of params' attention_input, sequence_lengths,
  * block_pointers and context_buf are HOST pointers here; the scales, the KV pool and the workspace
- * stay on the device.  Asynchronous on the stream unless sync != 0.  Mirrors what the reference
- * runtime does every step before enqueueV3 (tensorrt_llm/runtime/generation.py:2219-2221). */
+ * stay on the device.  Mirrors what the reference runtime does every step before enqueueV3
+ * (tensorrt_llm/runtime/generation.py:2219-2221).
+ * The copies run on two streams owned by the handle, the kernels on cuda_stream, with four staging slots:
+ * with sync == 0 the call returns at once and the copies of later calls overlap these kernels; the
+ * output is in host memory after dx_attn_host_sync() (or when the fourth call after this one returns: it
+ * waits for the slot).  With sync != 0 the output is in host memory on return.  The host buffers of a
+ * call must stay untouched until then. */
 int dx_attn_enqueue_generation_host(
     dx_attn_t* handle, const dx_attn_generation_params* params, void* cuda_stream, int32_t sync);
 
@@ -204,6 +209,10 @@ int dx_attn_append_context(dx_attn_t* handle, const void* k_src, const void* v_s
     const int32_t* sequence_lengths, int32_t batch, int32_t seq_len, int32_t attention_window_size,
     const int64_t* block_pointers, int32_t max_blocks_per_sequence, const float* kv_scale_orig_quant,
     void* cuda_stream);
+
+/* Waits until the outputs of all dx_attn_enqueue_generation_host calls made so far are in host memory.
+ * No reference counterpart (the reference runtime synchronises the whole stream every step). */
+int dx_attn_host_sync(dx_attn_t* handle);
 
 /* Host-side check of a block-pointer table against the pool it must point into; launches nothing.
  * Stands in for the bounds checking the reference does not have (its kernels trust the table). */

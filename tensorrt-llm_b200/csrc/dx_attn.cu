@@ -74,8 +74,15 @@ struct dx_attn
     int last_cuda_error = 0;
     std::atomic<int64_t> launches{0};
     // staging for the host-buffer entry point
-    void* stage_dev = nullptr;
+    static constexpr int HOST_SLOTS = 4; // host-path steps that may be in flight
+    void* stage_dev = nullptr;           // HOST_SLOTS slots of stage_bytes each
     size_t stage_bytes = 0;
+    cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr; // copy streams of the host path (created on first use)
+    cudaEvent_t ev_in[HOST_SLOTS] = {};   // inputs of the slot are on the device
+    cudaEvent_t ev_done[HOST_SLOTS] = {}; // kernels of the slot have finished
+    cudaEvent_t ev_out[HOST_SLOTS] = {};  // output of the slot is in host memory
+    bool out_pending[HOST_SLOTS] = {};
+    unsigned host_calls = 0;
 };
 
 namespace
@@ -547,6 +554,14 @@ void dx_attn_destroy(dx_attn_t* h)
         cudaFree(h->status_dev);
     if (h->stage_dev)
         cudaFree(h->stage_dev);
+    for (int i = 0; i < dx_attn::HOST_SLOTS; ++i)
+    {
+        if (h->ev_in[i]) cudaEventDestroy(h->ev_in[i]);
+        if (h->ev_done[i]) cudaEventDestroy(h->ev_done[i]);
+        if (h->ev_out[i]) cudaEventDestroy(h->ev_out[i]);
+    }
+    if (h->h2d_stream) cudaStreamDestroy(h->h2d_stream);
+    if (h->d2h_stream) cudaStreamDestroy(h->d2h_stream);
     delete h;
 }
 
@@ -735,7 +750,7 @@ int dx_attn_enqueue_generation_host(
         return DX_OK;
     if (!p.attention_input || !p.sequence_lengths || !p.block_pointers || !p.context_buf)
         return DX_ERR_BAD_ARG;
-    const size_t B = (size_t) p.num_requests;
+    const size_t B = (size_t) p.num_requests * (size_t) std::max(1, p.beam_width); // sequences
     const size_t qkv_bytes = B * (size_t) (c.num_heads + 2 * c.num_kv_heads) * c.head_size * 2;
     const size_t out_bytes = B * (size_t) c.num_heads * c.head_size * 2;
     const size_t tbl_bytes = B * 2 * (size_t) p.max_blocks_per_sequence * sizeof(int64_t);
@@ -747,30 +762,61 @@ int dx_attn_enqueue_generation_host(
     int st = check_cuda(h, cudaSetDevice(c.device));
     if (st != DX_OK)
         return st;
+    if (!h->h2d_stream)
+    {
+        st = check_cuda(h, cudaStreamCreateWithFlags(&h->h2d_stream, cudaStreamNonBlocking));
+        if (st == DX_OK)
+            st = check_cuda(h, cudaStreamCreateWithFlags(&h->d2h_stream, cudaStreamNonBlocking));
+        for (int i = 0; i < dx_attn::HOST_SLOTS && st == DX_OK; ++i)
+        {
+            st = check_cuda(h, cudaEventCreateWithFlags(&h->ev_in[i], cudaEventDisableTiming));
+            if (st == DX_OK)
+                st = check_cuda(h, cudaEventCreateWithFlags(&h->ev_done[i], cudaEventDisableTiming));
+            if (st == DX_OK)
+                st = check_cuda(h, cudaEventCreateWithFlags(&h->ev_out[i], cudaEventDisableTiming));
+        }
+        if (st != DX_OK)
+            return st;
+    }
     if (h->stage_bytes < total)
     {
         // Growing the staging area is the one allocation made after create(); it synchronises.
+        st = check_cuda(h, cudaDeviceSynchronize());
+        if (st != DX_OK)
+            return st;
+        for (bool& pending : h->out_pending)
+            pending = false;
         if (h->stage_dev)
-        {
-            st = check_cuda(h, cudaDeviceSynchronize());
-            if (st != DX_OK)
-                return st;
             cudaFree(h->stage_dev);
-            h->stage_dev = nullptr;
-            h->stage_bytes = 0;
-        }
-        st = check_cuda(h, cudaMalloc(&h->stage_dev, total));
+        h->stage_dev = nullptr;
+        h->stage_bytes = 0;
+        st = check_cuda(h, cudaMalloc(&h->stage_dev, dx_attn::HOST_SLOTS * total));
         if (st != DX_OK)
             return st;
         h->stage_bytes = total;
     }
-    char* base = reinterpret_cast<char*>(h->stage_dev);
-    st = check_cuda(h, cudaMemcpyAsync(base + o_qkv, p.attention_input, qkv_bytes, cudaMemcpyHostToDevice, stream));
-    if (st == DX_OK)
-        st = check_cuda(h, cudaMemcpyAsync(base + o_tbl, p.block_pointers, tbl_bytes, cudaMemcpyHostToDevice, stream));
+    // Staging slots: the copies of this step run on their own streams beside the kernels of the steps before
+    // it.  A slot is reused only after the output of the step that used it last is in host memory.
+    const int slot = (int) (h->host_calls % dx_attn::HOST_SLOTS);
+    if (h->out_pending[slot])
+    {
+        st = check_cuda(h, cudaEventSynchronize(h->ev_out[slot]));
+        if (st != DX_OK)
+            return st;
+        h->out_pending[slot] = false;
+    }
+    char* base = reinterpret_cast<char*>(h->stage_dev) + (size_t) slot * h->stage_bytes;
+    st = check_cuda(h, cudaMemcpyAsync(base + o_qkv, p.attention_input, qkv_bytes, cudaMemcpyHostToDevice, h->h2d_stream));
     if (st == DX_OK)
         st = check_cuda(
-            h, cudaMemcpyAsync(base + o_len, p.sequence_lengths, len_bytes, cudaMemcpyHostToDevice, stream));
+            h, cudaMemcpyAsync(base + o_tbl, p.block_pointers, tbl_bytes, cudaMemcpyHostToDevice, h->h2d_stream));
+    if (st == DX_OK)
+        st = check_cuda(
+            h, cudaMemcpyAsync(base + o_len, p.sequence_lengths, len_bytes, cudaMemcpyHostToDevice, h->h2d_stream));
+    if (st == DX_OK)
+        st = check_cuda(h, cudaEventRecord(h->ev_in[slot], h->h2d_stream));
+    if (st == DX_OK)
+        st = check_cuda(h, cudaStreamWaitEvent(stream, h->ev_in[slot], 0));
     if (st != DX_OK)
         return st;
     void* host_out = p.context_buf;
@@ -781,9 +827,40 @@ int dx_attn_enqueue_generation_host(
     st = dx_attn_enqueue_generation(h, &p, cuda_stream);
     if (st != DX_OK)
         return st;
-    st = check_cuda(h, cudaMemcpyAsync(host_out, base + o_out, out_bytes, cudaMemcpyDeviceToHost, stream));
-    if (st == DX_OK && sync)
-        st = check_cuda(h, cudaStreamSynchronize(stream));
+    st = check_cuda(h, cudaEventRecord(h->ev_done[slot], stream));
+    if (st == DX_OK)
+        st = check_cuda(h, cudaStreamWaitEvent(h->d2h_stream, h->ev_done[slot], 0));
+    if (st == DX_OK)
+        st = check_cuda(h, cudaMemcpyAsync(host_out, base + o_out, out_bytes, cudaMemcpyDeviceToHost, h->d2h_stream));
+    if (st == DX_OK)
+        st = check_cuda(h, cudaEventRecord(h->ev_out[slot], h->d2h_stream));
+    if (st != DX_OK)
+        return st;
+    h->out_pending[slot] = true;
+    ++h->host_calls;
+    if (sync)
+    {
+        st = check_cuda(h, cudaEventSynchronize(h->ev_out[slot]));
+        h->out_pending[slot] = false;
+    }
+    return st;
+}
+
+int dx_attn_host_sync(dx_attn_t* h)
+{
+    if (!h)
+        return DX_ERR_BAD_ARG;
+    int st = DX_OK;
+    for (int i = 0; i < dx_attn::HOST_SLOTS; ++i)
+    {
+        if (h->out_pending[i])
+        {
+            const int e = check_cuda(h, cudaEventSynchronize(h->ev_out[i]));
+            if (e != DX_OK)
+                st = e;
+            h->out_pending[i] = false;
+        }
+    }
     return st;
 }
 

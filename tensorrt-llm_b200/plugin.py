@@ -82,7 +82,7 @@ class _GenParams(ctypes.Structure):
 
 EXPORTED_SYMBOLS = [
     "dx_abi_version", "dx_strerror", "dx_attn_create", "dx_attn_destroy", "dx_attn_workspace_size",
-    "dx_attn_enqueue_generation", "dx_attn_enqueue_generation_host", "dx_attn_validate", "dx_attn_plan",
+    "dx_attn_enqueue_generation", "dx_attn_enqueue_generation_host", "dx_attn_host_sync", "dx_attn_validate", "dx_attn_plan",
     "dx_attn_device_status", "dx_attn_last_cuda_error", "dx_attn_launch_count",
     "dx_attn_enqueue_generation_static_scratch", "dx_attn_static_scratch_bytes", "dx_attn_append_context",
 ]
@@ -117,6 +117,8 @@ def load_library() -> ctypes.CDLL:
     lib.dx_attn_enqueue_generation_host.restype = ctypes.c_int
     lib.dx_attn_enqueue_generation_host.argtypes = [ctypes.c_void_p, ctypes.POINTER(_GenParams), ctypes.c_void_p,
                                                     ctypes.c_int32]
+    lib.dx_attn_host_sync.restype = ctypes.c_int
+    lib.dx_attn_host_sync.argtypes = [ctypes.c_void_p]
     lib.dx_attn_enqueue_generation_static_scratch.restype = ctypes.c_int
     lib.dx_attn_enqueue_generation_static_scratch.argtypes = [ctypes.c_void_p, ctypes.POINTER(_GenParams),
                                                               ctypes.c_void_p]
@@ -359,6 +361,12 @@ class GPTAttentionPlugin:
                 if st != DX_OK:
                     raise DecodeAttnError(st, "dx_attn_enqueue_generation")
         return call
+
+    def host_sync(self) -> None:
+        """Waits until the outputs of all host-buffer calls made so far are in host memory."""
+        st = self.lib.dx_attn_host_sync(self._h)
+        if st != DX_OK:
+            raise DecodeAttnError(st, "dx_attn_host_sync")
 
     def enqueue_generation_host(self, qkv: torch.Tensor, sequence_length: torch.Tensor,
                                 host_past_key_value_lengths: torch.Tensor, kv_cache_block_pointers: torch.Tensor,
