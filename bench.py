@@ -49,13 +49,13 @@ def measured_peak_gbs():
 
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (gqa_decode_fp8_c4.md, gqa_decode_int8_c5.md, mha_int8_decode_c2.md,
-# gqa_decode_fp8_c3.md, gqa_decode_fp8_c4_tp8_shard.md).  Captured at full size: each fits the capture rule.
+# wide_decode_fp8_c3.md, gqa_decode_fp8_c4_tp8_shard.md).  Captured at full size: each fits the capture rule.
 PROFILED_TRAFFIC = {
-    "c4_llama2_70b_gqa_fp8_tp1": 807498752,
-    "c5_mixtral_long_gqa_int8_tp1": 377083136,
-    "c2_llama2_7b_mha_int8_tp1": 813831424,
-    "c3_falcon_7b_mqa_fp8_tp1": 20070400,
-    "c4_llama2_70b_gqa_fp8_tp8": 103741952,
+    "c4_llama2_70b_gqa_fp8_tp1": 807324416,
+    "c5_mixtral_long_gqa_int8_tp1": 378181120,
+    "c2_llama2_7b_mha_int8_tp1": 817228800,
+    "c3_falcon_7b_mqa_fp8_tp1": 20099584,
+    "c4_llama2_70b_gqa_fp8_tp8": 103595008,
 }
 
 
