@@ -214,6 +214,20 @@ int dx_attn_append_context(dx_attn_t* handle, const void* k_src, const void* v_s
  * No reference counterpart (the reference runtime synchronises the whole stream every step). */
 int dx_attn_host_sync(dx_attn_t* handle);
 
+/* Device-resident form of the runtime's per-step cache bookkeeping (KVCacheManager.step + get_block_pointers for
+ * unfinished sequences, tensorrt_llm/runtime/kv_cache_manager.py:305-345, :380-387, which the reference runs on
+ * the host and uploads every step, tensorrt_llm/runtime/generation.py:2219-2221).  On the stream: every
+ * sequence_lengths[b] grows by one (it then counts the token the next decode step writes); a sequence whose new
+ * token starts a block takes the next entry of free_blocks (device, int64 [n_free, 2]: K block pointer, V block
+ * pointer) in batch order, written into block_pointers (device, int64 [num_requests, 2, M]); *free_cursor
+ * (device) is the first unused entry, read and advanced.  The table is the one the host manager builds for the
+ * same free list.  An exhausted list or table row is reported by dx_attn_device_status as DX_ERR_BOUNDS (the
+ * pointer is then not written).  Launches one kernel; allocates nothing; may be captured in a CUDA graph
+ * together with dx_attn_enqueue_generation. */
+int dx_kv_cache_step(dx_attn_t* handle, int32_t* sequence_lengths, int64_t* block_pointers, int32_t num_requests,
+    int32_t max_blocks_per_sequence, const int64_t* free_blocks, int32_t n_free, int32_t* free_cursor,
+    void* cuda_stream);
+
 /* Host-side check of a block-pointer table against the pool it must point into; launches nothing.
  * Stands in for the bounds checking the reference does not have (its kernels trust the table). */
 int dx_attn_validate(const dx_attn_t* handle, const int64_t* host_block_pointers,

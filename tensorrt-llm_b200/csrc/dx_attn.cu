@@ -14,6 +14,7 @@
 
 #include "../../include/decode_attn.h"
 #include "dx_append_kernel.cuh"
+#include "dx_kvstep_kernel.cuh"
 #include "dx_launch.h"
 #include "dx_merge_kernel.cuh"
 #include "dx_prep_kernel.cuh"
@@ -915,7 +916,41 @@ int dx_attn_device_status(dx_attn_t* h)
         if (st != DX_OK)
             return st;
     }
-    return v == 0 ? DX_OK : (v == STATUS_TIMEOUT ? DX_ERR_TIMEOUT : DX_ERR_CUDA);
+    return v == 0 ? DX_OK : (v == STATUS_TIMEOUT ? DX_ERR_TIMEOUT : (v == STATUS_NO_BLOCKS ? DX_ERR_BOUNDS : DX_ERR_CUDA));
+}
+
+int dx_kv_cache_step(dx_attn_t* h, int32_t* sequence_lengths, int64_t* block_pointers, int32_t num_requests,
+    int32_t max_blocks_per_sequence, const int64_t* free_blocks, int32_t n_free, int32_t* free_cursor, void* cuda_stream)
+{
+    if (!h || num_requests < 0 || max_blocks_per_sequence <= 0 || n_free < 0)
+        return DX_ERR_BAD_ARG;
+    if (num_requests == 0)
+        return DX_OK;
+    if (!sequence_lengths || !block_pointers || !free_cursor || (n_free > 0 && !free_blocks))
+        return DX_ERR_BAD_ARG;
+    if (((uintptr_t) sequence_lengths | (uintptr_t) free_cursor) & 3)
+        return DX_ERR_BAD_ARG;
+    if (((uintptr_t) block_pointers | (uintptr_t) free_blocks) & 7)
+        return DX_ERR_BAD_ARG;
+    int st = check_cuda(h, cudaSetDevice(h->cfg.device));
+    if (st != DX_OK)
+        return st;
+    KvStepArgs a{};
+    a.seq_len = sequence_lengths;
+    a.block_ptrs = block_pointers;
+    a.free_list = free_blocks;
+    a.free_cursor = free_cursor;
+    a.status = h->status_dev;
+    a.batch = num_requests;
+    a.max_blocks_per_seq = max_blocks_per_sequence;
+    a.tpb_log2 = h->tpb_log2;
+    a.n_free = n_free;
+    void* args[] = {&a};
+    st = check_cuda(h, cudaLaunchKernel(reinterpret_cast<const void*>(&kv_cache_step_kernel), dim3(1), dim3(1024), args, 0,
+                           reinterpret_cast<cudaStream_t>(cuda_stream)));
+    if (st == DX_OK)
+        h->launches.fetch_add(1);
+    return st;
 }
 
 size_t dx_attn_static_scratch_bytes(void)

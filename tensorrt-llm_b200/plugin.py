@@ -82,7 +82,7 @@ class _GenParams(ctypes.Structure):
 
 EXPORTED_SYMBOLS = [
     "dx_abi_version", "dx_strerror", "dx_attn_create", "dx_attn_destroy", "dx_attn_workspace_size",
-    "dx_attn_enqueue_generation", "dx_attn_enqueue_generation_host", "dx_attn_host_sync", "dx_attn_validate", "dx_attn_plan",
+    "dx_attn_enqueue_generation", "dx_attn_enqueue_generation_host", "dx_attn_host_sync", "dx_kv_cache_step", "dx_attn_validate", "dx_attn_plan",
     "dx_attn_device_status", "dx_attn_last_cuda_error", "dx_attn_launch_count",
     "dx_attn_enqueue_generation_static_scratch", "dx_attn_static_scratch_bytes", "dx_attn_append_context",
 ]
@@ -117,6 +117,9 @@ def load_library() -> ctypes.CDLL:
     lib.dx_attn_enqueue_generation_host.restype = ctypes.c_int
     lib.dx_attn_enqueue_generation_host.argtypes = [ctypes.c_void_p, ctypes.POINTER(_GenParams), ctypes.c_void_p,
                                                     ctypes.c_int32]
+    lib.dx_kv_cache_step.restype = ctypes.c_int
+    lib.dx_kv_cache_step.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
+                                     ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
     lib.dx_attn_host_sync.restype = ctypes.c_int
     lib.dx_attn_host_sync.argtypes = [ctypes.c_void_p]
     lib.dx_attn_enqueue_generation_static_scratch.restype = ctypes.c_int
@@ -361,6 +364,24 @@ class GPTAttentionPlugin:
                 if st != DX_OK:
                     raise DecodeAttnError(st, "dx_attn_enqueue_generation")
         return call
+
+    def kv_cache_step(self, sequence_length: torch.Tensor, kv_cache_block_pointers: torch.Tensor,
+                      free_blocks: torch.Tensor, free_cursor: torch.Tensor,
+                      stream: Optional[torch.cuda.Stream] = None) -> None:
+        """Device-resident KVCacheManager.step: sequence_length (int32 [B], device) += 1 in place; sequences whose
+        new token starts a block take the next (K pointer, V pointer) row of free_blocks (int64 [n, 2], device)
+        into kv_cache_block_pointers (int64 [B, 2, M], device) in place; free_cursor (int32 [1], device)
+        advances.  Asynchronous; capturable in a CUDA graph."""
+        for t in (sequence_length, kv_cache_block_pointers, free_blocks, free_cursor):
+            if not t.is_cuda or not t.is_contiguous():
+                raise DecodeAttnError(DX_ERR_BAD_ARG, "kv_cache_step needs contiguous device tensors")
+        s = stream if stream is not None else torch.cuda.current_stream(sequence_length.device)
+        st = self.lib.dx_kv_cache_step(self._h, sequence_length.data_ptr(), kv_cache_block_pointers.data_ptr(),
+                                       sequence_length.numel(), kv_cache_block_pointers.shape[-1],
+                                       free_blocks.data_ptr(), free_blocks.shape[0], free_cursor.data_ptr(),
+                                       ctypes.c_void_p(s.cuda_stream))
+        if st != DX_OK:
+            raise DecodeAttnError(st, "dx_kv_cache_step")
 
     def host_sync(self) -> None:
         """Waits until the outputs of all host-buffer calls made so far are in host memory."""
