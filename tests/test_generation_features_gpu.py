@@ -218,3 +218,75 @@ def test_oracle_matches_reference_kernel_features(pkg, name):
     err = (out - ref).abs()
     print(name, "reference-kernel deviation from the oracle: max", err.max().item(), "mean", err.mean().item())
     assert err.max().item() < tol and err.mean().item() < tol / 10
+
+
+def test_beams_with_bias_and_rotary_embedding(pkg):
+    """The in-step pre-processing (bias add, GPT-NeoX rotary embedding) in front of the feature path:
+    the rotated k of every beam is what gets stored, and the indirection table still picks the beams."""
+    P = pkg.plugin
+    c = Case((8, 2), 128, torch.bfloat16, "int8", 64, 2, beam=2, seed=11)
+    w_cpu, ex = _build(pkg, c)
+    cfg = w_cpu.cfg
+    rope = dict(position_embedding_type=2, rotary_embedding_dim=128, rotary_embedding_base=10000.0)
+    g = torch.Generator().manual_seed(5)
+    bias = (0.1 * torch.randn((cfg.num_heads + 2 * cfg.num_kv_heads) * cfg.head_size, generator=g)).to(cfg.dtype)
+    qkv_pre = oracle.apply_bias_rope(w_cpu.qkv, w_cpu.sequence_length, num_heads=cfg.num_heads,
+                                     num_kv_heads=cfg.num_kv_heads, head_size=cfg.head_size, qkv_bias=bias, **rope)
+    ref, pool_ref = _oracle(dataclasses.replace(w_cpu, qkv=qkv_pre), ex)
+    w = pkg.workloads.to_device(w_cpu, "cuda:0")
+    plugin = P.GPTAttentionPlugin(num_heads=cfg.num_heads, num_kv_heads=cfg.num_kv_heads, head_size=cfg.head_size,
+                                  kv_cache_quant_mode=cfg.quant_mode, tokens_per_block=cfg.tokens_per_block,
+                                  multi_block_mode=True, type_id=cfg.dtype, qkv_bias=True, **rope)
+    try:
+        out = plugin.enqueue_generation(
+            w.qkv, w.sequence_length, w.host_past_key_value_lengths, w.kv_cache_block_pointers,
+            w.kv_orig_quant_scale, w.kv_quant_orig_scale, max_attention_window=ex["max_attention_window"],
+            cache_indirection=ex["cache_indirection"].cuda(), beam_width=2,
+            context_lengths=ex["context_lengths"].cuda(), qkv_bias=bias.cuda())
+        torch.cuda.synchronize()
+        assert plugin.device_status() == 0
+        # the rotation is fp32 cos / sin / pow: allow the odd one-ulp difference in the stored bytes
+        same = (w.pool.cpu() == pool_ref).double().mean().item()
+        assert same > 0.9999, same
+        err = (out.float().cpu() - ref).abs()
+        assert err.max().item() < MAX_ABS_TOL and err.mean().item() < MEAN_ABS_TOL
+    finally:
+        plugin.close()
+
+
+def test_report_feature_path_time(pkg):
+    """Times the feature path on a beam-search batch of c4's shape (recorded in gpurun_out/feature_path.jsonl)."""
+    import json
+    import os
+    c = Case((64, 8), 128, torch.bfloat16, "fp8", 64, 16, beam=4, past_lo=2048, past_hi=4096, seed=3)
+    w_cpu, ex = _build(pkg, c)
+    w = pkg.workloads.to_device(w_cpu, "cuda:0")
+    plugin = _plugin(pkg, c)
+    try:
+        ci, cl = ex["cache_indirection"].cuda(), ex["context_lengths"].cuda()
+        out = torch.empty(w.cfg.batch, 64 * 128, dtype=torch.bfloat16, device="cuda:0")
+
+        def step():
+            plugin.enqueue_generation(w.qkv, w.sequence_length, w.host_past_key_value_lengths,
+                                      w.kv_cache_block_pointers, w.kv_orig_quant_scale, w.kv_quant_orig_scale, out=out,
+                                      max_attention_window=ex["max_attention_window"], cache_indirection=ci,
+                                      beam_width=4, context_lengths=cl)
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(10):
+            step()
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) / 10 * 1e3
+        kv = float((w_cpu.host_past_key_value_lengths.double().sum()) * 8 * 128 * 2)
+        rec = {"case": "beam 4 x 16 requests, 64 q / 8 kv heads, Dh 128, FP8, past 2048-4096", "us": us,
+               "unique_kv_GBps": kv / us / 1e3}
+        os.makedirs("gpurun_out", exist_ok=True)
+        with open("gpurun_out/feature_path.jsonl", "a") as f:
+            f.write(json.dumps(rec) + "\n")
+        print(rec)
+    finally:
+        plugin.close()
