@@ -70,6 +70,7 @@ struct dx_attn
     bool tok = false;        // token-major tcgen05 kernel usable for this configuration
     GeneralKernels k_general{}; // beams / cyclic window / sinks / ALiBi
     int force_chunk = 0;     // > 0: partition bound forced (tuning)
+    double wave_slack_from = 2.0; // waves beyond which 5 % of a wave of extra CTAs is not counted as a further wave
     bool prep = false; // bias / rotary embedding configured: QKV is pre-processed into the workspace
     int32_t* status_dev = nullptr;
     int last_cuda_error = 0;
@@ -167,7 +168,10 @@ Plan make_plan(const dx_attn* h, int batch, int max_past_len, const int32_t* hos
             for (int i = 0; i < batch; ++i)
                 cnt += parts_of(host_past ? (long) host_past[i] + 1 : max_total, t);
             cnt *= rows_per_seq;
-            const double waves = std::max(1.0, std::ceil((double) cnt / (double) slots - 0.05));
+            // a few CTAs over a whole number of waves ride along with the ragged finish of many waves, but cost a
+            // whole extra round when there are only one or two
+            const double fill = (double) cnt / (double) slots;
+            const double waves = std::max(1.0, std::ceil(fill - (fill > h->wave_slack_from ? 0.05 : 0.0)));
             const double cost = waves * fixed + 0.5 * (double) std::min(t, max_total);
             const bool allowed = t == t_max || cnt <= (long) h->waves * slots; // keeps workspace_bound() valid
             if (allowed && cost < best)
@@ -487,6 +491,8 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
         h->fixed_cost_tokens = std::max(0, atoi(w));
     if (const char* w = getenv("DX_ATTN_FORCE_CHUNK"))
         h->force_chunk = atoi(w);
+    if (const char* w = getenv("DX_ATTN_WAVE_SLACK_FROM"))
+        h->wave_slack_from = atof(w);
 
     int st = check_cuda(h, cudaSetDevice(c.device));
     if (st == DX_OK)
