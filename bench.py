@@ -219,7 +219,7 @@ def run_own_arm(args):
     wsize = plugin.get_workspace_size(cfg.batch, max_past)
     workspace = torch.empty(max(wsize, 1), dtype=torch.uint8, device=dev) if wsize else None
     out = torch.empty(cfg.batch, cfg.num_heads * cfg.head_size, dtype=cfg.dtype, device=dev)
-    plan = plugin.plan(cfg.batch, max_past)
+    plan = plugin.plan(cfg.batch, max_past, w0.host_past_key_value_lengths)
     stream = torch.cuda.current_stream(dev)
 
     # one pre-marshalled C call per replica: the timed loop does nothing but the C-ABI call

@@ -239,6 +239,10 @@ int dx_attn_validate(const dx_attn_t* handle, const int64_t* host_block_pointers
  * cpp/tensorrt_llm/kernels/decoderMaskedMultiheadAttention/decoderMaskedMultiheadAttentionLaunch.h:94-143). */
 int dx_attn_plan(const dx_attn_t* handle, int32_t batch, int32_t max_past_len, int32_t* num_partitions,
     int32_t* tokens_per_partition, int32_t* kernel_kind);
+/* The same for a given vector of host past lengths: exactly what dx_attn_enqueue_generation plans when it is
+ * passed host_past_key_value_lengths (dx_attn_plan assumes every sequence has max_past_len tokens). */
+int dx_attn_plan_lengths(const dx_attn_t* handle, const int32_t* host_past_key_value_lengths, int32_t batch,
+    int32_t* num_partitions, int32_t* tokens_per_partition, int32_t* kernel_kind);
 
 /* Reads (synchronously) and clears the device status word: DX_OK or DX_ERR_TIMEOUT. */
 int dx_attn_device_status(dx_attn_t* handle);

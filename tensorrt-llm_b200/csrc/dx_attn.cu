@@ -594,6 +594,28 @@ int dx_attn_plan(const dx_attn_t* h, int32_t batch, int32_t max_past_len, int32_
     return DX_OK;
 }
 
+int dx_attn_plan_lengths(const dx_attn_t* h, const int32_t* host_past_key_value_lengths, int32_t batch,
+    int32_t* num_partitions, int32_t* tokens_per_partition, int32_t* kernel_kind)
+{
+    if (!h || batch <= 0 || !host_past_key_value_lengths)
+        return DX_ERR_BAD_ARG;
+    int max_past = 0;
+    for (int i = 0; i < batch; ++i)
+    {
+        if (host_past_key_value_lengths[i] < 0)
+            return DX_ERR_BAD_ARG;
+        max_past = std::max(max_past, host_past_key_value_lengths[i]);
+    }
+    const Plan p = make_plan(h, batch, max_past, host_past_key_value_lengths);
+    if (num_partitions)
+        *num_partitions = p.nsplit;
+    if (tokens_per_partition)
+        *tokens_per_partition = p.chunk_tokens;
+    if (kernel_kind)
+        *kernel_kind = p.kind;
+    return DX_OK;
+}
+
 int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* params, void* cuda_stream)
 {
     dx_attn_generation_params p;

@@ -82,7 +82,7 @@ class _GenParams(ctypes.Structure):
 
 EXPORTED_SYMBOLS = [
     "dx_abi_version", "dx_strerror", "dx_attn_create", "dx_attn_destroy", "dx_attn_workspace_size",
-    "dx_attn_enqueue_generation", "dx_attn_enqueue_generation_host", "dx_attn_host_sync", "dx_kv_cache_step", "dx_attn_validate", "dx_attn_plan",
+    "dx_attn_enqueue_generation", "dx_attn_enqueue_generation_host", "dx_attn_host_sync", "dx_kv_cache_step", "dx_attn_validate", "dx_attn_plan", "dx_attn_plan_lengths",
     "dx_attn_device_status", "dx_attn_last_cuda_error", "dx_attn_launch_count",
     "dx_attn_enqueue_generation_static_scratch", "dx_attn_static_scratch_bytes", "dx_attn_append_context",
 ]
@@ -133,6 +133,10 @@ def load_library() -> ctypes.CDLL:
     lib.dx_attn_validate.restype = ctypes.c_int
     lib.dx_attn_validate.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
                                      ctypes.c_int32, ctypes.c_void_p, ctypes.c_size_t]
+    lib.dx_attn_plan_lengths.restype = ctypes.c_int
+    lib.dx_attn_plan_lengths.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
+                                         ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32),
+                                         ctypes.POINTER(ctypes.c_int32)]
     lib.dx_attn_plan.restype = ctypes.c_int
     lib.dx_attn_plan.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(ctypes.c_int32),
                                  ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]
@@ -203,13 +207,21 @@ class GPTAttentionPlugin:
     def get_workspace_size(self, batch: int, max_past_len: int) -> int:
         return int(self.lib.dx_attn_workspace_size(self._h, batch, max_past_len))
 
-    def plan(self, batch: int, max_past_len: int):
+    def plan(self, batch: int, max_past_len: int, host_past_key_value_lengths: Optional[torch.Tensor] = None):
+        """Split-K plan of the next enqueue: for the given host lengths when passed (what the enqueue itself
+        plans), else for a batch in which every sequence has max_past_len tokens."""
         n, c, k = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_int32()
-        st = self.lib.dx_attn_plan(self._h, batch, max_past_len, ctypes.byref(n), ctypes.byref(c), ctypes.byref(k))
+        if host_past_key_value_lengths is not None:
+            hp = host_past_key_value_lengths.to(torch.int32).contiguous().cpu()
+            st = self.lib.dx_attn_plan_lengths(self._h, ctypes.c_void_p(hp.data_ptr()), hp.numel(), ctypes.byref(n),
+                                               ctypes.byref(c), ctypes.byref(k))
+        else:
+            st = self.lib.dx_attn_plan(self._h, batch, max_past_len, ctypes.byref(n), ctypes.byref(c), ctypes.byref(k))
         if st != DX_OK:
             raise DecodeAttnError(st, "dx_attn_plan")
         return {"num_partitions": n.value, "tokens_per_partition": c.value,
-                "kernel": {0: "mha_cuda_core", 1: "gqa_tensor_core", 2: "wide_group_tcgen05", 3: "token_major_tcgen05"}.get(k.value, "?")}
+                "kernel": {0: "mha_cuda_core", 1: "gqa_tensor_core", 2: "wide_group_tcgen05",
+                           3: "token_major_tcgen05"}.get(k.value, "?")}
 
     def launch_count(self) -> int:
         return int(self.lib.dx_attn_launch_count(self._h))
