@@ -49,13 +49,14 @@ def measured_peak_gbs():
 
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (gqa_decode_fp8_c4.md, gqa_decode_int8_c5.md, mha_int8_decode_c2.md,
-# wide_decode_fp8_c3.md, gqa_decode_fp8_c4_tp8_shard.md).  Captured at full size: each fits the capture rule.
+# wide_decode_fp8_c3.md, gqa_decode_fp8_c4_tp8_shard.md, gqa16_decode_bf16_c4kv16.md).  Captured at full size: each fits the capture rule.
 PROFILED_TRAFFIC = {
     "c4_llama2_70b_gqa_fp8_tp1": 807324416,
     "c5_mixtral_long_gqa_int8_tp1": 378181120,
     "c2_llama2_7b_mha_int8_tp1": 817228800,
     "c3_falcon_7b_mqa_fp8_tp1": 20099584,
     "c4_llama2_70b_gqa_fp8_tp8": 103595008,
+    "c4kv16_llama2_70b_gqa_bf16_cache_tp1": 798231296,
 }
 
 
@@ -370,7 +371,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--config", default="c4", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--config", default="c4", choices=["c1", "c2", "c3", "c4", "c5", "c4kv16"])
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--cpu-sample", type=int, default=32, help="sequences per CPU-oracle step")
     ap.add_argument("--no-cpu-baseline", action="store_true")

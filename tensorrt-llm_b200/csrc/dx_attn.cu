@@ -119,7 +119,7 @@ Plan make_plan(const dx_attn* h, int batch, int max_past_len, const int32_t* hos
 {
     Plan p;
     const dx_attn_config& c = h->cfg;
-    const bool grouped = h->group > 1 && h->cache_kind != CACHE_T && c.tokens_per_block >= 32;
+    const bool grouped = h->group > 1 && c.tokens_per_block >= (h->cache_kind == CACHE_T ? 16 : 32) && h->k_gqa[0].fn;
     p.kind = grouped ? KIND_GQA : KIND_MHA;
     int resident = 2, rows_per_seq = c.num_heads;
     if (grouped && h->wide)
@@ -506,7 +506,8 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
         h->k_merge = merge_kernel_info(c.type_id, c.head_size);
         h->k_append = append_kernel_info(c.type_id, h->cache_kind, c.head_size);
         h->k_general = general_kernel_info(c.type_id, h->cache_kind, c.head_size);
-        if (h->cache_kind != CACHE_T)
+        const char* g16 = getenv("DX_ATTN_GQA16"); // "0": grouped heads over a 16-bit cache stay on the per-head kernel
+        if (h->cache_kind != CACHE_T || !g16 || atoi(g16) != 0)
         {
             for (int h16 = 0; h16 < 2; ++h16)
                 h->k_gqa[h16] = gqa_kernel_info(c.type_id, h->cache_kind, c.head_size, h16 != 0);

@@ -1,0 +1,396 @@
+// Grouped-head (GQA / MQA) decode attention over a 16-bit (fp16 / bf16) paged KV cache on the tensor cores.
+//
+// One CTA per (split-K partition, kv head x 16-head slice of its q group, sequence).  The q heads that share
+// the kv head are the M rows of S = Q K^T and of O = P V (mma.sync.m16n8k16, fp32 accumulation), so every cache
+// byte is fetched from HBM once for the whole group instead of once per q head.  Cache rows are used as stored:
+// K rows are the "col" B operand of Q K^T (ldmatrix), V rows the B operand of P V (ldmatrix.trans); the S
+// accumulators of two 8-token tiles are exactly the A fragment of P for a 16-token k-step.
+//
+// Each of the 4 warps owns every 4th 16-token group of the partition and runs its own online softmax; groups are
+// staged through a warp-private 3-stage ring filled with 16-byte cp.async copies (16-byte chunks XOR-swizzled
+// with the row number so that both ldmatrix patterns are bank-conflict free) whose completion is tracked by
+// mbarriers (cp.async.mbarrier.arrive.noinc).  Every wait is bounded.
+//
+// Replaces, for an unquantised cache, the XQA kernels (binary-only in the reference, dispatched from
+//   cpp/tensorrt_llm/kernels/decoderMaskedMultiheadAttention/decoderXQAImplPrecompiled.cpp:263-374)
+// and the MMHA kernel for grouped heads (decoderMaskedMultiheadAttentionTemplate.h:1303).
+#pragma once
+
+#include <type_traits>
+
+#include "dx_common.cuh"
+
+namespace dx
+{
+
+template <int DH>
+struct Gqa16Traits
+{
+    static constexpr int TG = 16;                 // tokens per stage (per warp)
+    static constexpr int ROW = DH * 2;            // bytes of a token row
+    static constexpr int CPR = ROW / 16;          // 16-byte chunks per row
+    static constexpr int SLAB = TG * ROW;         // bytes of K (or V) per stage
+    static constexpr int STAGE_BYTES = 2 * SLAB;
+    static constexpr int STAGES = 3;
+    static constexpr int NWARPS = 4;
+    static constexpr int NCP = SLAB / 512;        // 16-byte copies per lane and slab
+    static constexpr int RING_BYTES = NWARPS * STAGES * STAGE_BYTES;
+    static constexpr int MERGE_BYTES = NWARPS * (16 * DH + 32) * 4;
+    static constexpr int SMEM_BYTES = (RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES) + NWARPS * STAGES * 8 + 16;
+    static constexpr int MIN_BLOCKS = 2;
+};
+
+// Byte offset of 16-byte chunk `chunk` of row `row` inside a slab (chunks swizzled with the row number).
+template <int DH>
+__device__ __forceinline__ uint32_t sw16(uint32_t row, uint32_t chunk)
+{
+    return row * (uint32_t) (DH * 2) + ((chunk ^ (row & 7u)) << 4);
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+template <typename T>
+__device__ __forceinline__ void mma_16bit(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    if constexpr (std::is_same<T, __half>::value)
+    {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+    else
+    {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+}
+
+template <typename T, int DH>
+__global__ void __launch_bounds__(128, Gqa16Traits<DH>::MIN_BLOCKS) gqa16_decode_kernel(const AttnArgs a, const int hgroups)
+{
+    using Tr = Gqa16Traits<DH>;
+    constexpr int TG = Tr::TG, ROW = Tr::ROW, CPR = Tr::CPR, SLAB = Tr::SLAB, STAGES = Tr::STAGES;
+    constexpr int NWARPS = Tr::NWARPS, NCP = Tr::NCP;
+    constexpr int KSTEPS = DH / 16; // k-steps of Q K^T
+    constexpr int NT = DH / 8;      // n-tiles (8 channels) of O
+
+    const int chunk = blockIdx.x;
+    const int hk = blockIdx.y / hgroups, hg = blockIdx.y % hgroups;
+    const int b = blockIdx.z;
+    const int total = a.seq_len[b];
+    int chunk_start, ctoks, nparts;
+    partition_of(total, a.chunk_tokens, chunk, chunk_start, ctoks, nparts);
+    if (chunk >= nparts)
+        return; // ragged batch: this sequence uses fewer partitions
+    const int n_groups = (ctoks + TG - 1) / TG;
+    const int new_pos = total - 1;
+
+    griddep_launch_dependents(); // the merge kernel may be scheduled; it waits for this grid to finish
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int G = a.num_heads / a.num_kv_heads;
+    const int nh = min(16, G - hg * 16); // q heads handled by this CTA
+    const int head0 = hk * G + hg * 16;  // first of them
+    const int tpb_log2 = a.tpb_log2, tpb_mask = (1 << tpb_log2) - 1;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    constexpr int BAR_OFF = (Tr::RING_BYTES > Tr::MERGE_BYTES ? Tr::RING_BYTES : Tr::MERGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BAR_OFF) + warp * STAGES;
+    const uint32_t ring_u32 = smem_u32(smem) + warp * (STAGES * Tr::STAGE_BYTES);
+
+    if (lane == 0)
+    {
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s)
+            mbar_init(&bars[s], 32);
+        fence_mbar_init();
+    }
+    __syncwarp();
+
+    const int64_t* krow = a.block_ptrs + (int64_t) b * 2 * a.max_blocks_per_seq;
+    const int64_t* vrow = krow + a.max_blocks_per_seq;
+    const size_t head_off = (size_t) hk * ((size_t) ROW << tpb_log2);
+
+    // Copy j of a slab moves linear bytes [(lane + 32 j) * 16, +16) = chunk (lane + 32 j) % CPR of row (lane + 32 j) / CPR.
+    uint32_t cdst[NCP];
+#pragma unroll
+    for (int j = 0; j < NCP; ++j)
+        cdst[j] = sw16<DH>((uint32_t) (lane + 32 * j) / CPR, (uint32_t) (lane + 32 * j) % CPR);
+
+    // Every lane copies its share of the i-th group of this warp into ring stage i % STAGES.
+    auto issue = [&](int i)
+    {
+        const int gi = warp + NWARPS * i;
+        const int t0 = chunk_start + gi * TG;
+        const int rows = new_pos - t0; // rows already in the cache (>= TG for all but the last group)
+        const uint32_t kdst = ring_u32 + (i % STAGES) * Tr::STAGE_BYTES;
+        const size_t off = head_off + (size_t) (t0 & tpb_mask) * ROW + lane * 16;
+        const char* kb = reinterpret_cast<const char*>(__ldg(krow + (t0 >> tpb_log2))) + off;
+        const char* vb = reinterpret_cast<const char*>(__ldg(vrow + (t0 >> tpb_log2))) + off;
+        if (rows >= TG)
+        {
+#pragma unroll
+            for (int j = 0; j < NCP; ++j)
+            {
+                cp_async16_u32(kdst + cdst[j], kb + j * 512);
+                cp_async16_u32(kdst + SLAB + cdst[j], vb + j * 512);
+            }
+        }
+        else
+        {
+            // last group of the sequence: rows at and behind the new token are zero-filled
+            const int valid_bytes = rows > 0 ? rows * ROW : 0;
+#pragma unroll
+            for (int j = 0; j < NCP; ++j)
+            {
+                const bool ok = (lane + 32 * j) * 16 < valid_bytes;
+                cp_async16_zfill_u32(kdst + cdst[j], ok ? kb + j * 512 : kb, ok ? 16u : 0u);
+                cp_async16_zfill_u32(kdst + SLAB + cdst[j], ok ? vb + j * 512 : vb, ok ? 16u : 0u);
+            }
+        }
+        cp_async_mbar_arrive_noinc(&bars[i % STAGES]);
+    };
+
+    const int my_groups = (n_groups > warp) ? (n_groups - warp + NWARPS - 1) / NWARPS : 0;
+    for (int i = 0; i < min(STAGES, my_groups); ++i)
+        issue(i);
+
+    // ---- Q as A fragments: rows = heads g and g + 8, k-step j covers channels 16 j .. 16 j + 15 ----
+    const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
+    const T* qkv_b = reinterpret_cast<const T*>(a.qkv) + (size_t) b * qkv_stride;
+    uint32_t qa[KSTEPS][4];
+    {
+        const uint32_t* q0 = reinterpret_cast<const uint32_t*>(qkv_b + (size_t) (head0 + g) * DH);
+        const uint32_t* q1 = reinterpret_cast<const uint32_t*>(qkv_b + (size_t) (head0 + g + 8) * DH);
+        const bool v0 = g < nh, v1 = g + 8 < nh;
+#pragma unroll
+        for (int j = 0; j < KSTEPS; ++j)
+        {
+            qa[j][0] = v0 ? q0[8 * j + t] : 0u;     // (row g, channels 16 j + 2 t, + 1)
+            qa[j][1] = v1 ? q1[8 * j + t] : 0u;     // (row g + 8, same channels)
+            qa[j][2] = v0 ? q0[8 * j + 4 + t] : 0u; // (row g, channels 16 j + 8 + 2 t, + 1)
+            qa[j][3] = v1 ? q1[8 * j + 4 + t] : 0u;
+        }
+    }
+    const float sscale = a.softmax_scale_log2;
+
+    // Per-lane ldmatrix row addresses inside a slab.
+    //   K, 8-token tile nt, k-steps 2 jj and 2 jj + 1: matrix q = lane >> 3 is chunk 4 jj + q of rows 8 nt + (lane & 7)
+    //   V, channel tiles 2 a and 2 a + 1: matrices (tokens 0-7 | 8-15) x (chunk 2 a | 2 a + 1), transposed on load
+    const uint32_t k_row = lane & 7, k_q = lane >> 3;
+    const uint32_t v_row = (lane & 7) + 8 * ((lane >> 3) & 1), v_q = lane >> 4;
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float of[NT][4]; // O fragments: [channel tile][c0, c1: head g | c2, c3: head g + 8]
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            of[nt][c] = 0.f;
+
+    bool timed_out = false;
+    for (int i = 0; i < my_groups; ++i)
+    {
+        const int s = i % STAGES;
+        const uint32_t parity = (i / STAGES) & 1;
+        const uint32_t kbuf = ring_u32 + s * Tr::STAGE_BYTES;
+        const uint32_t vbuf = kbuf + SLAB;
+        if (!mbar_wait_bounded(&bars[s], parity, a.status))
+        {
+            timed_out = true;
+            break;
+        }
+        const int gi = warp + NWARPS * i;
+        const int t0 = chunk_start + gi * TG;
+        const int lim = total - t0; // valid tokens in this group if < TG
+        if (new_pos < t0 + TG)
+        {
+            // The group ends with the new token: put its k / v rows into the staged tile (rows behind it were
+            // zero-filled by the copies) and, from the first head slice only, append them to the paged cache.
+            const int r_new = new_pos - t0;
+            if (lane < CPR)
+            {
+                const T* kp = qkv_b + (size_t) (a.num_heads + hk) * DH + lane * 8;
+                const T* vp = qkv_b + (size_t) (a.num_heads + a.num_kv_heads + hk) * DH + lane * 8;
+                const uint4 kq = *reinterpret_cast<const uint4*>(kp);
+                const uint4 vq = *reinterpret_cast<const uint4*>(vp);
+                unsigned char* stage = smem + warp * (STAGES * Tr::STAGE_BYTES) + s * Tr::STAGE_BYTES;
+                const uint32_t lin = sw16<DH>((uint32_t) r_new, (uint32_t) lane);
+                *reinterpret_cast<uint4*>(stage + lin) = kq;
+                *reinterpret_cast<uint4*>(stage + SLAB + lin) = vq;
+                if (hg == 0)
+                {
+                    const size_t off = head_off + (size_t) (new_pos & tpb_mask) * ROW + lane * 16;
+                    char* kb = reinterpret_cast<char*>(__ldg(krow + (new_pos >> tpb_log2))) + off;
+                    char* vb = reinterpret_cast<char*>(__ldg(vrow + (new_pos >> tpb_log2))) + off;
+                    *reinterpret_cast<uint4*>(kb) = kq;
+                    *reinterpret_cast<uint4*>(vb) = vq;
+                }
+            }
+            __syncwarp();
+        }
+
+        // ---- S = Q K^T: 16 head rows x 16 tokens (two 8-token tiles) ----
+        float sacc[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                sacc[nt][c] = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+        {
+#pragma unroll
+            for (int jj = 0; jj < KSTEPS / 2; ++jj)
+            {
+                uint32_t kf[4];
+                ldmatrix_x4(kf, kbuf + sw16<DH>(8 * nt + k_row, 4 * jj + k_q));
+                mma_16bit<T>(sacc[nt], qa[2 * jj], kf[0], kf[1]);
+                mma_16bit<T>(sacc[nt], qa[2 * jj + 1], kf[2], kf[3]);
+            }
+        }
+
+        // ---- online softmax over the 16 tokens: thread holds tokens 8 nt + 2 t, + 1 of head rows g and g + 8 ----
+        float p[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                p[nt][c] = sacc[nt][c] * sscale;
+        if (lim < TG)
+        {
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    if (8 * nt + 2 * t + (c & 1) >= lim)
+                        p[nt][c] = -INFINITY;
+        }
+        float alpha[2];
+        bool changed = false;
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+        {
+            float mx = fmaxf(fmaxf(p[0][2 * r], p[0][2 * r + 1]), fmaxf(p[1][2 * r], p[1][2 * r + 1]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m[r], mx);
+            alpha[r] = fast_exp2(m[r] - m_new);
+            changed |= m_new != m[r];
+            m[r] = m_new;
+            l[r] *= alpha[r];
+        }
+        // P as the A fragment of the 16-token k-step: a0 / a1 from tile 0 (rows g / g + 8), a2 / a3 from tile 1
+        uint32_t pa[4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+            {
+                const float p0 = fast_exp2(p[nt][2 * r] - m[r]), p1 = fast_exp2(p[nt][2 * r + 1] - m[r]);
+                l[r] += p0 + p1;
+                pa[2 * nt + r] = TypeOps<T>::pack2(p0, p1);
+            }
+        // ---- rescale the running O when a row maximum moved ----
+        if (__any_sync(0xffffffffu, changed))
+        {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+            {
+                of[nt][0] *= alpha[0];
+                of[nt][1] *= alpha[0];
+                of[nt][2] *= alpha[1];
+                of[nt][3] *= alpha[1];
+            }
+        }
+        // ---- O += P V ----
+#pragma unroll
+        for (int av = 0; av < NT / 2; ++av)
+        {
+            uint32_t vf[4];
+            ldmatrix_x4_trans(vf, vbuf + sw16<DH>(v_row, 2 * av + v_q));
+            mma_16bit<T>(of[2 * av], pa, vf[0], vf[1]);
+            mma_16bit<T>(of[2 * av + 1], pa, vf[2], vf[3]);
+        }
+
+        __syncwarp(); // every lane is done reading this stage
+        if (i + STAGES < my_groups)
+            issue(i + STAGES);
+    }
+
+    if (timed_out && lane == 0)
+        atomicExch(a.status, STATUS_TIMEOUT);
+
+    // ---- per-warp results -> shared memory, then combine the 4 warps ----
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+    {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncthreads(); // all warps have drained their rings; the ring memory is reused below
+    float* mo = reinterpret_cast<float*>(smem) + warp * (16 * DH + 32);
+    float* mm = mo + 16 * DH; // m[16], then l[16]
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            mo[(g + 8 * (c >> 1)) * DH + 8 * nt + 2 * t + (c & 1)] = of[nt][c];
+    if (t == 0)
+    {
+        mm[g] = m[0];
+        mm[8 + g] = m[1];
+        mm[16 + g] = l[0];
+        mm[16 + 8 + g] = l[1];
+    }
+    __syncthreads();
+
+    const float* base = reinterpret_cast<const float*>(smem);
+    for (int idx = threadIdx.x; idx < nh * DH; idx += blockDim.x)
+    {
+        const int head = idx / DH, dh = idx % DH;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w)
+            M = fmaxf(M, base[w * (16 * DH + 32) + 16 * DH + head]);
+        float L = 0.f, o = 0.f;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w)
+        {
+            const float* wb = base + w * (16 * DH + 32);
+            const float mw = wb[16 * DH + head];
+            const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
+            L = fmaf(wb[16 * DH + 16 + head], f, L);
+            o = fmaf(wb[head * DH + dh], f, o);
+        }
+        const size_t row = (size_t) b * a.num_heads + head0 + head;
+        if (a.nsplit == 1)
+        {
+            reinterpret_cast<T*>(a.out)[row * DH + dh] = TypeOps<T>::from_float(o / L);
+        }
+        else
+        {
+            a.part_o[(row * a.nsplit + chunk) * DH + dh] = o;
+            if (dh == 0)
+                a.part_ml[row * a.nsplit + chunk] = make_float2(M, L);
+        }
+    }
+}
+
+} // namespace dx

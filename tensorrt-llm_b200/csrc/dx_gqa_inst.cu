@@ -1,6 +1,7 @@
 // Instantiations of the tensor-core grouped-head decode kernel.
 #include <type_traits>
 
+#include "dx_gqa16_kernel.cuh"
 #include "dx_gqa_kernel.cuh"
 #include "dx_launch.h"
 
@@ -15,9 +16,22 @@ static KernelInfo mk()
     return k;
 }
 
+// 16-bit cache: one kernel for any group size up to 16 heads per CTA
+template <typename T, int DH>
+static KernelInfo mk16()
+{
+    KernelInfo k;
+    k.fn = reinterpret_cast<const void*>(&gqa16_decode_kernel<T, DH>);
+    k.smem = Gqa16Traits<DH>::SMEM_BYTES;
+    k.resident = Gqa16Traits<DH>::MIN_BLOCKS;
+    return k;
+}
+
 template <typename T, bool H16>
 static KernelInfo by_cache_dh(int cache, int dh)
 {
+    if (cache == CACHE_T)
+        return dh == 64 ? mk16<T, 64>() : (dh == 128 ? mk16<T, 128>() : KernelInfo{});
     if (dh == 64)
     {
         if (cache == CACHE_INT8) return mk<T, CACHE_INT8, 64, H16>();

@@ -59,6 +59,10 @@ CONFIGS: Dict[str, DecodeConfig] = {
                        "Llama-2-70B-shaped GQA (group 8), FP8 paged cache, ragged"),
     "c5": DecodeConfig("c5_mixtral_long_gqa_int8", 8, 32, 8, 128, torch.bfloat16, "int8", 128, 16384, 32768, True, 1005,
                        "Mixtral-8x7B-shaped long-context GQA (group 4), INT8 paged cache, split-K"),
+    # not one of the reference's benchmark configurations: c4's shape with an unquantised cache (half the batch,
+    # the same KV bytes), the case the 16-bit grouped-head kernel exists for
+    "c4kv16": DecodeConfig("c4kv16_llama2_70b_gqa_bf16_cache", 64, 64, 8, 128, torch.bfloat16, "none", 64, 2048, 4096,
+                           True, 1006, "Llama-2-70B-shaped GQA (group 8), bf16 paged cache, ragged"),
 }
 
 
