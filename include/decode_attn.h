@@ -240,7 +240,9 @@ int dx_attn_validate(const dx_attn_t* handle, const int64_t* host_block_pointers
 int dx_attn_plan(const dx_attn_t* handle, int32_t batch, int32_t max_past_len, int32_t* num_partitions,
     int32_t* tokens_per_partition, int32_t* kernel_kind);
 /* The same for a given vector of host past lengths: exactly what dx_attn_enqueue_generation plans when it is
- * passed host_past_key_value_lengths (dx_attn_plan assumes every sequence has max_past_len tokens). */
+ * passed host_past_key_value_lengths and enough workspace (dx_attn_plan assumes every sequence has max_past_len
+ * tokens).  A stream-K launch (equal ranges of the batch's tokens per CTA instead of per-sequence partitions) is
+ * reported as *num_partitions = -(number of CTAs), *tokens_per_partition = tokens per CTA. */
 int dx_attn_plan_lengths(const dx_attn_t* handle, const int32_t* host_past_key_value_lengths, int32_t batch,
     int32_t* num_partitions, int32_t* tokens_per_partition, int32_t* kernel_kind);
 

@@ -38,6 +38,7 @@ struct Plan
     int hgroups = 1;    // 16-head slices per kv head (GQA kernel)
     bool heads16 = false;
     int rows = 0;       // grid.y * grid.z
+    int resident = 2;   // CTAs per SM of the chosen kernel
     int nsplit = 1;     // grid.x
     int chunk_tokens = 0;
     size_t part_o_bytes = 0, part_ml_bytes = 0;
@@ -69,6 +70,13 @@ struct dx_attn
     bool wide = false;       // wide-group kernel usable for this configuration
     bool tok = false;        // token-major tcgen05 kernel usable for this configuration
     GeneralKernels k_general{}; // beams / cyclic window / sinks / ALiBi
+    const void* k_merge_sk = nullptr;
+    bool streamk = true;        // grouped-head kernels: equal ranges of token groups per CTA instead of per-row partitions
+    int sk_min_units = 48;      // stream-K only when a CTA's range is at least this many token groups: below, the
+                                // second prologue / epilogue of a CTA that straddles a row boundary costs more
+                                // than the even split wins (measured on the TP8 shards)
+    int sk_row_factor = 6;      // ... and only when the average row is at most this many ranges long
+    SkSchedule sk_zero{};       // third argument of classic launches of the grouped-head kernels
     int force_chunk = 0;     // > 0: partition bound forced (tuning)
     double wave_slack_from = 2.0; // waves beyond which 5 % of a wave of extra CTAs is not counted as a further wave
     bool prep = false; // bias / rotary embedding configured: QKV is pre-processed into the workspace
@@ -148,6 +156,7 @@ Plan make_plan(const dx_attn* h, int batch, int max_past_len, const int32_t* hos
         resident = 3;
     }
     p.rows = batch * rows_per_seq;
+    p.resident = resident;
     const long max_total = (long) max_past_len + 1;
     long target = (long) align_up((size_t) max_total, 128);
     if (c.multi_block_mode)
@@ -199,6 +208,49 @@ Plan make_plan(const dx_attn* h, int batch, int max_past_len, const int32_t* hos
     return p;
 }
 
+// Stream-K schedule (SkSchedule in dx_common.cuh) for a call planned on the grouped-head 8-bit kernel.  On
+// success the plan's slot count and partial sizes are those of the schedule.  False: keep the classic plan.
+bool build_streamk(const dx_attn* h, Plan& plan, const int32_t* host_past, int batch, SkSchedule& sk, int& ctas)
+{
+    const dx_attn_config& c = h->cfg;
+    if (!h->streamk || !c.multi_block_mode || plan.kind != KIND_GQA || h->cache_kind == CACHE_T || !host_past
+        || batch > DX_SK_MAX_SEQ || !h->k_merge_sk)
+        return false;
+    const uint32_t unit = 32;
+    const uint32_t Y = (uint32_t) (c.num_kv_heads * plan.hgroups);
+    uint64_t acc = 0;
+    uint32_t nmax = 1;
+    sk.prefix[0] = 0;
+    for (int i = 0; i < batch; ++i)
+    {
+        const uint32_t n = ((uint32_t) host_past[i] + 1 + unit - 1) / unit;
+        nmax = std::max(nmax, n);
+        acc += n;
+        sk.prefix[i + 1] = (uint32_t) acc;
+    }
+    const uint64_t total = acc * Y;
+    if (total >= (1ull << 31))
+        return false;
+    const uint64_t slots = (uint64_t) h->sm_count * plan.resident;
+    const uint64_t U = (total + slots - 1) / slots;
+    // Worth it when the ranges are long (see sk_min_units) and the rows are not many times longer than a range:
+    // few very long rows are cut evenly by the classic partitions already.
+    if (U < (uint64_t) h->sk_min_units || acc > (uint64_t) h->sk_row_factor * U * (uint64_t) batch)
+        return false;
+    const uint64_t pmax = (nmax - 1) / U + 2; // pieces of the longest row, at most
+    const size_t qrows = (size_t) batch * c.num_heads;
+    sk.units_per_cta = (uint32_t) U;
+    sk.total_units = (uint32_t) total;
+    sk.rows_per_seq = Y;
+    sk.nseq = (uint32_t) batch;
+    ctas = (int) ((total + U - 1) / U);
+    plan.nsplit = (int) pmax;
+    plan.chunk_tokens = (int) (U * unit);
+    plan.part_o_bytes = align_up(qrows * pmax * c.head_size * sizeof(float), 128);
+    plan.part_ml_bytes = align_up(qrows * pmax * sizeof(float2), 128);
+    return true;
+}
+
 // Upper bound of Plan::workspace() over every length vector with lengths <= max_past_len.
 size_t workspace_bound(const dx_attn* h, int batch, int max_past_len)
 {
@@ -212,8 +264,10 @@ size_t workspace_bound(const dx_attn* h, int batch, int max_past_len)
     const long t_min = std::max<long>(128, h->min_chunk);
     long nsplit = std::min(parts_of(max_total, t_min), std::max<long>(1, h->waves * h->sm_count * resident / rows_per_seq));
     nsplit = std::max<long>(nsplit, shape.nsplit);
-    if (nsplit <= 1)
+    if (nsplit <= 1 && shape.kind != KIND_GQA)
         return 0;
+    if (shape.kind == KIND_GQA)
+        nsplit += 2; // stream-K launches: a row of n groups cut by ranges of U groups has at most n / U + 2 pieces
     const size_t qrows = (size_t) batch * c.num_heads;
     return align_up(qrows * nsplit * c.head_size * sizeof(float), 128) + align_up(qrows * nsplit * sizeof(float2), 128);
 }
@@ -248,6 +302,21 @@ template <typename T, int DH>
 const void* merge_fn()
 {
     return reinterpret_cast<const void*>(&lse_merge_kernel<T, DH>);
+}
+
+template <typename T, int DH>
+const void* merge_sk_fn()
+{
+    return reinterpret_cast<const void*>(&lse_merge_sk_kernel<T, DH>);
+}
+
+const void* merge_sk_kernel(int dtype, int dh)
+{
+    if (dh == 64)
+        return dtype == 0 ? merge_sk_fn<__half, 64>() : merge_sk_fn<__nv_bfloat16, 64>();
+    if (dh == 128)
+        return dtype == 0 ? merge_sk_fn<__half, 128>() : merge_sk_fn<__nv_bfloat16, 128>();
+    return nullptr;
 }
 
 } // namespace
@@ -493,6 +562,12 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
         h->force_chunk = atoi(w);
     if (const char* w = getenv("DX_ATTN_WAVE_SLACK_FROM"))
         h->wave_slack_from = atof(w);
+    if (const char* w = getenv("DX_ATTN_STREAMK"))
+        h->streamk = atoi(w) != 0;
+    if (const char* w = getenv("DX_ATTN_SK_MIN_UNITS"))
+        h->sk_min_units = std::max(1, atoi(w));
+    if (const char* w = getenv("DX_ATTN_SK_ROW_FACTOR"))
+        h->sk_row_factor = std::max(1, atoi(w));
 
     int st = check_cuda(h, cudaSetDevice(c.device));
     if (st == DX_OK)
@@ -504,6 +579,7 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
     {
         h->k_mha = mha_kernel_info(c.type_id, h->cache_kind, c.head_size, c.tokens_per_block);
         h->k_merge = merge_kernel_info(c.type_id, c.head_size);
+        h->k_merge_sk = merge_sk_kernel(c.type_id, c.head_size);
         h->k_append = append_kernel_info(c.type_id, h->cache_kind, c.head_size);
         h->k_general = general_kernel_info(c.type_id, h->cache_kind, c.head_size);
         const char* g16 = getenv("DX_ATTN_GQA16"); // "0": grouped heads over a 16-bit cache stay on the per-head kernel
@@ -607,9 +683,12 @@ int dx_attn_plan_lengths(const dx_attn_t* h, const int32_t* host_past_key_value_
             return DX_ERR_BAD_ARG;
         max_past = std::max(max_past, host_past_key_value_lengths[i]);
     }
-    const Plan p = make_plan(h, batch, max_past, host_past_key_value_lengths);
+    Plan p = make_plan(h, batch, max_past, host_past_key_value_lengths);
+    SkSchedule sk;
+    int ctas = 0;
+    const bool streamk = build_streamk(h, p, host_past_key_value_lengths, batch, sk, ctas);
     if (num_partitions)
-        *num_partitions = p.nsplit;
+        *num_partitions = streamk ? -ctas : p.nsplit; // stream-K: minus the number of CTAs, each tokens_per_partition tokens
     if (tokens_per_partition)
         *tokens_per_partition = p.chunk_tokens;
     if (kernel_kind)
@@ -665,10 +744,19 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     if ((int64_t) max_past + 1 > (int64_t) p.max_blocks_per_sequence * c.tokens_per_block)
         return DX_ERR_BAD_ARG; // the table cannot hold that many tokens
 
-    const Plan plan = make_plan(h, p.num_requests, max_past, p.host_past_key_value_lengths);
+    Plan plan = make_plan(h, p.num_requests, max_past, p.host_past_key_value_lengths);
     if (plan.kind == KIND_MHA && c.tokens_per_block < 16)
         return DX_ERR_UNSUPPORTED;
     const size_t prep = prep_bytes(h, p.num_requests);
+
+    // Stream-K schedule for the 8-bit grouped-head kernel: equal ranges of 32-token groups per CTA, computed from
+    // the host lengths.  Used when the workspace given can hold one partial result per piece of a cut row.
+    SkSchedule sk;
+    int sk_ctas = 0;
+    const bool use_sk = build_streamk(h, plan, p.host_past_key_value_lengths, p.num_requests, sk, sk_ctas)
+        && p.workspace && !((uintptr_t) p.workspace & 127) && p.workspace_bytes >= prep + plan.workspace();
+    if (!use_sk)
+        plan = make_plan(h, p.num_requests, max_past, p.host_past_key_value_lengths);
     if (plan.nsplit > 1 || prep)
     {
         if (!p.workspace || ((uintptr_t) p.workspace & 127))
@@ -696,6 +784,7 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     a.chunk_tokens = plan.chunk_tokens;
     a.nsplit = plan.nsplit;
     a.softmax_scale_log2 = 1.4426950408889634f / (sqrtf((float) c.head_size) * c.q_scaling);
+    a.streamk = use_sk ? 1 : 0;
 
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
     int st = check_cuda(h, cudaSetDevice(c.device));
@@ -729,8 +818,8 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
         if (!k.fn)
             return DX_ERR_UNSUPPORTED;
         int hgroups = plan.hgroups;
-        void* args[] = {&a, &hgroups};
-        dim3 grid(plan.nsplit, c.num_kv_heads * plan.hgroups, p.num_requests);
+        void* args[] = {&a, &hgroups, use_sk ? &sk : &h->sk_zero}; // (the 16-bit kernel takes the first two)
+        const dim3 grid = use_sk ? dim3(sk_ctas) : dim3(plan.nsplit, c.num_kv_heads * plan.hgroups, p.num_requests);
         st = check_cuda(h, cudaLaunchKernel(k.fn, grid, dim3(128), args, (size_t) k.smem, stream));
     }
     else
@@ -745,7 +834,8 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
 
     if (plan.nsplit > 1)
     {
-        void* args[] = {&a};
+        int hgroups = plan.hgroups;
+        void* args[] = {&a, &hgroups, &sk}; // (the classic merge kernel takes the first)
         const int rows = p.num_requests * c.num_heads;
         // Programmatic dependent launch: the merge grid is scheduled while the attention grid drains and
         // blocks in griddepcontrol.wait until that grid has completed (hides the launch gap).
@@ -759,7 +849,7 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        st = check_cuda(h, cudaLaunchKernelExC(&cfg, h->k_merge.fn, args));
+        st = check_cuda(h, cudaLaunchKernelExC(&cfg, use_sk ? h->k_merge_sk : h->k_merge.fn, args));
         if (st != DX_OK)
             return st;
         h->launches.fetch_add(1);

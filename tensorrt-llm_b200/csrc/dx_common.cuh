@@ -36,8 +36,9 @@ struct AttnArgs
     int32_t max_blocks_per_seq;
     int32_t tpb_log2;
     int32_t chunk_tokens; // upper bound of tokens per split-K partition (multiple of 128), see partition_of()
-    int32_t nsplit;       // grid.x; 1 => kernels write the final output themselves
+    int32_t nsplit;       // grid.x; 1 => kernels write the final output themselves.  Stream-K: result slots per row
     float softmax_scale_log2; // log2(e) / (sqrt(Dh) * q_scaling)
+    int32_t streamk;          // 1: the CTAs walk equal ranges of the batch's token groups (SkSchedule), see below
 };
 
 // Arguments of the feature-complete path (beam search, cyclic window, sink tokens, ALiBi).
@@ -70,6 +71,95 @@ __host__ __device__ __forceinline__ int cyclic_slot(int tok, int sink, int cycli
 }
 
 static constexpr int32_t STATUS_TIMEOUT = 5;
+
+// ----------------------------------------------------------------------------------------------
+// Stream-K schedule of the grouped-head kernels.  The rows of the batch - (sequence b, kv-head slice y), y fastest -
+// are laid end to end in units of token groups (32 tokens for the 8-bit kernels, 16 for the 16-bit one); row (b, y)
+// has n_b = prefix[b+1] - prefix[b] groups and starts at unit rows_per_seq * prefix[b] + y * n_b.  CTA c owns units
+// [c * units_per_cta, (c+1) * units_per_cta): a few pieces of consecutive rows, every CTA the same amount of
+// streaming, whatever the mix of lengths.  A row cut into several pieces leaves one partial result per piece in
+// slot (c - first CTA of the row); a row inside one CTA is written out directly.  The lengths are the HOST lengths
+// the call was planned with; the kernels clamp every piece to the device length.
+// ----------------------------------------------------------------------------------------------
+static constexpr int DX_SK_MAX_SEQ = 1024;
+
+struct SkSchedule
+{
+    uint32_t units_per_cta;
+    uint32_t total_units;
+    uint32_t rows_per_seq;
+    uint32_t nseq;
+    uint32_t prefix[DX_SK_MAX_SEQ + 1];
+};
+
+struct SkCursor
+{
+    uint32_t u, u1;  // next unit, end of this CTA's range
+    uint32_t b, y;   // row the cursor is in
+    uint32_t g0, nb; // group inside the row, groups of the row
+};
+
+__device__ __forceinline__ bool sk_begin(const SkSchedule& sk, int cta, SkCursor& c)
+{
+    c.u = (uint32_t) cta * sk.units_per_cta;
+    if (c.u >= sk.total_units)
+        return false;
+    c.u1 = min(c.u + sk.units_per_cta, sk.total_units);
+    uint32_t lo = 0, hi = sk.nseq - 1;
+    while (lo < hi) // largest b whose first unit is <= u
+    {
+        const uint32_t mid = (lo + hi + 1) >> 1;
+        if (sk.rows_per_seq * sk.prefix[mid] <= c.u)
+            lo = mid;
+        else
+            hi = mid - 1;
+    }
+    c.b = lo;
+    c.nb = sk.prefix[lo + 1] - sk.prefix[lo];
+    const uint32_t rem = c.u - sk.rows_per_seq * sk.prefix[lo];
+    c.y = rem / c.nb;
+    c.g0 = rem - c.y * c.nb;
+    return true;
+}
+
+// The piece under the cursor: row (b, y), groups [g0, g0 + ng), result slot, and whether it is the whole row.
+__device__ __forceinline__ void sk_piece(
+    const SkSchedule& sk, const SkCursor& c, int& b, int& y, int& g0, int& ng, int& slot, bool& whole)
+{
+    b = (int) c.b, y = (int) c.y, g0 = (int) c.g0;
+    ng = (int) min(c.nb - c.g0, c.u1 - c.u);
+    const uint32_t row_start = sk.rows_per_seq * sk.prefix[c.b] + c.y * c.nb;
+    slot = (int) (blockIdx.x - row_start / sk.units_per_cta);
+    whole = c.g0 == 0 && (uint32_t) ng == c.nb;
+}
+
+// Moves the cursor behind the current piece; false when the CTA's range is used up.
+__device__ __forceinline__ bool sk_next(const SkSchedule& sk, SkCursor& c)
+{
+    const uint32_t ng = min(c.nb - c.g0, c.u1 - c.u);
+    c.u += ng;
+    c.g0 += ng;
+    if (c.g0 == c.nb)
+    {
+        c.g0 = 0;
+        if (++c.y == sk.rows_per_seq)
+        {
+            c.y = 0;
+            ++c.b;
+            if (c.u < c.u1)
+                c.nb = sk.prefix[c.b + 1] - sk.prefix[c.b];
+        }
+    }
+    return c.u < c.u1;
+}
+
+// Pieces row (b, y) was cut into (1: the kernel wrote the final output itself).
+__device__ __forceinline__ int sk_pieces_of_row(const SkSchedule& sk, int b, int y)
+{
+    const uint32_t nb = sk.prefix[b + 1] - sk.prefix[b];
+    const uint32_t row_start = sk.rows_per_seq * sk.prefix[b] + (uint32_t) y * nb;
+    return (int) ((row_start + nb - 1) / sk.units_per_cta - row_start / sk.units_per_cta) + 1;
+}
 
 // Split-K partitioning of one sequence: `total` tokens are cut into the fewest partitions of at
 // most `target` tokens, and those partitions are made equal (rounded up to 128 tokens) so that no

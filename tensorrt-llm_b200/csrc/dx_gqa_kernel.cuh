@@ -197,7 +197,7 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr)
 }
 
 template <typename T, int CACHE, int DH, bool H16>
-__global__ void __launch_bounds__(128, gqa_min_blocks<CACHE, DH, H16>()) gqa_decode_kernel(const AttnArgs a, const int hgroups)
+__global__ void __launch_bounds__(128, gqa_min_blocks<CACHE, DH, H16>()) gqa_decode_kernel(const AttnArgs a, const int hgroups, const __grid_constant__ SkSchedule sk)
 {
     static_assert(CACHE == CACHE_INT8 || CACHE == CACHE_FP8, "8-bit caches only");
     using Tr = GqaTraits<DH, gqa_min_blocks<CACHE, DH, H16>()>;
@@ -211,24 +211,28 @@ __global__ void __launch_bounds__(128, gqa_min_blocks<CACHE, DH, H16>()) gqa_dec
     constexpr int NCP = (DH == 128) ? 2 : 4; // distinct per-lane destination offsets of the copies
     using Acc = typename std::conditional<IS_FP8, float, int>::type;
 
-    const int chunk = blockIdx.x;
-    const int hk = blockIdx.y / hgroups, hg = blockIdx.y % hgroups;
-    const int b = blockIdx.z;
-    const int total = a.seq_len[b];
-    int chunk_start, ctoks, nparts;
-    partition_of(total, a.chunk_tokens, chunk, chunk_start, ctoks, nparts);
-    if (chunk >= nparts)
-        return; // ragged batch: this sequence uses fewer partitions
-    const int n_groups = (ctoks + TG - 1) / TG;
-    const int new_pos = total - 1;
-
-    griddep_launch_dependents(); // the merge kernel may be scheduled; it waits for this grid to finish
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int G = a.num_heads / a.num_kv_heads;
-    const int nh = min(16, G - hg * 16); // q heads handled by this CTA
-    const int head0 = hk * G + hg * 16;  // first of them
     const int tpb_log2 = a.tpb_log2, tpb_mask = (1 << tpb_log2) - 1;
+
+    // Work of this CTA.  Classic launch: one piece, the (partition, kv-head slice, sequence) of its grid
+    // position.  Stream-K launch (a.streamk): a contiguous range of 32-token groups of the whole batch
+    // (SkSchedule), i.e. a few pieces of consecutive rows, every CTA the same amount.
+    SkCursor cur;
+    if (a.streamk)
+    {
+        if (!sk_begin(sk, (int) blockIdx.x, cur))
+            return;
+    }
+    else
+    {
+        int cs, ct, np;
+        partition_of(a.seq_len[blockIdx.z], a.chunk_tokens, (int) blockIdx.x, cs, ct, np);
+        if ((int) blockIdx.x >= np)
+            return; // ragged batch: this sequence uses fewer partitions
+    }
+    griddep_launch_dependents(); // the merge kernel may be scheduled; it waits for this grid to finish
 
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int BAR_OFF = (Tr::RING_BYTES > Tr::MERGE_BYTES ? Tr::RING_BYTES : Tr::MERGE_BYTES);
@@ -244,522 +248,556 @@ __global__ void __launch_bounds__(128, gqa_min_blocks<CACHE, DH, H16>()) gqa_dec
     }
     __syncwarp();
 
-    const int64_t* krow = a.block_ptrs + (int64_t) b * 2 * a.max_blocks_per_seq;
-    const int64_t* vrow = krow + a.max_blocks_per_seq;
-    const size_t head_off = (size_t) hk * ((size_t) DH << tpb_log2);
-
-    // Per-lane constant destination offsets of the 16-byte copies (copy j of a slab moves linear
-    // bytes [(lane + 32 j) * 16, +16)).
-    uint32_t cdst[NCP];
-#pragma unroll
-    for (int j = 0; j < NCP; ++j)
-        cdst[j] = swz<DH>((uint32_t) (lane + 32 * j) * 16);
-
-    // Every lane copies its share of the i-th group of this warp into ring stage i % STAGES.
-    auto issue = [&](int i)
+    int ring_base = 0; // groups this warp has put through its ring so far (stage / phase bookkeeping across pieces)
+    for (;;)
     {
-        const int gi = warp + NWARPS * i;
-        const int t0 = chunk_start + gi * TG;
-        const int rows = new_pos - t0; // rows already in the cache (>= TG for all but the last group)
-        const uint32_t kdst = ring_u32 + (i % STAGES) * Tr::STAGE_BYTES;
-        const size_t off = head_off + (size_t) (t0 & tpb_mask) * DH + lane * 16;
-        const char* kb = reinterpret_cast<const char*>(__ldg(krow + (t0 >> tpb_log2))) + off;
-        const char* vb = reinterpret_cast<const char*>(__ldg(vrow + (t0 >> tpb_log2))) + off;
-        if (rows >= TG)
+        // ---- this piece: row (b, hk, hg), tokens [chunk_start, chunk_start + ctoks), result slot `chunk` ----
+        int b, hk, hg, chunk, chunk_start, ctoks;
+        bool final_out;
+        if (a.streamk)
         {
-#pragma unroll
-            for (int j = 0; j < SLAB / 512; ++j)
-            {
-                const uint32_t d = (DH == 128) ? cdst[j & 1] + (j >> 1) * 1024 : cdst[j];
-                cp_async16_u32(kdst + d, kb + j * 512);
-                cp_async16_u32(kdst + SLAB + d, vb + j * 512);
-            }
+            int y, g0, ng;
+            sk_piece(sk, cur, b, y, g0, ng, chunk, final_out);
+            hk = y / hgroups, hg = y % hgroups;
+            chunk_start = g0 * TG;
+            ctoks = ng * TG;
         }
         else
         {
-            // last group of the sequence: rows at and behind the new token are zero-filled
-            const int valid_bytes = rows > 0 ? rows * DH : 0;
-#pragma unroll
-            for (int j = 0; j < SLAB / 512; ++j)
-            {
-                const uint32_t d = (DH == 128) ? cdst[j & 1] + (j >> 1) * 1024 : cdst[j];
-                const bool ok = (lane + 32 * j) * 16 < valid_bytes;
-                cp_async16_zfill_u32(kdst + d, ok ? kb + j * 512 : kb, ok ? 16u : 0u);
-                cp_async16_zfill_u32(kdst + SLAB + d, ok ? vb + j * 512 : vb, ok ? 16u : 0u);
-            }
+            int np;
+            chunk = blockIdx.x, hk = blockIdx.y / hgroups, hg = blockIdx.y % hgroups, b = blockIdx.z;
+            partition_of(a.seq_len[b], a.chunk_tokens, chunk, chunk_start, ctoks, np);
+            final_out = a.nsplit == 1;
         }
-        cp_async_mbar_arrive_noinc(&bars[i % STAGES]);
-    };
+        const int total = a.seq_len[b];
+        ctoks = max(0, min(ctoks, total - chunk_start)); // the schedule counts host lengths; the device length decides
+        const int n_groups = (ctoks + TG - 1) / TG;
+        const int new_pos = total - 1;
+        const int nh = min(16, G - hg * 16); // q heads handled in this piece
+        const int head0 = hk * G + hg * 16;  // first of them
 
-    const int my_groups = (n_groups > warp) ? (n_groups - warp + NWARPS - 1) / NWARPS : 0;
-    for (int i = 0; i < min(STAGES, my_groups); ++i)
-        issue(i);
+        const int64_t* krow = a.block_ptrs + (int64_t) b * 2 * a.max_blocks_per_seq;
+        const int64_t* vrow = krow + a.max_blocks_per_seq;
+        const size_t head_off = (size_t) hk * ((size_t) DH << tpb_log2);
 
-    // ---- Q: load the head rows, scale each row into the 8-bit range, split into high and low
-    // parts and pack straight into A fragments.  The k index of every MMA is a fixed permutation
-    // of Dh chosen so that a K fragment is one (Dh 64) or two (Dh 128) 16-byte shared loads.
-    //   <= 8 heads : one fragment set, rows 0..7 = high parts, rows 8..15 = low parts of head g
-    //   16 heads   : two fragment sets (high, low), rows = heads g and g + 8 ----
-    const float deq = __ldg(a.scale_quant_orig);
-    const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
-    const T* qkv_b = reinterpret_cast<const T*>(a.qkv) + (size_t) b * qkv_stride;
-    // FP8 cache: Q stays 16-bit (f16 A fragments, one k16 step per 4 channels of a thread);
-    // INT8 cache: 8-bit high/low fragments as described above.
-    constexpr int KS16 = DH / 16;
-    uint32_t qa[IS_FP8 ? 1 : NR][IS_FP8 ? KS16 : KS][4];
-    float sfac[NR]; // accumulator -> score in log2 units, per head-row half
+        // Per-lane constant destination offsets of the 16-byte copies (copy j of a slab moves linear
+        // bytes [(lane + 32 j) * 16, +16)).
+        uint32_t cdst[NCP];
 #pragma unroll
-    for (int r = 0; r < NR; ++r)
-    {
-        float qv[QV];
-        const int hl = g + 8 * r; // head within this CTA
-        if (hl < nh)
+        for (int j = 0; j < NCP; ++j)
+            cdst[j] = swz<DH>((uint32_t) (lane + 32 * j) * 16);
+
+        // Every lane copies its share of the i-th group of this warp into ring stage (ring_base + i) % STAGES.
+        auto issue = [&](int i)
         {
-            const T* qp = qkv_b + (size_t) (head0 + hl) * DH + t * QV;
-#pragma unroll
-            for (int i = 0; i < QV; i += 8)
+            const int gi = warp + NWARPS * i;
+            const int t0 = chunk_start + gi * TG;
+            const int rows = new_pos - t0; // rows already in the cache (>= TG for all but the last group)
+            const uint32_t kdst = ring_u32 + ((ring_base + i) % STAGES) * Tr::STAGE_BYTES;
+            const size_t off = head_off + (size_t) (t0 & tpb_mask) * DH + lane * 16;
+            const char* kb = reinterpret_cast<const char*>(__ldg(krow + (t0 >> tpb_log2))) + off;
+            const char* vb = reinterpret_cast<const char*>(__ldg(vrow + (t0 >> tpb_log2))) + off;
+            if (rows >= TG)
             {
-                const uint4 raw = *reinterpret_cast<const uint4*>(qp + i);
-                const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int j = 0; j < SLAB / 512; ++j)
                 {
-                    const float2 v = TypeOps<T>::unpack2(w[j]);
-                    qv[i + 2 * j] = v.x;
-                    qv[i + 2 * j + 1] = v.y;
+                    const uint32_t d = (DH == 128) ? cdst[j & 1] + (j >> 1) * 1024 : cdst[j];
+                    cp_async16_u32(kdst + d, kb + j * 512);
+                    cp_async16_u32(kdst + SLAB + d, vb + j * 512);
                 }
             }
-        }
-        else
-        {
-#pragma unroll
-            for (int i = 0; i < QV; ++i)
-                qv[i] = 0.f;
-        }
-        float amax = 0.f;
-#pragma unroll
-        for (int i = 0; i < QV; ++i)
-            amax = fmaxf(amax, fabsf(qv[i]));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        float qmul, qinv;
-        if constexpr (IS_FP8)
-        {
-            // power-of-two scale that puts amax into [128, 256)
-            int e = 0;
-            if (amax > 0.f)
-                e = 7 - (int) (((__float_as_uint(amax) >> 23) & 0xff) - 127);
-            e = max(-100, min(100, e));
-            qmul = __uint_as_float((uint32_t) (e + 127) << 23);
-            qinv = __uint_as_float((uint32_t) (127 - e) << 23);
-        }
-        else
-        {
-            const float qs = amax > 0.f ? amax * (1.f / 127.f) : 1.f;
-            qmul = 1.f / qs;
-            qinv = qs * (1.f / kLoWeight);
-        }
-        sfac[r] = qinv * deq * a.softmax_scale_log2;
-        if constexpr (IS_FP8)
-        {
-            // k16 step j of this thread covers channels 4j .. 4j+3 of its QV-channel slice:
-            // (4j, 4j+1) -> k slots (2t, 2t+1), (4j+2, 4j+3) -> k slots (2t+8, 2t+9).
-#pragma unroll
-            for (int j = 0; j < KS16; ++j)
+            else
             {
-                qa[0][j][r] = pack_f16x2(qv[4 * j] * qmul, qv[4 * j + 1] * qmul);
-                qa[0][j][2 + r] = pack_f16x2(qv[4 * j + 2] * qmul, qv[4 * j + 3] * qmul);
-                if constexpr (!H16)
+                // last group of the sequence: rows at and behind the new token are zero-filled
+                const int valid_bytes = rows > 0 ? rows * DH : 0;
+#pragma unroll
+                for (int j = 0; j < SLAB / 512; ++j)
                 {
-                    qa[0][j][1] = 0u;
-                    qa[0][j][3] = 0u;
+                    const uint32_t d = (DH == 128) ? cdst[j & 1] + (j >> 1) * 1024 : cdst[j];
+                    const bool ok = (lane + 32 * j) * 16 < valid_bytes;
+                    cp_async16_zfill_u32(kdst + d, ok ? kb + j * 512 : kb, ok ? 16u : 0u);
+                    cp_async16_zfill_u32(kdst + SLAB + d, ok ? vb + j * 512 : vb, ok ? 16u : 0u);
                 }
             }
-        }
-        else
-        {
-#pragma unroll
-            for (int s = 0; s < KS; ++s)
-            {
-#pragma unroll
-                for (int half = 0; half < 2; ++half)
-                {
-                    // elements of this thread that feed the low-k (half 0) or high-k (half 1) registers of k-step s
-                    const int base = (DH == 128) ? (16 * half + 4 * s) : (8 * s + 4 * half);
-                    uint32_t whi, wlo;
-                    split4<CACHE>(qv[base] * qmul, qv[base + 1] * qmul, qv[base + 2] * qmul, qv[base + 3] * qmul, whi, wlo);
-                    if constexpr (H16)
-                    {
-                        qa[0][s][2 * half + r] = whi; // set 0 = high parts, register = row half r
-                        qa[1][s][2 * half + r] = wlo; // set 1 = low parts
-                    }
-                    else
-                    {
-                        qa[0][s][2 * half] = whi;     // rows 0..7
-                        qa[0][s][2 * half + 1] = wlo; // rows 8..15
-                    }
-                }
-            }
-        }
-    }
+            cp_async_mbar_arrive_noinc(&bars[(ring_base + i) % STAGES]);
+        };
 
-    // Per-thread shared-memory offsets of the fragment loads (inside a K / V slab).
-    uint32_t koff[4], voff[8];
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
-        koff[nt] = swz<DH>((uint32_t) sigma_row<DH>(nt, g) * DH + t * (DH / 4));
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-        voff[i] = swz<DH>((uint32_t) sigma_row<DH>(i >> 1, 2 * t + (i & 1)) * DH + g * (DH / 8));
+        const int my_groups = (n_groups > warp) ? (n_groups - warp + NWARPS - 1) / NWARPS : 0;
+        for (int i = 0; i < min(STAGES, my_groups); ++i)
+            issue(i);
 
-    float m[NR], l[NR];
-#pragma unroll
-    for (int r = 0; r < NR; ++r)
-        m[r] = -INFINITY, l[r] = 0.f;
-    float of[MT][NR][4]; // O^T fragments: [m-tile][head half][c0..c3]
-    int oi[IS_FP8 ? 1 : 2][IS_FP8 ? 1 : MT][NR][4]; // integer path: pending high / low sums
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
+        // ---- Q: load the head rows, scale each row into the 8-bit range, split into high and low
+        // parts and pack straight into A fragments.  The k index of every MMA is a fixed permutation
+        // of Dh chosen so that a K fragment is one (Dh 64) or two (Dh 128) 16-byte shared loads.
+        //   <= 8 heads : one fragment set, rows 0..7 = high parts, rows 8..15 = low parts of head g
+        //   16 heads   : two fragment sets (high, low), rows = heads g and g + 8 ----
+        const float deq = __ldg(a.scale_quant_orig);
+        const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
+        const T* qkv_b = reinterpret_cast<const T*>(a.qkv) + (size_t) b * qkv_stride;
+        // FP8 cache: Q stays 16-bit (f16 A fragments, one k16 step per 4 channels of a thread);
+        // INT8 cache: 8-bit high/low fragments as described above.
+        constexpr int KS16 = DH / 16;
+        uint32_t qa[IS_FP8 ? 1 : NR][IS_FP8 ? KS16 : KS][4];
+        float sfac[NR]; // accumulator -> score in log2 units, per head-row half
 #pragma unroll
         for (int r = 0; r < NR; ++r)
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-            {
-                of[mt][r][c] = 0.f;
-                if constexpr (!IS_FP8)
-                    oi[0][mt][r][c] = 0, oi[1][mt][r][c] = 0;
-            }
-    // integer path: move the pending integer sums into the fp32 running sums
-    auto fold = [&]()
-    {
-        if constexpr (!IS_FP8)
         {
+            float qv[QV];
+            const int hl = g + 8 * r; // head within this CTA
+            if (hl < nh)
+            {
+                const T* qp = qkv_b + (size_t) (head0 + hl) * DH + t * QV;
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
+                for (int i = 0; i < QV; i += 8)
+                {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(qp + i);
+                    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-                for (int r = 0; r < NR; ++r)
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
+                    for (int j = 0; j < 4; ++j)
                     {
-                        of[mt][r][c] += (float) (oi[0][mt][r][c] * kLoWeight + oi[1][mt][r][c]);
-                        oi[0][mt][r][c] = 0;
-                        oi[1][mt][r][c] = 0;
+                        const float2 v = TypeOps<T>::unpack2(w[j]);
+                        qv[i + 2 * j] = v.x;
+                        qv[i + 2 * j + 1] = v.y;
                     }
-        }
-    };
-
-    bool timed_out = false;
-    for (int i = 0; i < my_groups; ++i)
-    {
-        const int s = i % STAGES;
-        const uint32_t parity = (i / STAGES) & 1;
-        const uint32_t kbuf = ring_u32 + s * Tr::STAGE_BYTES;
-        const uint32_t vbuf = kbuf + SLAB;
-        if (!mbar_wait_bounded(&bars[s], parity, a.status))
-        {
-            timed_out = true;
-            break;
-        }
-        const int gi = warp + NWARPS * i;
-        const int t0 = chunk_start + gi * TG;
-        const int lim = total - t0; // valid tokens in this group if < TG
-        if (new_pos < t0 + TG)
-        {
-            // The group ends with the new token: quantise it exactly as it is stored, put it into
-            // the staged tile (rows behind it were zero-filled by the copies) and, from the first
-            // head slice only, append it to the paged cache.
-            const int r_new = new_pos - t0;
-            const float sc_f = __ldg(a.scale_orig_quant);
-            const T sc_t = TypeOps<T>::from_float(sc_f);
-            if (lane < DH / 16)
-            {
-                const T* kp = qkv_b + (size_t) (a.num_heads + hk) * DH + lane * 16;
-                const T* vp = qkv_b + (size_t) (a.num_heads + a.num_kv_heads + hk) * DH + lane * 16;
-                const uint4 kq = make_cache_vec<T, CACHE, 16>(kp, sc_f, sc_t);
-                const uint4 vq = make_cache_vec<T, CACHE, 16>(vp, sc_f, sc_t);
-                const uint32_t lin = swz<DH>((uint32_t) r_new * DH + lane * 16);
-                unsigned char* stage = smem + warp * (STAGES * Tr::STAGE_BYTES) + s * Tr::STAGE_BYTES;
-                *reinterpret_cast<uint4*>(stage + lin) = kq;
-                *reinterpret_cast<uint4*>(stage + SLAB + lin) = vq;
-                if (hg == 0)
-                {
-                    const size_t off = head_off + (size_t) (new_pos & tpb_mask) * DH + lane * 16;
-                    char* kb = reinterpret_cast<char*>(__ldg(krow + (new_pos >> tpb_log2))) + off;
-                    char* vb = reinterpret_cast<char*>(__ldg(vrow + (new_pos >> tpb_log2))) + off;
-                    *reinterpret_cast<uint4*>(kb) = kq;
-                    *reinterpret_cast<uint4*>(vb) = vq;
                 }
-            }
-            __syncwarp();
-        }
-
-        // ---- S = Q K^T for the head rows x 32 tokens ----
-        Acc sacc[NSA][4][4];
-#pragma unroll
-        for (int x = 0; x < NSA; ++x)
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    sacc[x][nt][c] = 0;
-#pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
-        {
-            uint32_t kw[2 * KS];
-            {
-                const uint4 v0 = lds128(kbuf + koff[nt]);
-                kw[0] = v0.x, kw[1] = v0.y, kw[2] = v0.z, kw[3] = v0.w;
-                if constexpr (DH == 128)
-                {
-                    const uint4 v1 = lds128(kbuf + (koff[nt] ^ 16u));
-                    kw[4] = v1.x, kw[5] = v1.y, kw[6] = v1.z, kw[7] = v1.w;
-                }
-            }
-            if constexpr (IS_FP8)
-            {
-                // word j of this thread's K bytes = channels 4j..4j+3 = one k16 step
-#pragma unroll
-                for (int j = 0; j < KS16; ++j)
-                    mma_f16(sacc[0][nt], qa[0][j], e4m3x2_to_f16x2_lo(kw[j]), e4m3x2_to_f16x2_hi(kw[j]));
             }
             else
             {
 #pragma unroll
-                for (int ks = 0; ks < KS; ++ks)
+                for (int i = 0; i < QV; ++i)
+                    qv[i] = 0.f;
+            }
+            float amax = 0.f;
+#pragma unroll
+            for (int i = 0; i < QV; ++i)
+                amax = fmaxf(amax, fabsf(qv[i]));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            float qmul, qinv;
+            if constexpr (IS_FP8)
+            {
+                // power-of-two scale that puts amax into [128, 256)
+                int e = 0;
+                if (amax > 0.f)
+                    e = 7 - (int) (((__float_as_uint(amax) >> 23) & 0xff) - 127);
+                e = max(-100, min(100, e));
+                qmul = __uint_as_float((uint32_t) (e + 127) << 23);
+                qinv = __uint_as_float((uint32_t) (127 - e) << 23);
+            }
+            else
+            {
+                const float qs = amax > 0.f ? amax * (1.f / 127.f) : 1.f;
+                qmul = 1.f / qs;
+                qinv = qs * (1.f / kLoWeight);
+            }
+            sfac[r] = qinv * deq * a.softmax_scale_log2;
+            if constexpr (IS_FP8)
+            {
+                // k16 step j of this thread covers channels 4j .. 4j+3 of its QV-channel slice:
+                // (4j, 4j+1) -> k slots (2t, 2t+1), (4j+2, 4j+3) -> k slots (2t+8, 2t+9).
+#pragma unroll
+                for (int j = 0; j < KS16; ++j)
                 {
-                    const uint32_t b0 = (DH == 128) ? kw[ks] : kw[2 * ks];
-                    const uint32_t b1 = (DH == 128) ? kw[4 + ks] : kw[2 * ks + 1];
-                    mma_s8(sacc[0][nt], qa[0][ks], b0, b1);
-                    if constexpr (H16)
-                        mma_s8(sacc[1][nt], qa[1][ks], b0, b1);
+                    qa[0][j][r] = pack_f16x2(qv[4 * j] * qmul, qv[4 * j + 1] * qmul);
+                    qa[0][j][2 + r] = pack_f16x2(qv[4 * j + 2] * qmul, qv[4 * j + 3] * qmul);
+                    if constexpr (!H16)
+                    {
+                        qa[0][j][1] = 0u;
+                        qa[0][j][3] = 0u;
+                    }
+                }
+            }
+            else
+            {
+#pragma unroll
+                for (int s = 0; s < KS; ++s)
+                {
+#pragma unroll
+                    for (int half = 0; half < 2; ++half)
+                    {
+                        // elements of this thread that feed the low-k (half 0) or high-k (half 1) registers of k-step s
+                        const int base = (DH == 128) ? (16 * half + 4 * s) : (8 * s + 4 * half);
+                        uint32_t whi, wlo;
+                        split4<CACHE>(qv[base] * qmul, qv[base + 1] * qmul, qv[base + 2] * qmul, qv[base + 3] * qmul, whi, wlo);
+                        if constexpr (H16)
+                        {
+                            qa[0][s][2 * half + r] = whi; // set 0 = high parts, register = row half r
+                            qa[1][s][2 * half + r] = wlo; // set 1 = low parts
+                        }
+                        else
+                        {
+                            qa[0][s][2 * half] = whi;     // rows 0..7
+                            qa[0][s][2 * half + 1] = wlo; // rows 8..15
+                        }
+                    }
                 }
             }
         }
 
-        // ---- online softmax over the 32 tokens ----
-        float p[4][2 * NR];
-        float mx[NR];
-#pragma unroll
-        for (int r = 0; r < NR; ++r)
-            mx[r] = -INFINITY;
+        // Per-thread shared-memory offsets of the fragment loads (inside a K / V slab).
+        uint32_t koff[4], voff[8];
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt)
-        {
+            koff[nt] = swz<DH>((uint32_t) sigma_row<DH>(nt, g) * DH + t * (DH / 4));
 #pragma unroll
-            for (int c = 0; c < 2 * NR; ++c)
-            {
-                float sv;
-                if constexpr (IS_FP8)
-                    sv = sacc[0][nt][c]; // rows g (c = 0, 1) and g + 8 (c = 2, 3)
-                else if constexpr (H16)
-                    sv = (float) (sacc[0][nt][c] * kLoWeight + sacc[NSA - 1][nt][c]);
-                else
-                    sv = (float) (sacc[0][nt][c] * kLoWeight + sacc[0][nt][c + 2]);
-                p[nt][c] = sv * sfac[c >> 1];
-            }
-        }
-        if (lim < TG)
+        for (int i = 0; i < 8; ++i)
+            voff[i] = swz<DH>((uint32_t) sigma_row<DH>(i >> 1, 2 * t + (i & 1)) * DH + g * (DH / 8));
+
+        float m[NR], l[NR];
+#pragma unroll
+        for (int r = 0; r < NR; ++r)
+            m[r] = -INFINITY, l[r] = 0.f;
+        float of[MT][NR][4]; // O^T fragments: [m-tile][head half][c0..c3]
+        int oi[IS_FP8 ? 1 : 2][IS_FP8 ? 1 : MT][NR][4]; // integer path: pending high / low sums
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int r = 0; r < NR; ++r)
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                {
+                    of[mt][r][c] = 0.f;
+                    if constexpr (!IS_FP8)
+                        oi[0][mt][r][c] = 0, oi[1][mt][r][c] = 0;
+                }
+        // integer path: move the pending integer sums into the fp32 running sums
+        auto fold = [&]()
         {
+            if constexpr (!IS_FP8)
+            {
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int r = 0; r < NR; ++r)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                        {
+                            of[mt][r][c] += (float) (oi[0][mt][r][c] * kLoWeight + oi[1][mt][r][c]);
+                            oi[0][mt][r][c] = 0;
+                            oi[1][mt][r][c] = 0;
+                        }
+            }
+        };
+
+        bool timed_out = false;
+        for (int i = 0; i < my_groups; ++i)
+        {
+            const int s = (ring_base + i) % STAGES;
+            const uint32_t parity = ((ring_base + i) / STAGES) & 1;
+            const uint32_t kbuf = ring_u32 + s * Tr::STAGE_BYTES;
+            const uint32_t vbuf = kbuf + SLAB;
+            if (!mbar_wait_bounded(&bars[s], parity, a.status))
+            {
+                timed_out = true;
+                break;
+            }
+            const int gi = warp + NWARPS * i;
+            const int t0 = chunk_start + gi * TG;
+            const int lim = total - t0; // valid tokens in this group if < TG
+            if (new_pos < t0 + TG)
+            {
+                // The group ends with the new token: quantise it exactly as it is stored, put it into
+                // the staged tile (rows behind it were zero-filled by the copies) and, from the first
+                // head slice only, append it to the paged cache.
+                const int r_new = new_pos - t0;
+                const float sc_f = __ldg(a.scale_orig_quant);
+                const T sc_t = TypeOps<T>::from_float(sc_f);
+                if (lane < DH / 16)
+                {
+                    const T* kp = qkv_b + (size_t) (a.num_heads + hk) * DH + lane * 16;
+                    const T* vp = qkv_b + (size_t) (a.num_heads + a.num_kv_heads + hk) * DH + lane * 16;
+                    const uint4 kq = make_cache_vec<T, CACHE, 16>(kp, sc_f, sc_t);
+                    const uint4 vq = make_cache_vec<T, CACHE, 16>(vp, sc_f, sc_t);
+                    const uint32_t lin = swz<DH>((uint32_t) r_new * DH + lane * 16);
+                    unsigned char* stage = smem + warp * (STAGES * Tr::STAGE_BYTES) + s * Tr::STAGE_BYTES;
+                    *reinterpret_cast<uint4*>(stage + lin) = kq;
+                    *reinterpret_cast<uint4*>(stage + SLAB + lin) = vq;
+                    if (hg == 0)
+                    {
+                        const size_t off = head_off + (size_t) (new_pos & tpb_mask) * DH + lane * 16;
+                        char* kb = reinterpret_cast<char*>(__ldg(krow + (new_pos >> tpb_log2))) + off;
+                        char* vb = reinterpret_cast<char*>(__ldg(vrow + (new_pos >> tpb_log2))) + off;
+                        *reinterpret_cast<uint4*>(kb) = kq;
+                        *reinterpret_cast<uint4*>(vb) = vq;
+                    }
+                }
+                __syncwarp();
+            }
+
+            // ---- S = Q K^T for the head rows x 32 tokens ----
+            Acc sacc[NSA][4][4];
+#pragma unroll
+            for (int x = 0; x < NSA; ++x)
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        sacc[x][nt][c] = 0;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+            {
+                uint32_t kw[2 * KS];
+                {
+                    const uint4 v0 = lds128(kbuf + koff[nt]);
+                    kw[0] = v0.x, kw[1] = v0.y, kw[2] = v0.z, kw[3] = v0.w;
+                    if constexpr (DH == 128)
+                    {
+                        const uint4 v1 = lds128(kbuf + (koff[nt] ^ 16u));
+                        kw[4] = v1.x, kw[5] = v1.y, kw[6] = v1.z, kw[7] = v1.w;
+                    }
+                }
+                if constexpr (IS_FP8)
+                {
+                    // word j of this thread's K bytes = channels 4j..4j+3 = one k16 step
+#pragma unroll
+                    for (int j = 0; j < KS16; ++j)
+                        mma_f16(sacc[0][nt], qa[0][j], e4m3x2_to_f16x2_lo(kw[j]), e4m3x2_to_f16x2_hi(kw[j]));
+                }
+                else
+                {
+#pragma unroll
+                    for (int ks = 0; ks < KS; ++ks)
+                    {
+                        const uint32_t b0 = (DH == 128) ? kw[ks] : kw[2 * ks];
+                        const uint32_t b1 = (DH == 128) ? kw[4 + ks] : kw[2 * ks + 1];
+                        mma_s8(sacc[0][nt], qa[0][ks], b0, b1);
+                        if constexpr (H16)
+                            mma_s8(sacc[1][nt], qa[1][ks], b0, b1);
+                    }
+                }
+            }
+
+            // ---- online softmax over the 32 tokens ----
+            float p[4][2 * NR];
+            float mx[NR];
+#pragma unroll
+            for (int r = 0; r < NR; ++r)
+                mx[r] = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+            {
+#pragma unroll
+                for (int c = 0; c < 2 * NR; ++c)
+                {
+                    float sv;
+                    if constexpr (IS_FP8)
+                        sv = sacc[0][nt][c]; // rows g (c = 0, 1) and g + 8 (c = 2, 3)
+                    else if constexpr (H16)
+                        sv = (float) (sacc[0][nt][c] * kLoWeight + sacc[NSA - 1][nt][c]);
+                    else
+                        sv = (float) (sacc[0][nt][c] * kLoWeight + sacc[0][nt][c + 2]);
+                    p[nt][c] = sv * sfac[c >> 1];
+                }
+            }
+            if (lim < TG)
+            {
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                    for (int c = 0; c < 2 * NR; ++c)
+                        if (sigma_row<DH>(nt, 2 * t + (c & 1)) >= lim)
+                            p[nt][c] = -INFINITY;
+            }
 #pragma unroll
             for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
                 for (int c = 0; c < 2 * NR; ++c)
-                    if (sigma_row<DH>(nt, 2 * t + (c & 1)) >= lim)
-                        p[nt][c] = -INFINITY;
-        }
+                    mx[c >> 1] = fmaxf(mx[c >> 1], p[nt][c]);
+            float alpha[NR];
+            bool changed = false;
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
+            for (int r = 0; r < NR; ++r)
+            {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m[r], mx[r]);
+                alpha[r] = fast_exp2(m[r] - m_new);
+                changed |= m_new != m[r];
+                m[r] = m_new;
+                l[r] *= alpha[r];
+            }
+            // FP8 cache: P as f16 (scaled by 1024 to stay clear of f16 subnormals), pb[r][k16 step][b0/b1];
+            // INT8 cache: P split into high / low 8-bit parts, pb[r][hi/lo][b0/b1].
+            constexpr float PSCALE = IS_FP8 ? 1024.f : 127.f;
+            uint32_t pb[NR][2][2];
 #pragma unroll
-            for (int c = 0; c < 2 * NR; ++c)
-                mx[c >> 1] = fmaxf(mx[c >> 1], p[nt][c]);
-        float alpha[NR];
-        bool changed = false;
+            for (int r = 0; r < NR; ++r)
+            {
 #pragma unroll
-        for (int r = 0; r < NR; ++r)
-        {
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            const float m_new = fmaxf(m[r], mx[r]);
-            alpha[r] = fast_exp2(m[r] - m_new);
-            changed |= m_new != m[r];
-            m[r] = m_new;
-            l[r] *= alpha[r];
-        }
-        // FP8 cache: P as f16 (scaled by 1024 to stay clear of f16 subnormals), pb[r][k16 step][b0/b1];
-        // INT8 cache: P split into high / low 8-bit parts, pb[r][hi/lo][b0/b1].
-        constexpr float PSCALE = IS_FP8 ? 1024.f : 127.f;
-        uint32_t pb[NR][2][2];
+                for (int kh = 0; kh < 2; ++kh)
+                {
+                    float pv[4];
 #pragma unroll
-        for (int r = 0; r < NR; ++r)
-        {
+                    for (int q4 = 0; q4 < 4; ++q4)
+                    {
+                        pv[q4] = fast_exp2(p[2 * kh + (q4 >> 1)][2 * r + (q4 & 1)] - m[r]);
+                        l[r] += pv[q4];
+                    }
+                    if constexpr (IS_FP8)
+                    {
+                        pb[r][kh][0] = pack_f16x2(pv[0] * PSCALE, pv[1] * PSCALE);
+                        pb[r][kh][1] = pack_f16x2(pv[2] * PSCALE, pv[3] * PSCALE);
+                    }
+                    else
+                    {
+                        split4<CACHE>(pv[0] * PSCALE, pv[1] * PSCALE, pv[2] * PSCALE, pv[3] * PSCALE, pb[r][0][kh], pb[r][1][kh]);
+                    }
+                }
+            }
+
+            // ---- rescale the running O^T when a row maximum moved (its columns are heads 2t, 2t+1 (+8)) ----
+            if (__any_sync(0xffffffffu, changed))
+            {
+                fold();
+#pragma unroll
+                for (int r = 0; r < NR; ++r)
+                {
+                    const float a0 = __shfl_sync(0xffffffffu, alpha[r], 8 * t);
+                    const float a1 = __shfl_sync(0xffffffffu, alpha[r], 8 * t + 4);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+                    {
+                        of[mt][r][0] *= a0;
+                        of[mt][r][1] *= a1;
+                        of[mt][r][2] *= a0;
+                        of[mt][r][3] *= a1;
+                    }
+                }
+            }
+            else if ((i & 255) == 255)
+            {
+                fold(); // keeps the pending integer sums far from overflow on very long partitions
+            }
+
+            // ---- O^T += V^T P^T ----
+            uint32_t tr[2][NW][4]; // [k half][word][byte column] -> one A register each
 #pragma unroll
             for (int kh = 0; kh < 2; ++kh)
             {
-                float pv[4];
+                uint32_t rv[4][NW];
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4)
                 {
-                    pv[q4] = fast_exp2(p[2 * kh + (q4 >> 1)][2 * r + (q4 & 1)] - m[r]);
-                    l[r] += pv[q4];
+                    if constexpr (DH == 128)
+                    {
+                        const uint4 v = lds128(vbuf + voff[4 * kh + q4]);
+                        rv[q4][0] = v.x, rv[q4][1] = v.y, rv[q4][2] = v.z, rv[q4][3] = v.w;
+                    }
+                    else
+                    {
+                        const uint2 v = lds64(vbuf + voff[4 * kh + q4]);
+                        rv[q4][0] = v.x, rv[q4][1] = v.y;
+                    }
                 }
-                if constexpr (IS_FP8)
-                {
-                    pb[r][kh][0] = pack_f16x2(pv[0] * PSCALE, pv[1] * PSCALE);
-                    pb[r][kh][1] = pack_f16x2(pv[2] * PSCALE, pv[3] * PSCALE);
-                }
-                else
-                {
-                    split4<CACHE>(pv[0] * PSCALE, pv[1] * PSCALE, pv[2] * PSCALE, pv[3] * PSCALE, pb[r][0][kh], pb[r][1][kh]);
-                }
-            }
-        }
-
-        // ---- rescale the running O^T when a row maximum moved (its columns are heads 2t, 2t+1 (+8)) ----
-        if (__any_sync(0xffffffffu, changed))
-        {
-            fold();
 #pragma unroll
-            for (int r = 0; r < NR; ++r)
+                for (int w = 0; w < NW; ++w)
+                    transpose4x4(rv[0][w], rv[1][w], rv[2][w], rv[3][w], tr[kh][w]);
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
             {
-                const float a0 = __shfl_sync(0xffffffffu, alpha[r], 8 * t);
-                const float a1 = __shfl_sync(0xffffffffu, alpha[r], 8 * t + 4);
+                const int w = mt >> 1, bc = 2 * (mt & 1);
+                const uint32_t av[4] = {tr[0][w][bc], tr[0][w][bc + 1], tr[1][w][bc], tr[1][w][bc + 1]};
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt)
+                for (int r = 0; r < NR; ++r)
                 {
-                    of[mt][r][0] *= a0;
-                    of[mt][r][1] *= a1;
-                    of[mt][r][2] *= a0;
-                    of[mt][r][3] *= a1;
+                    if constexpr (IS_FP8)
+                    {
+                        // two k16 steps: tokens of k half 0 (av[0], av[1]) and of k half 1 (av[2], av[3])
+                        const uint32_t a0[4] = {e4m3x2_to_f16x2_lo(av[0]), e4m3x2_to_f16x2_lo(av[1]),
+                            e4m3x2_to_f16x2_hi(av[0]), e4m3x2_to_f16x2_hi(av[1])};
+                        const uint32_t a1[4] = {e4m3x2_to_f16x2_lo(av[2]), e4m3x2_to_f16x2_lo(av[3]),
+                            e4m3x2_to_f16x2_hi(av[2]), e4m3x2_to_f16x2_hi(av[3])};
+                        mma_f16(of[mt][r], a0, pb[r][0][0], pb[r][0][1]);
+                        mma_f16(of[mt][r], a1, pb[r][1][0], pb[r][1][1]);
+                    }
+                    else
+                    {
+                        mma_s8(oi[0][mt][r], av, pb[r][0][0], pb[r][0][1]);
+                        mma_s8(oi[1][mt][r], av, pb[r][1][0], pb[r][1][1]);
+                    }
                 }
             }
-        }
-        else if ((i & 255) == 255)
-        {
-            fold(); // keeps the pending integer sums far from overflow on very long partitions
-        }
 
-        // ---- O^T += V^T P^T ----
-        uint32_t tr[2][NW][4]; // [k half][word][byte column] -> one A register each
-#pragma unroll
-        for (int kh = 0; kh < 2; ++kh)
-        {
-            uint32_t rv[4][NW];
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4)
-            {
-                if constexpr (DH == 128)
-                {
-                    const uint4 v = lds128(vbuf + voff[4 * kh + q4]);
-                    rv[q4][0] = v.x, rv[q4][1] = v.y, rv[q4][2] = v.z, rv[q4][3] = v.w;
-                }
-                else
-                {
-                    const uint2 v = lds64(vbuf + voff[4 * kh + q4]);
-                    rv[q4][0] = v.x, rv[q4][1] = v.y;
-                }
-            }
-#pragma unroll
-            for (int w = 0; w < NW; ++w)
-                transpose4x4(rv[0][w], rv[1][w], rv[2][w], rv[3][w], tr[kh][w]);
+            __syncwarp(); // every lane is done reading this stage
+            if (i + STAGES < my_groups)
+                issue(i + STAGES);
         }
+        fold();
+
+        if (timed_out && lane == 0)
+            atomicExch(a.status, STATUS_TIMEOUT);
+
+        // ---- per-warp results -> shared memory, then combine the 4 warps ----
+#pragma unroll
+        for (int r = 0; r < NR; ++r)
+        {
+            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+        }
+        __syncthreads(); // all warps have drained their rings; the ring memory is reused below
+        float* mo = reinterpret_cast<float*>(smem) + warp * (16 * DH + 32);
+        float* mm = mo + 16 * DH; // m[16], then l[16]
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int r = 0; r < NR; ++r)
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                {
+                    const int head = 8 * r + 2 * t + (c & 1);
+                    const int dh = (DH / 8) * g + 2 * mt + (c >> 1);
+                    mo[head * DH + dh] = of[mt][r][c];
+                }
+        if (t == 0)
         {
-            const int w = mt >> 1, bc = 2 * (mt & 1);
-            const uint32_t av[4] = {tr[0][w][bc], tr[0][w][bc + 1], tr[1][w][bc], tr[1][w][bc + 1]};
 #pragma unroll
             for (int r = 0; r < NR; ++r)
             {
-                if constexpr (IS_FP8)
-                {
-                    // two k16 steps: tokens of k half 0 (av[0], av[1]) and of k half 1 (av[2], av[3])
-                    const uint32_t a0[4] = {e4m3x2_to_f16x2_lo(av[0]), e4m3x2_to_f16x2_lo(av[1]),
-                        e4m3x2_to_f16x2_hi(av[0]), e4m3x2_to_f16x2_hi(av[1])};
-                    const uint32_t a1[4] = {e4m3x2_to_f16x2_lo(av[2]), e4m3x2_to_f16x2_lo(av[3]),
-                        e4m3x2_to_f16x2_hi(av[2]), e4m3x2_to_f16x2_hi(av[3])};
-                    mma_f16(of[mt][r], a0, pb[r][0][0], pb[r][0][1]);
-                    mma_f16(of[mt][r], a1, pb[r][1][0], pb[r][1][1]);
-                }
-                else
-                {
-                    mma_s8(oi[0][mt][r], av, pb[r][0][0], pb[r][0][1]);
-                    mma_s8(oi[1][mt][r], av, pb[r][1][0], pb[r][1][1]);
-                }
+                mm[8 * r + g] = m[r];
+                mm[16 + 8 * r + g] = l[r];
             }
         }
+        __syncthreads();
 
-        __syncwarp(); // every lane is done reading this stage
-        if (i + STAGES < my_groups)
-            issue(i + STAGES);
-    }
-    fold();
-
-    if (timed_out && lane == 0)
-        atomicExch(a.status, STATUS_TIMEOUT);
-
-    // ---- per-warp results -> shared memory, then combine the 4 warps ----
+        constexpr float ONORM = IS_FP8 ? (1.f / 1024.f) : (1.f / (127.f * kLoWeight));
+        const float ofac = deq * ONORM;
+        const float* base = reinterpret_cast<const float*>(smem);
+        for (int idx = threadIdx.x; idx < nh * DH; idx += blockDim.x)
+        {
+            const int head = idx / DH, dh = idx % DH;
+            float M = -INFINITY;
 #pragma unroll
-    for (int r = 0; r < NR; ++r)
-    {
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-    }
-    __syncthreads(); // all warps have drained their rings; the ring memory is reused below
-    float* mo = reinterpret_cast<float*>(smem) + warp * (16 * DH + 32);
-    float* mm = mo + 16 * DH; // m[16], then l[16]
+            for (int w = 0; w < NWARPS; ++w)
+                M = fmaxf(M, base[w * (16 * DH + 32) + 16 * DH + head]);
+            float L = 0.f, o = 0.f;
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int r = 0; r < NR; ++r)
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
+            for (int w = 0; w < NWARPS; ++w)
             {
-                const int head = 8 * r + 2 * t + (c & 1);
-                const int dh = (DH / 8) * g + 2 * mt + (c >> 1);
-                mo[head * DH + dh] = of[mt][r][c];
+                const float* wb = base + w * (16 * DH + 32);
+                const float mw = wb[16 * DH + head];
+                const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
+                L = fmaf(wb[16 * DH + 16 + head], f, L);
+                o = fmaf(wb[head * DH + dh], f, o);
             }
-    if (t == 0)
-    {
-#pragma unroll
-        for (int r = 0; r < NR; ++r)
-        {
-            mm[8 * r + g] = m[r];
-            mm[16 + 8 * r + g] = l[r];
+            const size_t row = (size_t) b * a.num_heads + head0 + head;
+            if (final_out)
+            {
+                reinterpret_cast<T*>(a.out)[row * DH + dh] = TypeOps<T>::from_float(o * ofac / L);
+            }
+            else
+            {
+                a.part_o[(row * a.nsplit + chunk) * DH + dh] = o * ofac;
+                if (dh == 0)
+                    a.part_ml[row * a.nsplit + chunk] = make_float2(M, L);
+            }
         }
-    }
-    __syncthreads();
-
-    constexpr float ONORM = IS_FP8 ? (1.f / 1024.f) : (1.f / (127.f * kLoWeight));
-    const float ofac = deq * ONORM;
-    const float* base = reinterpret_cast<const float*>(smem);
-    for (int idx = threadIdx.x; idx < nh * DH; idx += blockDim.x)
-    {
-        const int head = idx / DH, dh = idx % DH;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < NWARPS; ++w)
-            M = fmaxf(M, base[w * (16 * DH + 32) + 16 * DH + head]);
-        float L = 0.f, o = 0.f;
-#pragma unroll
-        for (int w = 0; w < NWARPS; ++w)
-        {
-            const float* wb = base + w * (16 * DH + 32);
-            const float mw = wb[16 * DH + head];
-            const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
-            L = fmaf(wb[16 * DH + 16 + head], f, L);
-            o = fmaf(wb[head * DH + dh], f, o);
-        }
-        const size_t row = (size_t) b * a.num_heads + head0 + head;
-        if (a.nsplit == 1)
-        {
-            reinterpret_cast<T*>(a.out)[row * DH + dh] = TypeOps<T>::from_float(o * ofac / L);
-        }
-        else
-        {
-            a.part_o[(row * a.nsplit + chunk) * DH + dh] = o * ofac;
-            if (dh == 0)
-                a.part_ml[row * a.nsplit + chunk] = make_float2(M, L);
-        }
+        // ---- next piece (the merge scratch above aliases the rings: everybody must be done reading it) ----
+        ring_base += my_groups;
+        const int stop = __syncthreads_or(timed_out ? 1 : 0);
+        if (!a.streamk || stop || !sk_next(sk, cur))
+            break;
     }
 }
 

@@ -13,19 +13,11 @@
 namespace dx
 {
 
+// Merges the first n partial results of q row `row` (= b * H + h) into the output row.  One warp.
 template <typename T, int DH>
-__global__ void __launch_bounds__(128) lse_merge_kernel(const AttnArgs a)
+__device__ __forceinline__ void merge_row(const AttnArgs& a, int row, int n, int lane)
 {
     constexpr int VPL = DH / 32; // floats per lane (2 or 4)
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * 4 + warp; // b * H + h
-    if (row >= a.batch * a.num_heads)
-        return;
-    const int b = row / a.num_heads;
-    const int total = a.seq_len[b];
-    griddep_wait(); // launched with programmatic stream serialisation: the partials are complete after this
-    const int n = (total + a.chunk_tokens - 1) / a.chunk_tokens; // partitions this sequence used (partition_of)
-
     // (m, l) of up to 32 partitions per pass, one per lane: all loads of a pass are in flight together.
     const float2* ml = a.part_ml + (size_t) row * a.nsplit;
     float M = -INFINITY;
@@ -103,6 +95,38 @@ __global__ void __launch_bounds__(128) lse_merge_kernel(const AttnArgs a)
     {
         *reinterpret_cast<uint32_t*>(dst) = TypeOps<T>::pack2(o[0] * inv, o[1] * inv);
     }
+}
+
+template <typename T, int DH>
+__global__ void __launch_bounds__(128) lse_merge_kernel(const AttnArgs a)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + warp; // b * H + h
+    if (row >= a.batch * a.num_heads)
+        return;
+    const int b = row / a.num_heads;
+    const int total = a.seq_len[b];
+    griddep_wait(); // launched with programmatic stream serialisation: the partials are complete after this
+    const int n = (total + a.chunk_tokens - 1) / a.chunk_tokens; // partitions this sequence used (partition_of)
+    merge_row<T, DH>(a, row, n, lane);
+}
+
+// Stream-K launches: a row cut into several pieces has one partial per piece; rows that one CTA covered alone
+// were written out by the attention kernel.
+template <typename T, int DH>
+__global__ void __launch_bounds__(128) lse_merge_sk_kernel(const AttnArgs a, const int hgroups, const __grid_constant__ SkSchedule sk)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + warp; // b * H + h
+    if (row >= a.batch * a.num_heads)
+        return;
+    const int b = row / a.num_heads, h = row % a.num_heads;
+    const int G = a.num_heads / a.num_kv_heads;
+    const int y = (h / G) * hgroups + (h % G) / 16;
+    const int n = sk_pieces_of_row(sk, b, y);
+    griddep_wait();
+    if (n > 1)
+        merge_row<T, DH>(a, row, n, lane);
 }
 
 } // namespace dx

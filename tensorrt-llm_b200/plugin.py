@@ -219,9 +219,12 @@ class GPTAttentionPlugin:
             st = self.lib.dx_attn_plan(self._h, batch, max_past_len, ctypes.byref(n), ctypes.byref(c), ctypes.byref(k))
         if st != DX_OK:
             raise DecodeAttnError(st, "dx_attn_plan")
-        return {"num_partitions": n.value, "tokens_per_partition": c.value,
-                "kernel": {0: "mha_cuda_core", 1: "gqa_tensor_core", 2: "wide_group_tcgen05",
-                           3: "token_major_tcgen05"}.get(k.value, "?")}
+        kernel = {0: "mha_cuda_core", 1: "gqa_tensor_core", 2: "wide_group_tcgen05",
+                  3: "token_major_tcgen05"}.get(k.value, "?")
+        if n.value < 0:  # stream-K launch: equal token ranges per CTA
+            return {"num_partitions": 0, "tokens_per_partition": c.value, "kernel": kernel,
+                    "stream_k_ctas": -n.value}
+        return {"num_partitions": n.value, "tokens_per_partition": c.value, "kernel": kernel}
 
     def launch_count(self) -> int:
         return int(self.lib.dx_attn_launch_count(self._h))

@@ -69,6 +69,7 @@ def gpu_step_and_compare(pkg, cfg, *, lengths=None, multi_block_mode=None, devic
             assert torch.equal(out, out2)
             assert torch.equal(w.pool.cpu(), pool_ref)
         return {"max_abs": err.max().item(), "mean_abs": err.mean().item(),
-                "plan": plugin.plan(cfg.batch, int(w_cpu.host_past_key_value_lengths.max()))}
+                "plan": plugin.plan(cfg.batch, int(w_cpu.host_past_key_value_lengths.max()),
+                                    w_cpu.host_past_key_value_lengths)}
     finally:
         plugin.close()

@@ -1,0 +1,82 @@
+"""Stream-K launches of the grouped-head 8-bit kernel (equal ranges of the batch's token groups per CTA, rows cut
+into pieces wherever a range ends): parity against the CPU oracle on shapes small enough for the oracle, with the
+threshold lowered so that they take the stream-K path."""
+import dataclasses
+
+import pytest
+import torch
+
+import oracle
+from helpers import CACHE_MODE, MAX_ABS_TOL, MEAN_ABS_TOL, gpu_step_and_compare
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _force(monkeypatch):
+    monkeypatch.setenv("DX_ATTN_SK_MIN_UNITS", "1")
+    monkeypatch.setenv("DX_ATTN_SK_ROW_FACTOR", "1000000")
+
+
+@pytest.mark.parametrize("cache", ["fp8", "int8"])
+@pytest.mark.parametrize("heads,dh", [((8, 1), 128), ((64, 8), 128), ((16, 1), 128), ((24, 1), 64), ((8, 2), 64)])
+def test_ragged_batches(pkg, cache, heads, dh):
+    cfg = pkg.workloads.DecodeConfig("sk", 7, heads[0], heads[1], dh, torch.bfloat16, cache, 64, 20, 3000, True, 77)
+    r = gpu_step_and_compare(pkg, cfg)
+    # (24 heads on one kv head with an FP8 cache run on the wide-group kernel, which has no stream-K form)
+    assert r["plan"]["kernel"] != "gqa_tensor_core" or r["plan"].get("stream_k_ctas", 0) > 0, r["plan"]
+
+
+def test_many_short_rows_and_boundary_lengths(pkg):
+    lens = [0, 1, 31, 32, 33, 63, 64, 65, 95, 96, 127, 128, 129, 255, 256, 257, 517, 1023, 1024, 1025, 2047, 2048]
+    cfg = dataclasses.replace(pkg.workloads.CONFIGS["c4"], batch=len(lens))
+    r = gpu_step_and_compare(pkg, cfg, lengths=torch.tensor(lens, dtype=torch.int32))
+    assert r["plan"].get("stream_k_ctas", 0) > 0
+
+
+def test_one_long_row_cut_into_many_pieces(pkg):
+    cfg = pkg.workloads.DecodeConfig("sk1", 1, 8, 1, 128, torch.bfloat16, "fp8", 128, 30000, 30000, True, 5)
+    r = gpu_step_and_compare(pkg, cfg)
+    assert r["plan"].get("stream_k_ctas", 0) > 100
+
+
+def test_host_lengths_may_be_upper_bounds(pkg):
+    """A captured graph replays with the host lengths it was planned with while the device lengths are the real
+    (shorter) ones: pieces scheduled beyond the real length are empty, the result is that of the real length."""
+    wl = pkg.workloads
+    cfg = wl.DecodeConfig("skub", 6, 32, 4, 128, torch.bfloat16, "fp8", 64, 100, 1500, True, 9)
+    w_cpu = wl.build_workload(cfg, "cpu")
+    w = wl.to_device(w_cpu, "cuda:0")
+    plugin = wl.make_plugin(cfg, 0)
+    try:
+        bound = w_cpu.host_past_key_value_lengths + torch.tensor([0, 5, 40, 333, 1000, 64], dtype=torch.int32)
+        M = w.kv_cache_block_pointers.shape[-1]
+        bound = torch.clamp(bound, max=M * cfg.tokens_per_block - 1)
+        assert plugin.plan(cfg.batch, int(bound.max()), bound).get("stream_k_ctas", 0) > 0
+        out = plugin.enqueue_generation(w.qkv, w.sequence_length, bound, w.kv_cache_block_pointers,
+                                        w.kv_orig_quant_scale, w.kv_quant_orig_scale)
+        torch.cuda.synchronize()
+        assert plugin.device_status() == 0
+        pool_ref = w_cpu.pool.clone()
+        ref = oracle.decode_attention_reference(
+            w_cpu.qkv, w_cpu.sequence_length, pool_ref, w_cpu.offset_table, num_heads=cfg.num_heads,
+            num_kv_heads=cfg.num_kv_heads, head_size=cfg.head_size, tokens_per_block=cfg.tokens_per_block,
+            cache_mode=CACHE_MODE[cfg.cache], kv_scale_orig_quant=w_cpu.scale_orig_quant,
+            kv_scale_quant_orig=w_cpu.scale_quant_orig)
+        assert torch.equal(w.pool.cpu(), pool_ref)
+        err = (out.float().cpu() - ref).abs()
+        assert err.max().item() < MAX_ABS_TOL and err.mean().item() < MEAN_ABS_TOL
+    finally:
+        plugin.close()
+
+
+def test_switch_and_threshold_keep_the_classic_plan(pkg, monkeypatch):
+    cfg = pkg.workloads.DecodeConfig("skoff", 4, 8, 1, 128, torch.bfloat16, "fp8", 64, 200, 900, True, 3)
+    monkeypatch.setenv("DX_ATTN_STREAMK", "0")
+    r = gpu_step_and_compare(pkg, cfg, check_twice=False)
+    assert "stream_k_ctas" not in r["plan"]
+    monkeypatch.delenv("DX_ATTN_STREAMK")
+    monkeypatch.delenv("DX_ATTN_SK_MIN_UNITS")  # default thresholds: this batch is far too small
+    monkeypatch.delenv("DX_ATTN_SK_ROW_FACTOR")
+    r = gpu_step_and_compare(pkg, cfg, check_twice=False)
+    assert "stream_k_ctas" not in r["plan"]
