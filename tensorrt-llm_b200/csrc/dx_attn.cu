@@ -75,6 +75,7 @@ struct dx_attn
     int sk_min_units = 48;      // stream-K only when a CTA's range is at least this many token groups: below, the
                                 // second prologue / epilogue of a CTA that straddles a row boundary costs more
                                 // than the even split wins (measured on the TP8 shards)
+    bool streamk16 = false;     // the 16-bit kernel measured slower with it on its benchmark shape (131 -> 137 us): opt-in
     int sk_row_factor = 6;      // ... and only when the average row is at most this many ranges long
     SkSchedule sk_zero{};       // third argument of classic launches of the grouped-head kernels
     int force_chunk = 0;     // > 0: partition bound forced (tuning)
@@ -208,15 +209,15 @@ Plan make_plan(const dx_attn* h, int batch, int max_past_len, const int32_t* hos
     return p;
 }
 
-// Stream-K schedule (SkSchedule in dx_common.cuh) for a call planned on the grouped-head 8-bit kernel.  On
+// Stream-K schedule (SkSchedule in dx_common.cuh) for a call planned on a grouped-head mma.sync kernel.  On
 // success the plan's slot count and partial sizes are those of the schedule.  False: keep the classic plan.
 bool build_streamk(const dx_attn* h, Plan& plan, const int32_t* host_past, int batch, SkSchedule& sk, int& ctas)
 {
     const dx_attn_config& c = h->cfg;
-    if (!h->streamk || !c.multi_block_mode || plan.kind != KIND_GQA || h->cache_kind == CACHE_T || !host_past
-        || batch > DX_SK_MAX_SEQ || !h->k_merge_sk)
+    if (!h->streamk || !c.multi_block_mode || plan.kind != KIND_GQA || !host_past || batch > DX_SK_MAX_SEQ
+        || !h->k_merge_sk || (h->cache_kind == CACHE_T && !h->streamk16))
         return false;
-    const uint32_t unit = 32;
+    const uint32_t unit = h->cache_kind == CACHE_T ? 16 : 32; // tokens per group of the kernel
     const uint32_t Y = (uint32_t) (c.num_kv_heads * plan.hgroups);
     uint64_t acc = 0;
     uint32_t nmax = 1;
@@ -235,7 +236,7 @@ bool build_streamk(const dx_attn* h, Plan& plan, const int32_t* host_past, int b
     const uint64_t U = (total + slots - 1) / slots;
     // Worth it when the ranges are long (see sk_min_units) and the rows are not many times longer than a range:
     // few very long rows are cut evenly by the classic partitions already.
-    if (U < (uint64_t) h->sk_min_units || acc > (uint64_t) h->sk_row_factor * U * (uint64_t) batch)
+    if (U * unit < (uint64_t) h->sk_min_units * 32 || acc > (uint64_t) h->sk_row_factor * U * (uint64_t) batch)
         return false;
     const uint64_t pmax = (nmax - 1) / U + 2; // pieces of the longest row, at most
     const size_t qrows = (size_t) batch * c.num_heads;
@@ -566,6 +567,8 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
         h->streamk = atoi(w) != 0;
     if (const char* w = getenv("DX_ATTN_SK_MIN_UNITS"))
         h->sk_min_units = std::max(1, atoi(w));
+    if (const char* w = getenv("DX_ATTN_STREAMK_16BIT"))
+        h->streamk16 = atoi(w) != 0;
     if (const char* w = getenv("DX_ATTN_SK_ROW_FACTOR"))
         h->sk_row_factor = std::max(1, atoi(w));
 
@@ -818,7 +821,7 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
         if (!k.fn)
             return DX_ERR_UNSUPPORTED;
         int hgroups = plan.hgroups;
-        void* args[] = {&a, &hgroups, use_sk ? &sk : &h->sk_zero}; // (the 16-bit kernel takes the first two)
+        void* args[] = {&a, &hgroups, use_sk ? &sk : &h->sk_zero};
         const dim3 grid = use_sk ? dim3(sk_ctas) : dim3(plan.nsplit, c.num_kv_heads * plan.hgroups, p.num_requests);
         st = check_cuda(h, cudaLaunchKernel(k.fn, grid, dim3(128), args, (size_t) k.smem, stream));
     }

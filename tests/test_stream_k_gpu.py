@@ -16,14 +16,17 @@ pytestmark = pytest.mark.gpu
 def _force(monkeypatch):
     monkeypatch.setenv("DX_ATTN_SK_MIN_UNITS", "1")
     monkeypatch.setenv("DX_ATTN_SK_ROW_FACTOR", "1000000")
+    monkeypatch.setenv("DX_ATTN_STREAMK_16BIT", "1")
 
 
-@pytest.mark.parametrize("cache", ["fp8", "int8"])
+@pytest.mark.parametrize("cache", ["fp8", "int8", "none"])
 @pytest.mark.parametrize("heads,dh", [((8, 1), 128), ((64, 8), 128), ((16, 1), 128), ((24, 1), 64), ((8, 2), 64)])
 def test_ragged_batches(pkg, cache, heads, dh):
     cfg = pkg.workloads.DecodeConfig("sk", 7, heads[0], heads[1], dh, torch.bfloat16, cache, 64, 20, 3000, True, 77)
     r = gpu_step_and_compare(pkg, cfg)
     # (24 heads on one kv head with an FP8 cache run on the wide-group kernel, which has no stream-K form)
+    if cache == "none":
+        assert r["plan"].get("stream_k_ctas", 0) > 0, r["plan"]
     assert r["plan"]["kernel"] != "gqa_tensor_core" or r["plan"].get("stream_k_ctas", 0) > 0, r["plan"]
 
 
@@ -78,5 +81,6 @@ def test_switch_and_threshold_keep_the_classic_plan(pkg, monkeypatch):
     monkeypatch.delenv("DX_ATTN_STREAMK")
     monkeypatch.delenv("DX_ATTN_SK_MIN_UNITS")  # default thresholds: this batch is far too small
     monkeypatch.delenv("DX_ATTN_SK_ROW_FACTOR")
+    monkeypatch.delenv("DX_ATTN_STREAMK_16BIT")
     r = gpu_step_and_compare(pkg, cfg, check_twice=False)
     assert "stream_k_ctas" not in r["plan"]
