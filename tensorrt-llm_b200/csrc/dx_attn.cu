@@ -214,10 +214,11 @@ Plan make_plan(const dx_attn* h, int batch, int max_past_len, const int32_t* hos
 bool build_streamk(const dx_attn* h, Plan& plan, const int32_t* host_past, int batch, SkSchedule& sk, int& ctas)
 {
     const dx_attn_config& c = h->cfg;
-    if (!h->streamk || !c.multi_block_mode || plan.kind != KIND_GQA || !host_past || batch > DX_SK_MAX_SEQ
-        || !h->k_merge_sk || (h->cache_kind == CACHE_T && !h->streamk16))
+    if (!h->streamk || !c.multi_block_mode || (plan.kind != KIND_GQA && plan.kind != KIND_TOK) || !host_past
+        || batch > DX_SK_MAX_SEQ || !h->k_merge_sk || (h->cache_kind == CACHE_T && !h->streamk16))
         return false;
-    const uint32_t unit = h->cache_kind == CACHE_T ? 16 : 32; // tokens per group of the kernel
+    // tokens per schedule unit: a token group of the mma.sync kernels, a tile of the token-major tcgen05 kernel
+    const uint32_t unit = plan.kind == KIND_TOK ? 128 : h->cache_kind == CACHE_T ? 16 : 32;
     const uint32_t Y = (uint32_t) (c.num_kv_heads * plan.hgroups);
     uint64_t acc = 0;
     uint32_t nmax = 1;
@@ -265,9 +266,10 @@ size_t workspace_bound(const dx_attn* h, int batch, int max_past_len)
     const long t_min = std::max<long>(128, h->min_chunk);
     long nsplit = std::min(parts_of(max_total, t_min), std::max<long>(1, h->waves * h->sm_count * resident / rows_per_seq));
     nsplit = std::max<long>(nsplit, shape.nsplit);
-    if (nsplit <= 1 && shape.kind != KIND_GQA)
+    const bool sk_kind = shape.kind == KIND_GQA || shape.kind == KIND_TOK;
+    if (nsplit <= 1 && !sk_kind)
         return 0;
-    if (shape.kind == KIND_GQA)
+    if (sk_kind)
         nsplit += 2; // stream-K launches: a row of n groups cut by ranges of U groups has at most n / U + 2 pieces
     const size_t qrows = (size_t) batch * c.num_heads;
     return align_up(qrows * nsplit * c.head_size * sizeof(float), 128) + align_up(qrows * nsplit * sizeof(float2), 128);
@@ -811,8 +813,9 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     }
     else if (plan.kind == KIND_TOK)
     {
-        void* args[] = {&a};
-        dim3 grid(plan.nsplit, c.num_kv_heads, p.num_requests);
+        int hgroups = 1;
+        void* args[] = {&a, &hgroups, use_sk ? &sk : &h->sk_zero};
+        const dim3 grid = use_sk ? dim3(sk_ctas) : dim3(plan.nsplit, c.num_kv_heads, p.num_requests);
         st = check_cuda(h, cudaLaunchKernel(h->k_tok.fn, grid, dim3(128), args, (size_t) h->k_tok.smem, stream));
     }
     else if (plan.kind == KIND_GQA)

@@ -84,3 +84,23 @@ def test_switch_and_threshold_keep_the_classic_plan(pkg, monkeypatch):
     monkeypatch.delenv("DX_ATTN_STREAMK_16BIT")
     r = gpu_step_and_compare(pkg, cfg, check_twice=False)
     assert "stream_k_ctas" not in r["plan"]
+
+
+@pytest.mark.parametrize("heads,tpb", [((8, 1), 64), ((64, 8), 128), ((16, 1), 32), ((12, 2), 64)])
+def test_token_major_kernel_ragged_batches(pkg, monkeypatch, heads, tpb):
+    """The tcgen05 token-major kernel under the same schedule (unit: its 128-token tile)."""
+    monkeypatch.setenv("DX_ATTN_TOK", "1")
+    cfg = pkg.workloads.DecodeConfig("sktok", 7, heads[0], heads[1], 128, torch.bfloat16, "fp8", tpb, 20, 3000, True, 78)
+    r = gpu_step_and_compare(pkg, cfg)
+    assert r["plan"]["kernel"] == "token_major_tcgen05" and r["plan"].get("stream_k_ctas", 0) > 0, r["plan"]
+
+
+def test_token_major_kernel_boundary_lengths_and_long_row(pkg, monkeypatch):
+    monkeypatch.setenv("DX_ATTN_TOK", "1")
+    lens = [0, 1, 31, 32, 33, 63, 64, 65, 95, 96, 127, 128, 129, 255, 256, 257, 517, 1023, 1024, 1025, 2047, 2048]
+    cfg = dataclasses.replace(pkg.workloads.CONFIGS["c4"], batch=len(lens))
+    r = gpu_step_and_compare(pkg, cfg, lengths=torch.tensor(lens, dtype=torch.int32))
+    assert r["plan"].get("stream_k_ctas", 0) > 0
+    cfg = pkg.workloads.DecodeConfig("sktok1", 1, 8, 1, 128, torch.bfloat16, "fp8", 128, 30000, 30000, True, 5)
+    r = gpu_step_and_compare(pkg, cfg)
+    assert r["plan"].get("stream_k_ctas", 0) > 100
