@@ -146,10 +146,31 @@ typedef struct dx_attn_generation_params
     /* device, T [num_heads] or NULL: ALiBi slopes of this rank's heads; score += slope * (slot - past length)
      * (decoderMaskedMultiheadAttentionTemplate.h:1890-1895, :2026).  Needs position_embedding_type 3 or 4. */
     const void* alibi_slopes;
+    /* optional tail 3: several new tokens per sequence in one step - the reference's Medusa mode
+     * (is_medusa_enabled; gptAttentionPlugin.cpp:541-556, :622-627, :646-650; gptAttentionCommon.cpp:195-239).
+     * input_seq_length = Q = number of draft tokens + 1 (0 and 1 both mean the usual single token).  With Q > 1:
+     *   attention_input / context_buf have num_requests * Q rows, row b * Q + t is token t of sequence b;
+     *   sequence_lengths[b] INCLUDES the Q new tokens, token t is stored at cache index sequence_lengths[b] - Q + t
+     *     (unfusedAttentionKernels_2_template.h:254-255);
+     *   host_past_key_value_lengths[b] = sequence_lengths[b] - Q;
+     *   token t attends to every earlier cache entry and to new token j where bit j of its mask row is set
+     *     (bit j of row t = bit j % 32 of word j / 32; tensorrt_llm/runtime/medusa_utils.py:50-82; its own bit t is set);
+     *   with a rotary embedding configured, token t is rotated at position
+     *     medusa_position_offsets[b * Q + t] + sequence_lengths[b] - Q (unfusedAttentionKernels_2_template.h:258-262).
+     * beam_width must be 1; no cyclic window shorter than the sequences, no sink tokens, no ALiBi, no dynamic
+     * rotary scaling (DX_ERR_UNSUPPORTED).  Unlike the reference (whose multi-token kernels take 16-bit caches only,
+     * decoderXQAImplPrecompiled.cpp:322-323) every cache type is served. */
+    int32_t input_seq_length;
+    int32_t reserved0; /* 0 */
+    /* device, int32 [num_requests, Q, (Q + 31) / 32] (plugin input medusa_packed_mask) */
+    const int32_t* medusa_packed_mask;
+    /* device, int32 [num_requests, Q] or NULL = all zero (plugin input medusa_position_offsets) */
+    const int32_t* medusa_position_offsets;
 } dx_attn_generation_params;
-/* sizes of dx_attn_generation_params without the optional tails (all three are accepted by the enqueue calls) */
-#define DX_ATTN_GENERATION_PARAMS_SIZE_V1 (sizeof(dx_attn_generation_params) - 3 * sizeof(void*))
-#define DX_ATTN_GENERATION_PARAMS_SIZE_V2 (sizeof(dx_attn_generation_params) - 2 * sizeof(void*))
+/* sizes of dx_attn_generation_params without the optional tails (all are accepted by the enqueue calls) */
+#define DX_ATTN_GENERATION_PARAMS_SIZE_V1 offsetof(dx_attn_generation_params, qkv_bias)
+#define DX_ATTN_GENERATION_PARAMS_SIZE_V2 offsetof(dx_attn_generation_params, context_lengths)
+#define DX_ATTN_GENERATION_PARAMS_SIZE_V3 offsetof(dx_attn_generation_params, input_seq_length)
 
 typedef struct dx_attn dx_attn_t;
 

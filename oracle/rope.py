@@ -24,8 +24,12 @@ def apply_bias_rope(qkv: torch.Tensor, sequence_lengths: torch.Tensor, *, num_he
                     head_size: int, position_embedding_type: int = 0, rotary_embedding_dim: int = 0,
                     rotary_embedding_base: float = 10000.0, rotary_embedding_scale_type: int = 0,
                     rotary_embedding_scale: float = 1.0, rotary_embedding_max_positions: int = 1024,
-                    qkv_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """qkv: T [B, (H + 2 Hkv) Dh] -> same shape, pre-processed as the decode kernels see it."""
+                    qkv_bias: Optional[torch.Tensor] = None, q_len: int = 1,
+                    position_offsets: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """qkv: T [B, (H + 2 Hkv) Dh] -> same shape, pre-processed as the decode kernels see it.
+    q_len > 1 (several new tokens per sequence, rows b * q_len + t; sequence_lengths has one entry per sequence
+    and includes the new tokens): row r is rotated at position_offsets.flatten()[r] + length - q_len
+    (unfusedAttentionKernels_2_template.h:258-262)."""
     B = qkv.shape[0]
     H, Hkv, Dh = num_heads, num_kv_heads, head_size
     T = qkv.dtype
@@ -37,7 +41,11 @@ def apply_bias_rope(qkv: torch.Tensor, sequence_lengths: torch.Tensor, *, num_he
     rot = rotary_embedding_dim
     f32 = torch.float32
     for b in range(B):
-        t_step = int(sequence_lengths[b]) - 1
+        t_step = int(sequence_lengths[b // q_len]) - 1
+        if q_len > 1:
+            assert rotary_embedding_scale_type != ROT_SCALE_DYNAMIC
+            off = int(position_offsets.flatten()[b]) if position_offsets is not None else b % q_len
+            t_step = t_step + 1 - q_len + off
         base = torch.tensor(rotary_embedding_base, dtype=f32)
         scale = torch.tensor(rotary_embedding_scale, dtype=f32)
         if position_embedding_type == POS_ROPE_GPT_NEOX:

@@ -105,7 +105,7 @@ bool read_params(const dx_attn_generation_params* in, dx_attn_generation_params&
     if (!in)
         return false;
     if (in->struct_size != sizeof(dx_attn_generation_params) && in->struct_size != DX_ATTN_GENERATION_PARAMS_SIZE_V1
-        && in->struct_size != DX_ATTN_GENERATION_PARAMS_SIZE_V2)
+        && in->struct_size != DX_ATTN_GENERATION_PARAMS_SIZE_V2 && in->struct_size != DX_ATTN_GENERATION_PARAMS_SIZE_V3)
         return false;
     memset(&out, 0, sizeof(out));
     memcpy(&out, in, in->struct_size);
@@ -385,6 +385,8 @@ int launch_prep(dx_attn* h, const dx_attn_generation_params& p, int nseq, cudaSt
     pa.bias = p.qkv_bias;
     pa.out = p.workspace;
     pa.seq_len = p.sequence_lengths;
+    pa.q_len = std::max(1, p.input_seq_length);
+    pa.pos_offsets = pa.q_len > 1 ? p.medusa_position_offsets : nullptr;
     pa.batch = nseq;
     pa.num_heads = c.num_heads;
     pa.num_kv_heads = c.num_kv_heads;
@@ -469,6 +471,7 @@ int enqueue_general(dx_attn* h, const dx_attn_generation_params& p, int max_past
     g.cyclic_len = cyclic_len;
     g.sink = sink;
     g.softmax_scale_log2 = 1.4426950408889634f / (sqrtf((float) c.head_size) * c.q_scaling);
+    g.q_len = 1;
     void* args[] = {&g};
     st = check_cuda(h, cudaLaunchKernel(h->k_general.attn, dim3(c.num_heads, nseq), dim3(128), args,
                            (size_t) h->k_general.smem, stream));
@@ -476,6 +479,78 @@ int enqueue_general(dx_attn* h, const dx_attn_generation_params& p, int max_past
         return st;
     h->launches.fetch_add(1);
     st = check_cuda(h, cudaLaunchKernel(h->k_general.append, dim3(c.num_kv_heads, nseq), dim3(32), args, 0, stream));
+    if (st != DX_OK)
+        return st;
+    h->launches.fetch_add(1);
+    return DX_OK;
+}
+
+// Several new tokens per sequence (the reference's Medusa mode): append all of them, then one CTA per
+// (token, q head) reads the cache under the token's mask row.
+int enqueue_multi_token(dx_attn* h, const dx_attn_generation_params& p, int max_past, void* cuda_stream)
+{
+    const dx_attn_config& c = h->cfg;
+    const int Q = p.input_seq_length;
+    if (!h->k_general.multi)
+        return DX_ERR_UNSUPPORTED;
+    if (Q > 4096 || !p.medusa_packed_mask || ((uintptr_t) p.medusa_packed_mask & 3)
+        || ((uintptr_t) p.medusa_position_offsets & 3))
+        return DX_ERR_BAD_ARG;
+    // the reference runs this mode on its XQA kernels only: beam width 1, no sliding window, no sink tokens
+    // (decoderXQARunner.h:87-159), and asserts when they do not apply (gptAttentionCommon.cpp:1225-1228)
+    const int64_t need = (int64_t) max_past + Q;
+    if (p.beam_width != 1 || p.sink_token_length > 0 || c.position_embedding_type >= POS_ALIBI
+        || p.cyclic_attention_window_size < need || p.max_attention_window < need)
+        return DX_ERR_UNSUPPORTED;
+    if (c.position_embedding_type != POS_LEARNED_ABSOLUTE && c.rotary_embedding_scale_type == ROT_SCALE_DYNAMIC)
+        return DX_ERR_UNSUPPORTED; // (the reference's multi-token pre-processing rescales the base at every length)
+    if (need > (int64_t) p.max_blocks_per_sequence * c.tokens_per_block)
+        return DX_ERR_BAD_ARG; // the table cannot hold that many tokens
+    const int64_t rows64 = (int64_t) p.num_requests * Q;
+    if (rows64 > 65535)
+        return DX_ERR_UNSUPPORTED; // grid.y
+    const int rows = (int) rows64;
+    const size_t prep = prep_bytes(h, rows);
+    if (prep)
+    {
+        if (!p.workspace || ((uintptr_t) p.workspace & 127))
+            return p.workspace ? DX_ERR_BAD_ARG : DX_ERR_WORKSPACE;
+        if (p.workspace_bytes < prep)
+            return DX_ERR_WORKSPACE;
+    }
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+    int st = check_cuda(h, cudaSetDevice(c.device));
+    if (st == DX_OK && prep)
+        st = launch_prep(h, p, rows, stream);
+    if (st != DX_OK)
+        return st;
+
+    GeneralArgs g{};
+    g.qkv = prep ? p.workspace : p.attention_input;
+    g.out = p.context_buf;
+    g.seq_len = p.sequence_lengths;
+    g.block_ptrs = p.block_pointers;
+    g.scale_orig_quant = p.kv_scale_orig_quant;
+    g.scale_quant_orig = p.kv_scale_quant_orig;
+    g.num_heads = c.num_heads;
+    g.num_kv_heads = c.num_kv_heads;
+    g.max_blocks_per_seq = p.max_blocks_per_sequence;
+    g.tpb_log2 = h->tpb_log2;
+    g.beam_width = 1;
+    g.max_attention_window = p.max_attention_window;
+    g.cyclic_window = p.cyclic_attention_window_size;
+    g.cyclic_len = p.max_blocks_per_sequence * c.tokens_per_block; // no wrap: slot = token index
+    g.sink = 0;
+    g.softmax_scale_log2 = 1.4426950408889634f / (sqrtf((float) c.head_size) * c.q_scaling);
+    g.q_len = Q;
+    g.packed_mask = p.medusa_packed_mask;
+    void* args[] = {&g};
+    st = check_cuda(h, cudaLaunchKernel(h->k_general.append, dim3(c.num_kv_heads, rows), dim3(32), args, 0, stream));
+    if (st != DX_OK)
+        return st;
+    h->launches.fetch_add(1);
+    st = check_cuda(h, cudaLaunchKernel(h->k_general.multi, dim3(c.num_heads, rows), dim3(128), args,
+                           (size_t) h->k_general.smem, stream));
     if (st != DX_OK)
         return st;
     h->launches.fetch_add(1);
@@ -741,6 +816,10 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     }
     if (max_past < 0)
         return DX_ERR_BAD_ARG;
+    if (p.input_seq_length < 0 || p.reserved0 != 0)
+        return DX_ERR_BAD_ARG;
+    if (p.input_seq_length > 1)
+        return enqueue_multi_token(h, p, max_past, cuda_stream);
     // Beam search, a window shorter than some sequence, sink tokens and ALiBi go to the feature-complete kernel.
     const bool general = p.beam_width > 1 || p.sink_token_length > 0 || alibi
         || p.cyclic_attention_window_size < max_past + 1 || p.max_attention_window < max_past + 1;
@@ -876,6 +955,8 @@ int dx_attn_enqueue_generation_host(
         return DX_OK;
     if (!p.attention_input || !p.sequence_lengths || !p.block_pointers || !p.context_buf)
         return DX_ERR_BAD_ARG;
+    if (p.input_seq_length > 1)
+        return DX_ERR_UNSUPPORTED; // several tokens per sequence: device buffers only
     const size_t B = (size_t) p.num_requests * (size_t) std::max(1, p.beam_width); // sequences
     const size_t qkv_bytes = B * (size_t) (c.num_heads + 2 * c.num_kv_heads) * c.head_size * 2;
     const size_t out_bytes = B * (size_t) c.num_heads * c.head_size * 2;

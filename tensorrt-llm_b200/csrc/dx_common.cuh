@@ -63,6 +63,10 @@ struct GeneralArgs
     int32_t cyclic_len;    // period of the non-sink part of the cache
     int32_t sink;
     float softmax_scale_log2;
+    // several new tokens per sequence (the reference's Medusa mode): qkv / out row r is token r % q_len of sequence
+    // r / q_len; seq_len includes all q_len new tokens
+    int32_t q_len;               // 1: the usual single token
+    const int32_t* packed_mask;  // [B, q_len, (q_len + 31) / 32]: bit j of row t = token t attends new token j
 };
 
 __host__ __device__ __forceinline__ int cyclic_slot(int tok, int sink, int cyclic_len)

@@ -11,6 +11,7 @@ static GeneralKernels mk()
     GeneralKernels k;
     k.attn = reinterpret_cast<const void*>(&general_decode_kernel<T, CACHE, DH>);
     k.append = reinterpret_cast<const void*>(&kv_append_token_kernel<T, CACHE, DH>);
+    k.multi = reinterpret_cast<const void*>(&multi_token_decode_kernel<T, CACHE, DH>);
     k.smem = (4 * MhaTraits<CACHE, DH>::TPW * (DH + 2)) * (int) sizeof(float);
     return k;
 }

@@ -159,7 +159,8 @@ __global__ void __launch_bounds__(128) general_decode_kernel(const GeneralArgs a
 }
 
 // Writes the new token's K and V rows (quantised as the reference stores them) at its cyclic slot.
-// Grid (Hkv, B), one warp.
+// Grid (Hkv, B * q_len), one warp: row bb of QKV is token bb % q_len of sequence bb / q_len and goes to cache index
+// sequence length - q_len + token (unfusedAttentionKernels_2_template.h:254-255, :330-387).
 template <typename T, int CACHE, int DH>
 __global__ void __launch_bounds__(32) kv_append_token_kernel(const GeneralArgs a)
 {
@@ -168,7 +169,8 @@ __global__ void __launch_bounds__(32) kv_append_token_kernel(const GeneralArgs a
     const int hk = blockIdx.x, bb = blockIdx.y, lane = threadIdx.x;
     if (lane >= LPR)
         return;
-    const int tlength = a.seq_len[bb] - 1;
+    const int seq = bb / a.q_len, tok = bb % a.q_len;
+    const int tlength = a.seq_len[seq] - a.q_len + tok;
     const int slot = cyclic_slot(tlength, a.sink, a.cyclic_len);
     const int tpb_log2 = a.tpb_log2, tpb_mask = (1 << tpb_log2) - 1;
     const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
@@ -178,10 +180,132 @@ __global__ void __launch_bounds__(32) kv_append_token_kernel(const GeneralArgs a
     const uint4 kq = make_cache_vec<T, CACHE, EPL>(qkv_b + (size_t) (a.num_heads + hk) * DH + lane * EPL, sc_f, sc_t);
     const uint4 vq = make_cache_vec<T, CACHE, EPL>(
         qkv_b + (size_t) (a.num_heads + a.num_kv_heads + hk) * DH + lane * EPL, sc_f, sc_t);
-    const int64_t* rowp = a.block_ptrs + (int64_t) bb * 2 * a.max_blocks_per_seq + (slot >> tpb_log2);
+    const int64_t* rowp = a.block_ptrs + (int64_t) seq * 2 * a.max_blocks_per_seq + (slot >> tpb_log2);
     const size_t off = (size_t) hk * ((size_t) ROW_BYTES << tpb_log2) + (size_t) (slot & tpb_mask) * ROW_BYTES + lane * 16;
     *reinterpret_cast<uint4*>(reinterpret_cast<char*>(__ldg(rowp)) + off) = kq;
     *reinterpret_cast<uint4*>(reinterpret_cast<char*>(__ldg(rowp + a.max_blocks_per_seq)) + off) = vq;
+}
+
+// Several new tokens per sequence in one step (the reference's Medusa mode, which it serves with pre-compiled
+// multi-query-token XQA kernels: decoderXQAImplPrecompiled.cpp:315-338).  Launched BEHIND kv_append_token_kernel:
+// all q_len new tokens are in the cache, and token t of a sequence attends to the cache entries before the step
+// and to new token j where bit j of its packed mask row is set.  One CTA per (token row, q head), the lane
+// mapping and the merge of general_decode_kernel.  No beams, no cyclic wrap, no ALiBi.
+template <typename T, int CACHE, int DH>
+__global__ void __launch_bounds__(128) multi_token_decode_kernel(const GeneralArgs a)
+{
+    using Tr = MhaTraits<CACHE, DH>;
+    constexpr int LPR = Tr::LPR, TPW = Tr::TPW, EPL = Tr::EPL, ROW_BYTES = Tr::ROW_BYTES;
+    constexpr int U = 2;
+    constexpr int NSTATE = 4 * TPW;
+
+    const int h = blockIdx.x, bb = blockIdx.y;
+    const int seq = bb / a.q_len, tok = bb % a.q_len;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane / LPR, sl = lane % LPR;
+    const int G = a.num_heads / a.num_kv_heads;
+    const int hk = h / G;
+    const int tpb_log2 = a.tpb_log2, tpb_mask = (1 << tpb_log2) - 1;
+
+    const int total = a.seq_len[seq];
+    const int past = total - a.q_len;
+    const int32_t* mask_row = a.packed_mask + ((size_t) seq * a.q_len + tok) * ((a.q_len + 31) >> 5);
+
+    const float deq = (CACHE == CACHE_T) ? 1.f : __ldg(a.scale_quant_orig);
+    const float sscale = deq * a.softmax_scale_log2;
+    const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
+    float q[EPL];
+    {
+        const T* qp = reinterpret_cast<const T*>(a.qkv) + (size_t) bb * qkv_stride + (size_t) h * DH + sl * EPL;
+#pragma unroll
+        for (int i = 0; i < EPL; i += 2)
+        {
+            const float2 v = TypeOps<T>::unpack2(*reinterpret_cast<const uint32_t*>(qp + i));
+            q[i] = v.x;
+            q[i + 1] = v.y;
+        }
+    }
+    float m = -INFINITY, l = 0.f, o[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i)
+        o[i] = 0.f;
+
+    const int64_t* krow = a.block_ptrs + (int64_t) seq * 2 * a.max_blocks_per_seq;
+    const size_t head_off = (size_t) hk * ((size_t) ROW_BYTES << tpb_log2) + sl * 16;
+    const int step = 4 * TPW * U;
+    for (int base = 0; base < total; base += step)
+    {
+        uint4 kraw[U], vraw[U];
+        bool valid[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+        {
+            const int slot = base + (warp * U + u) * TPW + sub;
+            const int s = min(slot, total - 1);
+            valid[u] = slot < past;
+            if (slot >= past && slot < total)
+                valid[u] = (__ldg(mask_row + ((slot - past) >> 5)) >> ((slot - past) & 31)) & 1;
+            const int64_t* rowp = krow + (s >> tpb_log2);
+            const size_t off = head_off + (size_t) (s & tpb_mask) * ROW_BYTES;
+            kraw[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(__ldg(rowp)) + off);
+            vraw[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(__ldg(rowp + a.max_blocks_per_seq)) + off);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+        {
+            float kf[EPL], vf[EPL];
+            dequant_vec<T, CACHE, EPL>(kraw[u], kf);
+            dequant_vec<T, CACHE, EPL>(vraw[u], vf);
+            float d = 0.f;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i)
+                d = fmaf(q[i], kf[i], d);
+#pragma unroll
+            for (int x = LPR / 2; x >= 1; x >>= 1)
+                d += __shfl_xor_sync(0xffffffffu, d, x);
+            if (valid[u])
+            {
+                const float s = d * sscale;
+                const float mn = fmaxf(m, s);
+                const float alpha = fast_exp2(m - mn), p = fast_exp2(s - mn);
+                m = mn;
+                l = fmaf(l, alpha, p);
+#pragma unroll
+                for (int i = 0; i < EPL; ++i)
+                    o[i] = fmaf(o[i], alpha, p * vf[i]);
+            }
+        }
+    }
+
+    // ---- merge the NSTATE running states ----
+    extern __shared__ __align__(16) unsigned char smem_g[];
+    float* st_o = reinterpret_cast<float*>(smem_g); // [NSTATE][DH]
+    float* st_m = st_o + NSTATE * DH;                // [NSTATE]
+    float* st_l = st_m + NSTATE;                     // [NSTATE]
+    const int state = warp * TPW + sub;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i)
+        st_o[state * DH + sl * EPL + i] = o[i];
+    if (sl == 0)
+    {
+        st_m[state] = m;
+        st_l[state] = l;
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < DH; d += blockDim.x)
+    {
+        float M = -INFINITY;
+        for (int s = 0; s < NSTATE; ++s)
+            M = fmaxf(M, st_m[s]);
+        float L = 0.f, acc = 0.f;
+        for (int s = 0; s < NSTATE; ++s)
+        {
+            const float f = (st_m[s] == -INFINITY) ? 0.f : fast_exp2(st_m[s] - M);
+            L = fmaf(st_l[s], f, L);
+            acc = fmaf(st_o[s * DH + d], f, acc);
+        }
+        reinterpret_cast<T*>(a.out)[((size_t) bb * a.num_heads + h) * DH + d] = TypeOps<T>::from_float(acc * deq / L);
+    }
 }
 
 } // namespace dx

@@ -19,7 +19,8 @@ KernelInfo tok_kernel_info(int dtype, int dh, int group); // FP8 cache, Dh 128, 
 struct GeneralKernels
 {
     const void* attn = nullptr;   // general_decode_kernel: grid (H, B), 128 threads, `smem` dynamic bytes
-    const void* append = nullptr; // kv_append_token_kernel: grid (Hkv, B), 32 threads
+    const void* append = nullptr; // kv_append_token_kernel: grid (Hkv, B * q_len), 32 threads
+    const void* multi = nullptr;  // multi_token_decode_kernel: grid (H, B * q_len), 128 threads, `smem` dynamic bytes
     int smem = 0;
 };
 GeneralKernels general_kernel_info(int dtype, int cache, int dh);

@@ -40,7 +40,11 @@ struct PrepArgs
     const void* bias;  // T [(H + 2 Hkv) Dh] or nullptr
     void* out;         // T [B, (H + 2 Hkv) Dh]
     const int32_t* seq_len;
-    int32_t batch, num_heads, num_kv_heads, head_size;
+    // several new tokens per sequence: row r is token r % q_len of sequence r / q_len, rotated at position
+    // pos_offsets[r] (or r % q_len) + sequence length - q_len (unfusedAttentionKernels_2_template.h:254-262)
+    const int32_t* pos_offsets;
+    int32_t q_len; // 1: the usual single token at position sequence length - 1
+    int32_t batch, num_heads, num_kv_heads, head_size; // batch: rows
     int32_t pos_type, rot_dim, rot_scale_type, rot_max_positions;
     float rot_base, rot_scale;
 };
@@ -58,7 +62,9 @@ __global__ void __launch_bounds__(256) qkv_bias_rope_kernel(const PrepArgs a)
     const int rem = (int) (idx % per_seq);
     const int head = rem / half_dh, p = rem % half_dh;
     const bool is_v = head >= a.num_heads + a.num_kv_heads;
-    const int t_step = a.seq_len[b] - 1;
+    int t_step = a.seq_len[b / a.q_len] - 1;
+    if (a.q_len > 1)
+        t_step += 1 - a.q_len + (a.pos_offsets ? a.pos_offsets[b] : b % a.q_len);
 
     // which two channels this thread owns
     const bool rope = !is_v && a.pos_type != POS_LEARNED_ABSOLUTE && 2 * p < a.rot_dim;

@@ -40,6 +40,9 @@ struct EnqueueGenerationParams
     float const* kv_scale_orig_quant = nullptr;
     float const* kv_scale_quant_orig = nullptr;
     T const* alibi_slopes = nullptr; // needs an ALiBi position embedding type (setPositionEmbedding)
+    // Medusa mode (gptAttentionCommon.h:162-165): input_seq_length > 1 new tokens per sequence under a packed mask
+    int32_t const* medusa_packed_mask = nullptr;
+    int32_t const* medusa_position_offsets = nullptr;
     T* context_buf = nullptr;
     void* key_value_cache = nullptr; // contiguous cache: not supported, must be nullptr
     void* block_pointers = nullptr;
@@ -131,8 +134,8 @@ public:
     {
         if (!mHandle)
             return DX_ERR_BAD_ARG;
-        if (params.key_value_cache || params.input_seq_length != 1)
-            return DX_ERR_UNSUPPORTED; // contiguous cache, multi-token (Medusa) queries
+        if (params.key_value_cache)
+            return DX_ERR_UNSUPPORTED; // contiguous cache
         dx_attn_generation_params p{};
         p.struct_size = sizeof(p);
         p.attention_input = params.attention_input;
@@ -155,6 +158,9 @@ public:
         p.qkv_bias = params.qkv_bias;
         p.context_lengths = params.context_lengths;
         p.alibi_slopes = params.alibi_slopes;
+        p.input_seq_length = params.input_seq_length;
+        p.medusa_packed_mask = params.medusa_packed_mask;
+        p.medusa_position_offsets = params.medusa_position_offsets;
         return dx_attn_enqueue_generation(mHandle, &p, stream);
     }
 

@@ -77,7 +77,9 @@ class _GenParams(ctypes.Structure):
                 ("kv_scale_quant_orig", ctypes.c_void_p), ("context_buf", ctypes.c_void_p),
                 ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
                 ("cache_indir", ctypes.c_void_p), ("qkv_bias", ctypes.c_void_p),
-                ("context_lengths", ctypes.c_void_p), ("alibi_slopes", ctypes.c_void_p)]
+                ("context_lengths", ctypes.c_void_p), ("alibi_slopes", ctypes.c_void_p),
+                ("input_seq_length", ctypes.c_int32), ("reserved0", ctypes.c_int32),
+                ("medusa_packed_mask", ctypes.c_void_p), ("medusa_position_offsets", ctypes.c_void_p)]
 
 
 EXPORTED_SYMBOLS = [
@@ -242,8 +244,9 @@ class GPTAttentionPlugin:
     def _params(self, qkv, sequence_length, host_past_key_value_lengths, kv_cache_block_pointers,
                 kv_orig_quant_scale, kv_quant_orig_scale, out, workspace, max_attention_window,
                 host_kv_cache_block_pointers=None, cache_indirection=None, beam_width=1, sink_token_length=0,
-                qkv_bias=None, cyclic_attention_window_size=None, context_lengths=None, alibi_slopes=None):
-        B = qkv.shape[0]
+                qkv_bias=None, cyclic_attention_window_size=None, context_lengths=None, alibi_slopes=None,
+                input_seq_length=1, medusa_packed_mask=None, medusa_position_offsets=None):
+        B = qkv.shape[0] // max(1, input_seq_length)
         M = kv_cache_block_pointers.shape[-1]
         hp = host_past_key_value_lengths
         max_past = int(hp.max()) if hp is not None and hp.numel() else 0
@@ -271,6 +274,9 @@ class GPTAttentionPlugin:
         p.qkv_bias = _ptr(qkv_bias)
         p.context_lengths = _ptr(context_lengths)
         p.alibi_slopes = _ptr(alibi_slopes)
+        p.input_seq_length = input_seq_length
+        p.medusa_packed_mask = _ptr(medusa_packed_mask)
+        p.medusa_position_offsets = _ptr(medusa_position_offsets)
         return p, max_past
 
     def _ensure_workspace(self, batch: int, max_past: int, device) -> Optional[torch.Tensor]:
@@ -293,18 +299,24 @@ class GPTAttentionPlugin:
                            cyclic_attention_window_size: Optional[int] = None,
                            context_lengths: Optional[torch.Tensor] = None,
                            alibi_slopes: Optional[torch.Tensor] = None,
+                           medusa_packed_mask: Optional[torch.Tensor] = None,
+                           medusa_position_offsets: Optional[torch.Tensor] = None,
                            stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
         """qkv: T [B, (H+2Hkv)*Dh] (device); sequence_length: int32 [B] (device, includes the new token);
         host_past_key_value_lengths: int32 [B] (host); kv_cache_block_pointers: int64 [B, 2, M] (device).
         Appends the new token to the cache and returns the attention output T [B, H*Dh].  Asynchronous.
         Beam search: B = batch * beam_width, cache_indirection int32 [B, max_attention_window] and
         context_lengths int32 [B] on the device.  Sliding window: cyclic_attention_window_size (and
-        sink_token_length).  ALiBi: alibi_slopes T [H] on the device (plugin built with an ALiBi type)."""
+        sink_token_length).  ALiBi: alibi_slopes T [H] on the device (plugin built with an ALiBi type).
+        Several new tokens per sequence (the reference's Medusa mode): medusa_packed_mask int32
+        [B, Q, ceil(Q / 32)] on the device (and optionally medusa_position_offsets int32 [B, Q]); qkv and the
+        result then have B * Q rows and sequence_length includes all Q new tokens."""
         if not qkv.is_cuda:
             raise DecodeAttnError(DX_ERR_BAD_ARG, "enqueue_generation needs device tensors (no CPU path exists)")
         if qkv.dtype != self.dtype:
             raise DecodeAttnError(DX_ERR_BAD_ARG, "qkv dtype")
-        B = qkv.shape[0]
+        B = qkv.shape[0]  # rows: sequences x new tokens per sequence
+        q_len = 1 if medusa_packed_mask is None else int(medusa_packed_mask.shape[-2])
         if out is None:
             out = torch.empty(B, self.num_heads * self.head_size, dtype=self.dtype, device=qkv.device)
         hp = host_past_key_value_lengths.to(torch.int32).contiguous()
@@ -314,7 +326,9 @@ class GPTAttentionPlugin:
         p, _ = self._params(qkv, sequence_length, hp, kv_cache_block_pointers, kv_orig_quant_scale,
                             kv_quant_orig_scale, out, workspace, max_attention_window,
                             host_kv_cache_block_pointers, cache_indirection, beam_width, sink_token_length, qkv_bias,
-                            cyclic_attention_window_size, context_lengths, alibi_slopes)
+                            cyclic_attention_window_size, context_lengths, alibi_slopes, q_len,
+                            None if medusa_packed_mask is None else medusa_packed_mask.contiguous(),
+                            None if medusa_position_offsets is None else medusa_position_offsets.contiguous())
         s = stream if stream is not None else torch.cuda.current_stream(qkv.device)
         st = self.lib.dx_attn_enqueue_generation(self._h, ctypes.byref(p), ctypes.c_void_p(s.cuda_stream))
         if st != DX_OK:

@@ -13,6 +13,9 @@ Outputs (small, committed):
                             reference known-answer test's inputs (srand(42), scale 0.1;
                             cpp/tests/runtime/transposeKVKernelTest.cpp:152, :213-225) with the
                             expectations of its castTo<> functions (:76-88).
+  medusa_mask_golden.json - for a few draft trees: the dense attention mask, the packed mask and the position
+                            offsets that the reference's tensorrt_llm/runtime/medusa_utils.py builds (loaded by
+                            file path; only its CPU functions are called).
 """
 import ctypes
 import importlib.util
@@ -102,7 +105,47 @@ def quant_vectors():
     np.savez_compressed(HERE / "quant_golden.npz", **out)
 
 
+def medusa_masks():
+    import types
+    # the module's only package import is the reference logger: a stand-in keeps the import self-contained
+    pkg = types.ModuleType("tensorrt_llm")
+    log = types.ModuleType("tensorrt_llm.logger")
+    log.logger = types.SimpleNamespace(warning=lambda *a, **k: None, info=lambda *a, **k: None)
+    pkg.logger = log
+    sys.modules.setdefault("tensorrt_llm", pkg)
+    sys.modules.setdefault("tensorrt_llm.logger", log)
+    path = REF / "tensorrt_llm" / "runtime" / "medusa_utils.py"
+    spec = importlib.util.spec_from_file_location("ref_medusa_utils", path)
+    m = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(m)
+    import copy
+    trees = {
+        "chain3": [[0], [0, 0], [0, 0, 0]],
+        "small": [[0], [1], [0, 0], [0, 1], [1, 0], [0, 0, 0]],
+        "wide": [[i] for i in range(6)] + [[i, j] for i in range(4) for j in range(3)]
+                + [[i, j, 0] for i in range(3) for j in range(2)] + [[0, 0, 0, k] for k in range(12)],
+    }
+    out = {}
+    for name, choices in trees.items():
+        sorted_choices = sorted(copy.deepcopy(choices), key=m.path_sorting_key)
+        heads = max(len(c) for c in sorted_choices)
+        paths, level_counts, _, _ = m.choices_2_paths(heads, sorted_choices)
+        paths = sorted(paths, key=m.path_sorting_key)
+        topks = m.get_medusa_topks(heads, paths)
+        tree_ids, pos_off, tree_paths = m.get_medusa_tree(heads, topks, level_counts, paths)
+        n = len(tree_ids)
+        mpaths = torch.stack([torch.tensor([-1] + p + ([-2] * (heads - len(p)))) for p in tree_paths]) + 1
+        ids = torch.tensor([-1] + list(tree_ids)) + 1
+        offsets = torch.tensor([-1] + list(pos_off)) + 1
+        dense = m.get_medusa_mask(ids, mpaths)           # [n + 1, n + 1], row t: tokens token t attends to
+        packed = m.get_packed_mask(n, dense[1:, 1:])     # int32 [n + 1, ceil((n + 1) / 32)]
+        out[name] = {"choices": choices, "num_medusa_tokens": n, "dense_mask": dense.to(torch.int32).tolist(),
+                     "packed_mask": packed.tolist(), "position_offsets": offsets.tolist()}
+    (HERE / "medusa_mask_golden.json").write_text(json.dumps(out))
+
+
 if __name__ == "__main__":
     page_tables()
     quant_vectors()
+    medusa_masks()
     print("written:", [p.name for p in HERE.iterdir()])
