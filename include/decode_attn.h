@@ -182,7 +182,8 @@ void dx_attn_destroy(dx_attn_t* handle);
 
 /* Replaces GPTAttentionPluginCommon::getWorkspaceSizeForGeneration (gptAttentionCommon.cpp:585-626).
  * Upper bound for any call with num_requests <= batch; 0 when multi_block_mode is off and no in-step
- * pre-processing (bias / rotary embedding) is configured. */
+ * pre-processing (bias / rotary embedding) is configured.  `batch` counts rows of attention_input: sequences x beams,
+ * and x input_seq_length for calls with several new tokens per sequence (the reference sizes by total_num_seq too). */
 size_t dx_attn_workspace_size(const dx_attn_t* handle, int32_t batch, int32_t max_past_len);
 
 /* Replaces GPTAttentionPluginCommon::enqueueGeneration (gptAttentionCommon.cpp:1159-1364). */

@@ -198,11 +198,8 @@ __global__ void __launch_bounds__(128, Gqa16Traits<DH>::MIN_BLOCKS) gqa16_decode
             cp_async_mbar_arrive_noinc(&bars[(ring_base + i) % STAGES]);
         };
 
-        const int my_groups = (n_groups > warp) ? (n_groups - warp + NWARPS - 1) / NWARPS : 0;
-        for (int i = 0; i < min(STAGES, my_groups); ++i)
-            issue(i);
-
-        // ---- Q as A fragments: rows = heads g and g + 8, k-step j covers channels 16 j .. 16 j + 15 ----
+        // ---- Q as A fragments: rows = heads g and g + 8, k-step j covers channels 16 j .. 16 j + 15.  Requested
+        // before the first ring stages: behind those tens of KB per warp the same loads would wait for all of them ----
         const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
         const T* qkv_b = reinterpret_cast<const T*>(a.qkv) + (size_t) b * qkv_stride;
         uint32_t qa[KSTEPS][4];
@@ -219,6 +216,10 @@ __global__ void __launch_bounds__(128, Gqa16Traits<DH>::MIN_BLOCKS) gqa16_decode
                 qa[j][3] = v1 ? q1[8 * j + 4 + t] : 0u;
             }
         }
+        const int my_groups = (n_groups > warp) ? (n_groups - warp + NWARPS - 1) / NWARPS : 0;
+        for (int i = 0; i < min(STAGES, my_groups); ++i)
+            issue(i);
+
         const float sscale = a.softmax_scale_log2;
 
         // Per-lane ldmatrix row addresses inside a slab.

@@ -269,12 +269,27 @@ __global__ void __launch_bounds__(128, gqa_min_blocks<CACHE, DH, H16>()) gqa_dec
             partition_of(a.seq_len[b], a.chunk_tokens, chunk, chunk_start, ctoks, np);
             final_out = a.nsplit == 1;
         }
+        const int nh = min(16, G - hg * 16); // q heads handled in this piece
+        const int head0 = hk * G + hg * 16;  // first of them
+        // The q rows of this thread are requested before anything else of the piece: behind the first ring
+        // stages of K / V (tens of KB per warp) the same loads would wait for all of those bytes.
+        const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
+        const T* qkv_b = reinterpret_cast<const T*>(a.qkv) + (size_t) b * qkv_stride;
+        uint4 q_raw[NR][QV / 8];
+#pragma unroll
+        for (int r = 0; r < NR; ++r)
+        {
+            const int hl = g + 8 * r; // head within this CTA
+            const T* qp = qkv_b + (size_t) (head0 + min(hl, nh - 1)) * DH + t * QV;
+#pragma unroll
+            for (int i = 0; i < QV / 8; ++i)
+                q_raw[r][i] = *reinterpret_cast<const uint4*>(qp + 8 * i);
+        }
+        const float deq = __ldg(a.scale_quant_orig);
         const int total = a.seq_len[b];
         ctoks = max(0, min(ctoks, total - chunk_start)); // the schedule counts host lengths; the device length decides
         const int n_groups = (ctoks + TG - 1) / TG;
         const int new_pos = total - 1;
-        const int nh = min(16, G - hg * 16); // q heads handled in this piece
-        const int head0 = hk * G + hg * 16;  // first of them
 
         const int64_t* krow = a.block_ptrs + (int64_t) b * 2 * a.max_blocks_per_seq;
         const int64_t* vrow = krow + a.max_blocks_per_seq;
@@ -332,9 +347,6 @@ __global__ void __launch_bounds__(128, gqa_min_blocks<CACHE, DH, H16>()) gqa_dec
         // of Dh chosen so that a K fragment is one (Dh 64) or two (Dh 128) 16-byte shared loads.
         //   <= 8 heads : one fragment set, rows 0..7 = high parts, rows 8..15 = low parts of head g
         //   16 heads   : two fragment sets (high, low), rows = heads g and g + 8 ----
-        const float deq = __ldg(a.scale_quant_orig);
-        const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
-        const T* qkv_b = reinterpret_cast<const T*>(a.qkv) + (size_t) b * qkv_stride;
         // FP8 cache: Q stays 16-bit (f16 A fragments, one k16 step per 4 channels of a thread);
         // INT8 cache: 8-bit high/low fragments as described above.
         constexpr int KS16 = DH / 16;
@@ -347,11 +359,10 @@ __global__ void __launch_bounds__(128, gqa_min_blocks<CACHE, DH, H16>()) gqa_dec
             const int hl = g + 8 * r; // head within this CTA
             if (hl < nh)
             {
-                const T* qp = qkv_b + (size_t) (head0 + hl) * DH + t * QV;
 #pragma unroll
                 for (int i = 0; i < QV; i += 8)
                 {
-                    const uint4 raw = *reinterpret_cast<const uint4*>(qp + i);
+                    const uint4 raw = q_raw[r][i / 8];
                     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
                     for (int j = 0; j < 4; ++j)

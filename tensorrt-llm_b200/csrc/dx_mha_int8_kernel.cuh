@@ -101,6 +101,15 @@ __global__ void __launch_bounds__(128) mha_int8_decode_kernel(const AttnArgs a)
         }
     };
 
+    // this lane's q channels are requested before the first ring stages: behind those bulk copies (tens of KB per
+    // warp) the same loads would wait for all of their bytes
+    const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
+    const T* qkv_b = reinterpret_cast<const T*>(a.qkv) + (size_t) b * qkv_stride;
+    uint4 q_raw[16 / 8];
+#pragma unroll
+    for (int i = 0; i < 16 / 8; ++i)
+        q_raw[i] = *reinterpret_cast<const uint4*>(qkv_b + h * DH + sl * 16 + 8 * i);
+
     const int my_groups = (n_groups > warp) ? (n_groups - warp + NWARPS - 1) / NWARPS : 0;
     if (lane == 0)
     {
@@ -110,17 +119,14 @@ __global__ void __launch_bounds__(128) mha_int8_decode_kernel(const AttnArgs a)
 
     // ---- q: 16 channels per lane, quantised per head into high + low int8 parts ----
     const float deq = __ldg(a.scale_quant_orig);
-    const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
-    const T* qkv_b = reinterpret_cast<const T*>(a.qkv) + (size_t) b * qkv_stride;
     uint32_t qhi[4], qlo[4];
     float sfac;
     {
         float qv[16];
-        const T* qp = qkv_b + h * DH + sl * 16;
 #pragma unroll
         for (int i = 0; i < 16; i += 8)
         {
-            const uint4 r = *reinterpret_cast<const uint4*>(qp + i);
+            const uint4 r = q_raw[i / 8];
             const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j)

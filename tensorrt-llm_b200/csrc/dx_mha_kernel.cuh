@@ -153,6 +153,15 @@ __global__ void __launch_bounds__(128) mha_decode_kernel(const AttnArgs a)
         }
     };
 
+    // this lane's q channels are requested before the first ring stages: behind those bulk copies (tens of KB per
+    // warp) the same loads would wait for all of their bytes
+    const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
+    const T* qkv_b = reinterpret_cast<const T*>(a.qkv) + (size_t) b * qkv_stride;
+    uint4 q_raw[EPL / 8];
+#pragma unroll
+    for (int i = 0; i < EPL / 8; ++i)
+        q_raw[i] = *reinterpret_cast<const uint4*>(qkv_b + h * DH + sl * EPL + 8 * i);
+
     const int my_groups = (n_groups > warp) ? (n_groups - warp + NWARPS - 1) / NWARPS : 0;
     if (lane == 0)
     {
@@ -162,16 +171,13 @@ __global__ void __launch_bounds__(128) mha_decode_kernel(const AttnArgs a)
 
     // q, pre-multiplied by the softmax scale (log2 units) and the K dequantisation scale.
     const float deq = (CACHE == CACHE_T) ? 1.f : __ldg(a.scale_quant_orig);
-    const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
-    const T* qkv_b = reinterpret_cast<const T*>(a.qkv) + (size_t) b * qkv_stride;
     float qf[EPL];
     {
-        const T* qp = qkv_b + h * DH + sl * EPL;
         const float qs = a.softmax_scale_log2 * deq;
 #pragma unroll
         for (int i = 0; i < EPL; i += 8)
         {
-            uint4 r = *reinterpret_cast<const uint4*>(qp + i);
+            const uint4 r = q_raw[i / 8];
             const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j)
