@@ -20,6 +20,25 @@ __device__ __forceinline__ void merge_row(const AttnArgs& a, int row, int n, int
     constexpr int VPL = DH / 32; // floats per lane (2 or 4)
     // (m, l) of up to 32 partitions per pass, one per lane: all loads of a pass are in flight together.
     const float2* ml = a.part_ml + (size_t) row * a.nsplit;
+    const float* po = a.part_o + (size_t) row * a.nsplit * DH + lane * VPL;
+    // The first 8 partial rows are requested before the maxima are reduced: their latency then overlaps that of
+    // the (m, l) loads instead of following it.
+    float v0[8][VPL];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+    {
+        const int c = min(j, n - 1);
+        if constexpr (VPL == 4)
+        {
+            const float4 q = *reinterpret_cast<const float4*>(po + (size_t) c * DH);
+            v0[j][0] = q.x, v0[j][1] = q.y, v0[j][2] = q.z, v0[j][3] = q.w;
+        }
+        else
+        {
+            const float2 q = *reinterpret_cast<const float2*>(po + (size_t) c * DH);
+            v0[j][0] = q.x, v0[j][1] = q.y;
+        }
+    }
     float M = -INFINITY;
     for (int c0 = 0; c0 < n; c0 += 32)
     {
@@ -35,7 +54,6 @@ __device__ __forceinline__ void merge_row(const AttnArgs& a, int row, int n, int
 #pragma unroll
     for (int i = 0; i < VPL; ++i)
         o[i] = 0.f;
-    const float* po = a.part_o + (size_t) row * a.nsplit * DH + lane * VPL;
     for (int c0 = 0; c0 < n; c0 += 32)
     {
         // lane j holds the weight of partition c0 + j
@@ -52,19 +70,30 @@ __device__ __forceinline__ void merge_row(const AttnArgs& a, int row, int n, int
         {
             // 8 independent row loads, then the weighted sums
             float v[8][VPL];
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
+            if (c0 + j0 == 0)
             {
-                const int c = min(c0 + j0 + j, n - 1); // clamped: weight of a padded slot is 0
-                if constexpr (VPL == 4)
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+#pragma unroll
+                    for (int i = 0; i < VPL; ++i)
+                        v[j][i] = v0[j][i];
+            }
+            else
+            {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
                 {
-                    const float4 q = *reinterpret_cast<const float4*>(po + (size_t) c * DH);
-                    v[j][0] = q.x, v[j][1] = q.y, v[j][2] = q.z, v[j][3] = q.w;
-                }
-                else
-                {
-                    const float2 q = *reinterpret_cast<const float2*>(po + (size_t) c * DH);
-                    v[j][0] = q.x, v[j][1] = q.y;
+                    const int c = min(c0 + j0 + j, n - 1); // clamped: weight of a padded slot is 0
+                    if constexpr (VPL == 4)
+                    {
+                        const float4 q = *reinterpret_cast<const float4*>(po + (size_t) c * DH);
+                        v[j][0] = q.x, v[j][1] = q.y, v[j][2] = q.z, v[j][3] = q.w;
+                    }
+                    else
+                    {
+                        const float2 q = *reinterpret_cast<const float2*>(po + (size_t) c * DH);
+                        v[j][0] = q.x, v[j][1] = q.y;
+                    }
                 }
             }
 #pragma unroll
