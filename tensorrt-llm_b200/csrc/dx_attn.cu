@@ -124,7 +124,8 @@ inline long parts_of(long total, long target)
 // minimises  waves * (fixed cost + tokens per CTA);  the kernels then cut every sequence into equal
 // partitions of at most T tokens (partition_of).  host_past may be null: all sequences are then
 // taken to have max_past_len tokens.
-Plan make_plan(const dx_attn* h, int batch, int max_past_len, const int32_t* host_past = nullptr)
+// First half: which kernel, how many CTA rows per sequence, resident CTAs per SM.  No partitioning yet.
+Plan plan_shape(const dx_attn* h, int batch, int& rows_per_seq_out)
 {
     Plan p;
     const dx_attn_config& c = h->cfg;
@@ -158,6 +159,17 @@ Plan make_plan(const dx_attn* h, int batch, int max_past_len, const int32_t* hos
     }
     p.rows = batch * rows_per_seq;
     p.resident = resident;
+    rows_per_seq_out = rows_per_seq;
+    return p;
+}
+
+// Second half: the partition bound.  This runs on the host in front of every enqueue, so the search is kept
+// cheap: the bounds tried are multiples of 128 tokens, for which ceil(len / T) only depends on ceil(len / 128) -
+// the lengths are counted into 128-token buckets once and every candidate costs one division per occupied bucket.
+void plan_partitions(const dx_attn* h, Plan& p, int batch, int rows_per_seq, int max_past_len, const int32_t* host_past)
+{
+    const dx_attn_config& c = h->cfg;
+    const int resident = p.resident;
     const long max_total = (long) max_past_len + 1;
     long target = (long) align_up((size_t) max_total, 128);
     if (c.multi_block_mode)
@@ -172,11 +184,48 @@ Plan make_plan(const dx_attn* h, int batch, int max_past_len, const int32_t* hos
         const double fixed = (double) h->fixed_cost_tokens;
         const long t_max = (long) align_up((size_t) max_total, 128);
         double best = 1e300;
+        // occupied buckets: (ceil(len / 128), sequences)
+        constexpr int MAX_BUCKETS = 512;
+        const uint32_t nb128 = (uint32_t) (t_max / 128);
+        uint32_t bucket_len[MAX_BUCKETS], bucket_cnt[MAX_BUCKETS];
+        int nbuckets = 0;
+        const bool bucketed = host_past != nullptr && nb128 < MAX_BUCKETS;
+        if (bucketed)
+        {
+            uint32_t hist[MAX_BUCKETS];
+            for (uint32_t i = 0; i <= nb128; ++i)
+                hist[i] = 0;
+            for (int i = 0; i < batch; ++i)
+                ++hist[std::min<uint32_t>(((uint32_t) host_past[i] + 128) >> 7, nb128)]; // ceil((past + 1) / 128)
+            for (uint32_t i = 0; i <= nb128; ++i)
+            {
+                if (hist[i])
+                {
+                    bucket_len[nbuckets] = i;
+                    bucket_cnt[nbuckets++] = hist[i];
+                }
+            }
+        }
         for (long t = std::min(t_min, t_max); t <= t_max;)
         {
             long cnt = 0;
-            for (int i = 0; i < batch; ++i)
-                cnt += parts_of(host_past ? (long) host_past[i] + 1 : max_total, t);
+            if (!host_past)
+            {
+                cnt = (long) batch * parts_of(max_total, t);
+            }
+            else if (bucketed && (t & 127) == 0)
+            {
+                const uint32_t t128 = (uint32_t) (t >> 7);
+                uint32_t acc = 0;
+                for (int i = 0; i < nbuckets; ++i)
+                    acc += bucket_cnt[i] * ((bucket_len[i] + t128 - 1) / t128);
+                cnt = (long) acc;
+            }
+            else
+            {
+                for (int i = 0; i < batch; ++i)
+                    cnt += parts_of((long) host_past[i] + 1, t);
+            }
             cnt *= rows_per_seq;
             // a few CTAs over a whole number of waves ride along with the ragged finish of many waves, but cost a
             // whole extra round when there are only one or two
@@ -206,6 +255,13 @@ Plan make_plan(const dx_attn* h, int batch, int max_past_len, const int32_t* hos
         p.part_o_bytes = align_up(qrows * p.nsplit * c.head_size * sizeof(float), 128);
         p.part_ml_bytes = align_up(qrows * p.nsplit * sizeof(float2), 128);
     }
+}
+
+Plan make_plan(const dx_attn* h, int batch, int max_past_len, const int32_t* host_past = nullptr)
+{
+    int rows_per_seq = 1;
+    Plan p = plan_shape(h, batch, rows_per_seq);
+    plan_partitions(h, p, batch, rows_per_seq, max_past_len, host_past);
     return p;
 }
 
@@ -219,13 +275,14 @@ bool build_streamk(const dx_attn* h, Plan& plan, const int32_t* host_past, int b
         return false;
     // tokens per schedule unit: a token group of the mma.sync kernels, a tile of the token-major tcgen05 kernel
     const uint32_t unit = plan.kind == KIND_TOK ? 128 : h->cache_kind == CACHE_T ? 16 : 32;
+    const uint32_t unit_log2 = unit == 128 ? 7 : unit == 32 ? 5 : 4;
     const uint32_t Y = (uint32_t) (c.num_kv_heads * plan.hgroups);
     uint64_t acc = 0;
     uint32_t nmax = 1;
     sk.prefix[0] = 0;
     for (int i = 0; i < batch; ++i)
     {
-        const uint32_t n = ((uint32_t) host_past[i] + 1 + unit - 1) / unit;
+        const uint32_t n = ((uint32_t) host_past[i] + unit) >> unit_log2; // ceil((past + 1) / unit)
         nmax = std::max(nmax, n);
         acc += n;
         sk.prefix[i + 1] = (uint32_t) acc;
@@ -763,10 +820,13 @@ int dx_attn_plan_lengths(const dx_attn_t* h, const int32_t* host_past_key_value_
             return DX_ERR_BAD_ARG;
         max_past = std::max(max_past, host_past_key_value_lengths[i]);
     }
-    Plan p = make_plan(h, batch, max_past, host_past_key_value_lengths);
+    int rows_per_seq = 1;
+    Plan p = plan_shape(h, batch, rows_per_seq);
     SkSchedule sk;
     int ctas = 0;
     const bool streamk = build_streamk(h, p, host_past_key_value_lengths, batch, sk, ctas);
+    if (!streamk)
+        plan_partitions(h, p, batch, rows_per_seq, max_past, host_past_key_value_lengths);
     if (num_partitions)
         *num_partitions = streamk ? -ctas : p.nsplit; // stream-K: minus the number of CTAs, each tokens_per_partition tokens
     if (tokens_per_partition)
@@ -828,7 +888,8 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     if ((int64_t) max_past + 1 > (int64_t) p.max_blocks_per_sequence * c.tokens_per_block)
         return DX_ERR_BAD_ARG; // the table cannot hold that many tokens
 
-    Plan plan = make_plan(h, p.num_requests, max_past, p.host_past_key_value_lengths);
+    int rows_per_seq = 1;
+    Plan plan = plan_shape(h, p.num_requests, rows_per_seq);
     if (plan.kind == KIND_MHA && c.tokens_per_block < 16)
         return DX_ERR_UNSUPPORTED;
     const size_t prep = prep_bytes(h, p.num_requests);
@@ -840,7 +901,7 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     const bool use_sk = build_streamk(h, plan, p.host_past_key_value_lengths, p.num_requests, sk, sk_ctas)
         && p.workspace && !((uintptr_t) p.workspace & 127) && p.workspace_bytes >= prep + plan.workspace();
     if (!use_sk)
-        plan = make_plan(h, p.num_requests, max_past, p.host_past_key_value_lengths);
+        plan_partitions(h, plan, p.num_requests, rows_per_seq, max_past, p.host_past_key_value_lengths);
     if (plan.nsplit > 1 || prep)
     {
         if (!p.workspace || ((uintptr_t) p.workspace & 127))
