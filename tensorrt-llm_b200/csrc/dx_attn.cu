@@ -39,6 +39,7 @@ struct Plan
     bool heads16 = false;
     int rows = 0;       // grid.y * grid.z
     int resident = 2;   // CTAs per SM of the chosen kernel
+    bool six = false;   // stream-K launch on the six-warp form of the grouped-head kernel
     int nsplit = 1;     // grid.x
     int chunk_tokens = 0;
     size_t part_o_bytes = 0, part_ml_bytes = 0;
@@ -67,6 +68,7 @@ struct dx_attn
     int min_chunk = 256;         // smallest partition bound, tokens
     int fixed_cost_tokens = 400; // per-CTA fixed cost (prologue, pipeline fill, epilogue) in tokens of streaming time
     KernelInfo k_mha{}, k_gqa[2]{}, k_wide{}, k_tok{}, k_merge{}, k_append{}; // k_gqa[16 heads per CTA?]
+    KernelInfo k_gqa_six{}; // stream-K form of k_gqa[0] with two six-warp CTAs per SM (where built)
     bool wide = false;       // wide-group kernel usable for this configuration
     bool tok = false;        // token-major tcgen05 kernel usable for this configuration
     GeneralKernels k_general{}; // beams / cyclic window / sinks / ALiBi
@@ -75,6 +77,7 @@ struct dx_attn
     int sk_min_units = 48;      // stream-K only when a CTA's range is at least this many token groups: below, the
                                 // second prologue / epilogue of a CTA that straddles a row boundary costs more
                                 // than the even split wins (measured on the TP8 shards)
+    int six_min_tokens = 4096;  // stream-K launches use the six-warp CTAs when a range is at least this long
     bool streamk16 = false;     // the 16-bit kernel measured slower with it on its benchmark shape (131 -> 137 us): opt-in
     int sk_row_factor = 6;      // ... and only when the average row is at most this many ranges long
     SkSchedule sk_zero{};       // third argument of classic launches of the grouped-head kernels
@@ -308,6 +311,24 @@ bool build_streamk(const dx_attn* h, Plan& plan, const int32_t* host_past, int b
     plan.part_o_bytes = align_up(qrows * pmax * c.head_size * sizeof(float), 128);
     plan.part_ml_bytes = align_up(qrows * pmax * sizeof(float2), 128);
     return true;
+}
+
+// build_streamk for the kernel form stream-K launches use: the six-warp CTAs where they exist (two per SM, which
+// changes the number of ranges), else the kernel of the plan.
+bool plan_streamk(const dx_attn* h, Plan& plan, const int32_t* host_past, int batch, SkSchedule& sk, int& ctas)
+{
+    const Plan shape = plan;
+    plan.six = plan.kind == KIND_GQA && !plan.heads16 && h->k_gqa_six.fn != nullptr;
+    if (plan.six)
+    {
+        // pays when the ranges are long (c4: 10.6 K tokens per CTA, 140.5 against 142.2 us; its TP2 shard 78.2 / 78.7);
+        // the TP4 shard (2.7 K tokens) is 1 % slower with it
+        plan.resident = h->k_gqa_six.resident;
+        if (build_streamk(h, plan, host_past, batch, sk, ctas) && plan.chunk_tokens >= h->six_min_tokens)
+            return true;
+        plan = shape;
+    }
+    return build_streamk(h, plan, host_past, batch, sk, ctas);
 }
 
 // Upper bound of Plan::workspace() over every length vector with lengths <= max_past_len.
@@ -732,6 +753,16 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
         st = set_smem(h, h->k_mha);
     for (int i = 0; i < 2 && st == DX_OK; ++i)
         st = set_smem(h, h->k_gqa[i]);
+    if (st == DX_OK && h->k_gqa[0].fn)
+    {
+        const char* w = getenv("DX_ATTN_SK_SIX_WARPS"); // "0": stream-K launches stay on the four-warp CTAs
+        if (!w || atoi(w) != 0)
+        {
+            h->k_gqa_six = gqa_streamk_kernel_info(c.type_id, h->cache_kind, c.head_size, false);
+            if (h->k_gqa_six.fn && set_smem(h, h->k_gqa_six) != DX_OK)
+                h->k_gqa_six = KernelInfo{};
+        }
+    }
     if (st == DX_OK && h->cache_kind == CACHE_FP8 && h->group > 16 && c.tokens_per_block >= 64)
     {
         const char* w = getenv("DX_ATTN_WIDE"); // "0": keep such groups on the 16-head-slice kernel
@@ -824,7 +855,7 @@ int dx_attn_plan_lengths(const dx_attn_t* h, const int32_t* host_past_key_value_
     Plan p = plan_shape(h, batch, rows_per_seq);
     SkSchedule sk;
     int ctas = 0;
-    const bool streamk = build_streamk(h, p, host_past_key_value_lengths, batch, sk, ctas);
+    const bool streamk = plan_streamk(h, p, host_past_key_value_lengths, batch, sk, ctas);
     if (!streamk)
         plan_partitions(h, p, batch, rows_per_seq, max_past, host_past_key_value_lengths);
     if (num_partitions)
@@ -898,8 +929,12 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     // the host lengths.  Used when the workspace given can hold one partial result per piece of a cut row.
     SkSchedule sk;
     int sk_ctas = 0;
-    const bool use_sk = build_streamk(h, plan, p.host_past_key_value_lengths, p.num_requests, sk, sk_ctas)
-        && p.workspace && !((uintptr_t) p.workspace & 127) && p.workspace_bytes >= prep + plan.workspace();
+    bool use_sk = plan_streamk(h, plan, p.host_past_key_value_lengths, p.num_requests, sk, sk_ctas);
+    if (use_sk && !(p.workspace && !((uintptr_t) p.workspace & 127) && p.workspace_bytes >= prep + plan.workspace()))
+    {
+        use_sk = false;
+        plan = plan_shape(h, p.num_requests, rows_per_seq);
+    }
     if (!use_sk)
         plan_partitions(h, plan, p.num_requests, rows_per_seq, max_past, p.host_past_key_value_lengths);
     if (plan.nsplit > 1 || prep)
@@ -960,13 +995,13 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     }
     else if (plan.kind == KIND_GQA)
     {
-        const KernelInfo& k = h->k_gqa[plan.heads16 ? 1 : 0];
+        const KernelInfo& k = plan.six ? h->k_gqa_six : h->k_gqa[plan.heads16 ? 1 : 0];
         if (!k.fn)
             return DX_ERR_UNSUPPORTED;
         int hgroups = plan.hgroups;
         void* args[] = {&a, &hgroups, use_sk ? &sk : &h->sk_zero};
         const dim3 grid = use_sk ? dim3(sk_ctas) : dim3(plan.nsplit, c.num_kv_heads * plan.hgroups, p.num_requests);
-        st = check_cuda(h, cudaLaunchKernel(k.fn, grid, dim3(128), args, (size_t) k.smem, stream));
+        st = check_cuda(h, cudaLaunchKernel(k.fn, grid, dim3(k.threads), args, (size_t) k.smem, stream));
     }
     else
     {

@@ -45,6 +45,25 @@ static KernelInfo by_cache_dh(int cache, int dh)
     return KernelInfo{};
 }
 
+// The stream-K form with two CTAs of six warps per SM (FP8 cache, Dh 128, groups of up to 8 heads).
+template <typename T>
+static KernelInfo mk_six()
+{
+    KernelInfo k;
+    k.fn = reinterpret_cast<const void*>(&gqa_decode_kernel<T, CACHE_FP8, 128, false, 6>);
+    k.smem = GqaTraits<128, gqa_min_blocks<CACHE_FP8, 128, false, 6>(), 6>::SMEM_BYTES;
+    k.resident = 2;
+    k.threads = 192;
+    return k;
+}
+
+KernelInfo gqa_streamk_kernel_info(int dtype, int cache, int dh, bool heads16)
+{
+    if (cache != CACHE_FP8 || dh != 128 || heads16)
+        return KernelInfo{};
+    return dtype == 0 ? mk_six<__half>() : mk_six<__nv_bfloat16>();
+}
+
 KernelInfo gqa_kernel_info(int dtype, int cache, int dh, bool heads16)
 {
     if (dtype == 0)

@@ -36,14 +36,17 @@ namespace dx
 
 // CTAs per SM the kernel is built for: 3 (with a 2-stage ring) where the register budget allows
 // it - more resident warps hide the fixed instruction latencies better than a deeper ring - else 2
-// (3-stage ring).
-template <int CACHE, int DH, bool H16>
+// (3-stage ring).  WARPS = 6: the stream-K form of the FP8 / Dh 128 kernel, two CTAs of six warps with 2-stage
+// rings - the same twelve warps and 192 KB of rings per SM as three CTAs of four, but when a CTA has finished its
+// range the other one still keeps 96 KB in flight instead of 64 KB (c4: 140.5 us against 142.2 us in the same run;
+// one CTA of twelve warps: 152 us, every piece boundary then stalls the whole SM).
+template <int CACHE, int DH, bool H16, int WARPS = 4>
 constexpr int gqa_min_blocks()
 {
-    return (CACHE == CACHE_FP8 && DH == 128 && !H16) ? 3 : 2;
+    return WARPS == 6 ? 2 : (CACHE == CACHE_FP8 && DH == 128 && !H16) ? 3 : 2;
 }
 
-template <int DH, int MINB>
+template <int DH, int MINB, int WARPS = 4>
 struct GqaTraits
 {
     static constexpr int TG = 32;           // tokens per stage (per warp)
@@ -53,8 +56,8 @@ struct GqaTraits
     static constexpr int QV = DH / 4;       // q elements per thread per head row
     static constexpr int SLAB = TG * DH;    // bytes of K (or V) per stage
     static constexpr int STAGE_BYTES = 2 * SLAB;
-    static constexpr int STAGES = (MINB >= 3 && DH == 128) ? 2 : 3;
-    static constexpr int NWARPS = 4;
+    static constexpr int STAGES = ((MINB >= 3 || WARPS == 6) && DH == 128) ? 2 : 3;
+    static constexpr int NWARPS = WARPS;
     static constexpr int RING_BYTES = NWARPS * STAGES * STAGE_BYTES;
     static constexpr int MERGE_BYTES = NWARPS * (16 * DH + 32) * 4;
     static constexpr int SMEM_BYTES = (RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES) + NWARPS * STAGES * 8 + 16;
@@ -196,11 +199,12 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr)
     return v;
 }
 
-template <typename T, int CACHE, int DH, bool H16>
-__global__ void __launch_bounds__(128, gqa_min_blocks<CACHE, DH, H16>()) gqa_decode_kernel(const AttnArgs a, const int hgroups, const __grid_constant__ SkSchedule sk)
+template <typename T, int CACHE, int DH, bool H16, int WARPS = 4>
+__global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WARPS>())
+    gqa_decode_kernel(const AttnArgs a, const int hgroups, const __grid_constant__ SkSchedule sk)
 {
     static_assert(CACHE == CACHE_INT8 || CACHE == CACHE_FP8, "8-bit caches only");
-    using Tr = GqaTraits<DH, gqa_min_blocks<CACHE, DH, H16>()>;
+    using Tr = GqaTraits<DH, gqa_min_blocks<CACHE, DH, H16, WARPS>(), WARPS>;
     constexpr int TG = Tr::TG, KS = Tr::KS, MT = Tr::MT, NW = Tr::NW, QV = Tr::QV;
     constexpr int SLAB = Tr::SLAB, STAGES = Tr::STAGES, NWARPS = Tr::NWARPS;
     constexpr int NR = H16 ? 2 : 1;  // head-row halves in use (rows g, and rows g + 8)

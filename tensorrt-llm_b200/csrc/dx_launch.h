@@ -9,11 +9,13 @@ struct KernelInfo
     const void* fn = nullptr; // __global__ function address for cudaLaunchKernel
     int smem = 0;             // dynamic shared memory per CTA, bytes
     int resident = 0;         // CTAs per SM the kernel was built for (0: not stated)
+    int threads = 128;        // threads per CTA
 };
 
 // dtype: 0 fp16, 1 bf16.  cache: CacheKind.  dh: 64 or 128.
 KernelInfo mha_kernel_info(int dtype, int cache, int dh, int tokens_per_block);
 KernelInfo gqa_kernel_info(int dtype, int cache, int dh, bool heads16);
+KernelInfo gqa_streamk_kernel_info(int dtype, int cache, int dh, bool heads16); // 6-warp CTAs; empty where not built
 KernelInfo wide_kernel_info(int dtype, int dh); // FP8 cache only
 KernelInfo tok_kernel_info(int dtype, int dh, int group); // FP8 cache, Dh 128, group <= 16
 struct GeneralKernels
