@@ -79,8 +79,9 @@ typedef struct dx_attn_config
      * (decoderMaskedMultiheadAttentionTemplate.h:1587-1712): bias add, then rotary embedding on q and k.
      * Values of position_embedding_type / rotary_embedding_scale_type are the reference's
      * (cpp/tensorrt_llm/kernels/gptKernels.h:41-58): 0 learned-absolute (nothing to do), 1 RoPE GPT-J,
-     * 2 RoPE GPT-NeoX, 3 ALiBi, 4 ALiBi with scale (both: slopes per call, dx_attn_generation_params.alibi_slopes);
- * scale type 0 none, 1 linear, 2 dynamic.  Relative position bias: DX_ERR_UNSUPPORTED. */
+     * 2 RoPE GPT-NeoX, 3 ALiBi, 4 ALiBi with scale (both: slopes per call, dx_attn_generation_params.alibi_slopes),
+     * 5 relative (bias table per call, dx_attn_generation_params.relative_attention_bias);
+     * scale type 0 none, 1 linear, 2 dynamic. */
     int32_t position_embedding_type;
     int32_t rotary_embedding_dim;
     float rotary_embedding_base;
@@ -164,13 +165,24 @@ typedef struct dx_attn_generation_params
     int32_t reserved0; /* 0 */
     /* device, int32 [num_requests, Q, (Q + 31) / 32] (plugin input medusa_packed_mask) */
     const int32_t* medusa_packed_mask;
-    /* device, int32 [num_requests, Q] or NULL = all zero (plugin input medusa_position_offsets) */
+    /* device, int32 [num_requests, Q] or NULL = offset t for token t (plugin input medusa_position_offsets) */
     const int32_t* medusa_position_offsets;
+    /* optional tail 4: relative attention bias (T5-style; EnqueueGenerationParams::relative_attention_bias,
+     * gptAttentionCommon.h:156-158).  Needs position_embedding_type 5 (relative).
+     *   max_distance == 0: device, T [num_heads, stride, stride]; the score of cache slot s gets
+     *     bias[head][past length][s] added (decoderMaskedMultiheadAttentionTemplate.h:1773-1797, :1981-2026);
+     *   max_distance > 0 (the plugin attribute of that name): the implicit form, device T [num_heads, stride] with
+     *     stride = number of buckets; the bias is table[head][bucket(s - past length)] with the reference's bucket
+     *     function (decoderMaskedMultiheadAttentionTemplate.h:1957-1978). */
+    const void* relative_attention_bias;
+    int32_t relative_attention_bias_stride;
+    int32_t max_distance;
 } dx_attn_generation_params;
 /* sizes of dx_attn_generation_params without the optional tails (all are accepted by the enqueue calls) */
 #define DX_ATTN_GENERATION_PARAMS_SIZE_V1 offsetof(dx_attn_generation_params, qkv_bias)
 #define DX_ATTN_GENERATION_PARAMS_SIZE_V2 offsetof(dx_attn_generation_params, context_lengths)
 #define DX_ATTN_GENERATION_PARAMS_SIZE_V3 offsetof(dx_attn_generation_params, input_seq_length)
+#define DX_ATTN_GENERATION_PARAMS_SIZE_V4 offsetof(dx_attn_generation_params, relative_attention_bias)
 
 typedef struct dx_attn dx_attn_t;
 

@@ -40,15 +40,34 @@ def kv_token_slot(tok: int, sink: int, bubble: int, cyclic_len: int) -> int:
     return tok if tok < sink else sink + bubble + (tok - sink) % cyclic_len
 
 
+def relative_bucket(relative_position: int, table_buckets: int, max_distance: int) -> int:
+    """Bucket of a relative position, as the reference computes it on the fly
+    (decoderMaskedMultiheadAttentionTemplate.h:1957-1975; float32 arithmetic)."""
+    import numpy as np
+    num_buckets = table_buckets // 2
+    bucket = num_buckets if relative_position > 0 else 0
+    rp = abs(relative_position)
+    max_exact = num_buckets // 2
+    if rp < max_exact:
+        return bucket + rp
+    f32 = np.float32
+    large = max_exact + int(np.log(f32(rp) * f32(1.0) / f32(max_exact)) / np.log(f32(max_distance) / f32(max_exact))
+                            * f32(num_buckets - max_exact))
+    return bucket + min(large, num_buckets - 1)
+
+
 def decode_attention_general_reference(qkv, sequence_lengths, pool, offset_table, *, num_heads, num_kv_heads,
                                        head_size, tokens_per_block, cache_mode, q_scaling=1.0,
                                        kv_scale_orig_quant=1.0, kv_scale_quant_orig=1.0, beam_width=1,
                                        cache_indirection=None, context_lengths=None, max_attention_window=None,
                                        cyclic_attention_window_size=None, sink_token_length=0, alibi_slopes=None,
-                                       append=True):
+                                       relative_attention_bias=None, max_distance=0, append=True):
     """qkv: T [B, (H + 2 Hkv) Dh] (B counts beams); pool: uint8, mutated when append; offset_table int64
     [B, 2, M] byte offsets.  cache_indirection: int32 [B, max_attention_window]; context_lengths: int32 [B];
-    alibi_slopes: [H].  Returns fp32 [B, H * Dh]."""
+    alibi_slopes: [H].  relative_attention_bias: T [H, stride, stride] - slot s of a sequence with `past` earlier
+    tokens gets bias[h, past, s] added to its score (decoderMaskedMultiheadAttentionTemplate.h:1773-1797,
+    :1981-2026) - or, with max_distance > 0, the bucket table T [H, buckets] of the implicit form
+    (relative_bucket below).  Returns fp32 [B, H * Dh]."""
     B = qkv.shape[0]
     H, Hkv, Dh = num_heads, num_kv_heads, head_size
     G = H // Hkv
@@ -98,6 +117,15 @@ def decode_attention_general_reference(qkv, sequence_lengths, pool, offset_table
             dist = torch.arange(kv_len + 1, dtype=torch.float32) - float(tlength)
             dist[kv_len] = 0.0
             s_ = s_ + alibi_slopes.to(torch.float32).view(Hkv, G, 1) * dist.view(1, 1, -1)
+        if relative_attention_bias is not None:
+            slots = list(range(kv_len)) + [tlength]  # the new token is looked up at its own position
+            if max_distance > 0:
+                idx = torch.tensor([relative_bucket(s - tlength, relative_attention_bias.shape[1], max_distance)
+                                    for s in slots])
+                rb = relative_attention_bias.to(torch.float32)[:, idx]  # [H, kv_len + 1]
+            else:
+                rb = relative_attention_bias.to(torch.float32)[:, tlength, torch.tensor(slots)]
+            s_ = s_ + rb.view(Hkv, G, -1)
         p = torch.softmax(s_, dim=-1)
         out[bb] = torch.matmul(p, V).reshape(H * Dh)
         writes.append((bb, kv_token_slot(tlength, sink_token_length, bubble, cyclic_len), kq, vq))

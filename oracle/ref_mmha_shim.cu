@@ -42,6 +42,10 @@ namespace mmha
 template void mmha_launch_kernel<RefT, KVBlockArray, Masked_multihead_attention_params<RefT>, REF_DH, false>(
     const Masked_multihead_attention_params<RefT>& params, const KVBlockArray& kv_cache_buffer,
     const KVLinearBuffer& shift_k_cache, const cudaStream_t& stream);
+// the variant that computes the relative-position bucket on the fly (chosen like decoderMaskedMultiheadAttention.cu:62)
+template void mmha_launch_kernel<RefT, KVBlockArray, Masked_multihead_attention_params<RefT>, REF_DH, true>(
+    const Masked_multihead_attention_params<RefT>& params, const KVBlockArray& kv_cache_buffer,
+    const KVLinearBuffer& shift_k_cache, const cudaStream_t& stream);
 } // namespace mmha
 } // namespace kernels
 } // namespace tensorrt_llm
@@ -60,6 +64,9 @@ struct RefExtras
     int32_t cyclic_attention_window_size = 0; // 0: same as max_attention_window
     int32_t sink_token_length = 0;
     const void* linear_bias_slopes = nullptr; // T [num_heads]
+    const void* relative_attention_bias = nullptr; // T [num_heads, stride, stride], or [num_heads, stride] (implicit)
+    int32_t relative_attention_bias_stride = 0;
+    int32_t max_distance = 0;                      // > 0: implicit form, stride = number of buckets
 };
 
 static int ref_mmha_impl(const void* qkv, void* out, const int32_t* sequence_length_dev,
@@ -99,6 +106,9 @@ static int ref_mmha_impl(const void* qkv, void* out, const int32_t* sequence_len
     p.cache_indir = x.beam_width > 1 ? x.cache_indir : nullptr;
     p.input_lengths = x.input_lengths;
     p.linear_bias_slopes = reinterpret_cast<const RefT*>(x.linear_bias_slopes);
+    p.relative_attention_bias = reinterpret_cast<const RefT*>(x.relative_attention_bias);
+    p.relative_attention_bias_stride = x.relative_attention_bias_stride;
+    p.max_distance = x.max_distance;
     p.max_attention_window_size = max_attention_window;
     p.cyclic_attention_window_size = cyclic;
     p.sink_token_length = x.sink_token_length;
@@ -142,8 +152,12 @@ static int ref_mmha_impl(const void* qkv, void* out, const int32_t* sequence_len
     }
     try
     {
-        mmha::mmha_launch_kernel<RefT, KVBlockArray, Masked_multihead_attention_params<RefT>, REF_DH, false>(
-            p, kv, shift_k, stream);
+        if (p.max_distance > 0 && p.relative_attention_bias != nullptr)
+            mmha::mmha_launch_kernel<RefT, KVBlockArray, Masked_multihead_attention_params<RefT>, REF_DH, true>(
+                p, kv, shift_k, stream);
+        else
+            mmha::mmha_launch_kernel<RefT, KVBlockArray, Masked_multihead_attention_params<RefT>, REF_DH, false>(
+                p, kv, shift_k, stream);
     }
     catch (...)
     {
@@ -165,6 +179,24 @@ extern "C" int REF_CAT(REF_FN(ref_mmha), REF_DH)(const void* qkv, void* out, con
         kv_scale_quant_orig_dev, int8_kv, fp8_kv, tiles, workspace, sm_count, stream, qkv_bias, position_embedding_type,
         rotary_embedding_dim, rotary_embedding_base, rotary_embedding_scale_type, rotary_embedding_scale,
         rotary_embedding_max_positions, RefExtras{});
+}
+
+/* Relative attention bias (T5-style): explicit table [num_heads, stride, stride] or, with max_distance > 0, the
+ * implicit form with a bucket table [num_heads, stride]. */
+extern "C" int REF_CAT(REF_FN(ref_mmha_relbias), REF_DH)(const void* qkv, void* out, const int32_t* sequence_length_dev,
+    int64_t* block_pointers_dev, int32_t batch, int32_t num_heads, int32_t num_kv_heads, int32_t max_blocks_per_seq,
+    int32_t tokens_per_block, int32_t max_attention_window, int32_t past_kv_length, float q_scaling,
+    const float* kv_scale_orig_quant_dev, const float* kv_scale_quant_orig_dev, int32_t int8_kv, int32_t fp8_kv,
+    int32_t sm_count, cudaStream_t stream, const void* relative_attention_bias, int32_t relative_attention_bias_stride,
+    int32_t max_distance)
+{
+    RefExtras x;
+    x.relative_attention_bias = relative_attention_bias;
+    x.relative_attention_bias_stride = relative_attention_bias_stride;
+    x.max_distance = max_distance;
+    return ref_mmha_impl(qkv, out, sequence_length_dev, block_pointers_dev, batch, num_heads, num_kv_heads,
+        max_blocks_per_seq, tokens_per_block, max_attention_window, past_kv_length, q_scaling, kv_scale_orig_quant_dev,
+        kv_scale_quant_orig_dev, int8_kv, fp8_kv, 0, nullptr, sm_count, stream, nullptr, 5, 0, 10000.f, 0, 1.f, 0, x);
 }
 
 /* Same call with the remaining enqueueGeneration features: beam search (batch counts beams; cache_indir

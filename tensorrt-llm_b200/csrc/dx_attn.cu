@@ -108,7 +108,8 @@ bool read_params(const dx_attn_generation_params* in, dx_attn_generation_params&
     if (!in)
         return false;
     if (in->struct_size != sizeof(dx_attn_generation_params) && in->struct_size != DX_ATTN_GENERATION_PARAMS_SIZE_V1
-        && in->struct_size != DX_ATTN_GENERATION_PARAMS_SIZE_V2 && in->struct_size != DX_ATTN_GENERATION_PARAMS_SIZE_V3)
+        && in->struct_size != DX_ATTN_GENERATION_PARAMS_SIZE_V2 && in->struct_size != DX_ATTN_GENERATION_PARAMS_SIZE_V3
+        && in->struct_size != DX_ATTN_GENERATION_PARAMS_SIZE_V4)
         return false;
     memset(&out, 0, sizeof(out));
     memcpy(&out, in, in->struct_size);
@@ -538,7 +539,14 @@ int enqueue_general(dx_attn* h, const dx_attn_generation_params& p, int max_past
     g.scale_quant_orig = p.kv_scale_quant_orig;
     g.cache_indir = p.beam_width > 1 ? p.cache_indir : nullptr;
     g.context_lengths = p.context_lengths;
-    g.alibi_slopes = c.position_embedding_type >= POS_ALIBI ? p.alibi_slopes : nullptr;
+    const bool alibi_type = c.position_embedding_type == POS_ALIBI || c.position_embedding_type == POS_ALIBI_WITH_SCALE;
+    g.alibi_slopes = alibi_type ? p.alibi_slopes : nullptr;
+    if (c.position_embedding_type == POS_RELATIVE && p.relative_attention_bias)
+    {
+        g.rel_bias = p.relative_attention_bias;
+        g.rel_stride = p.relative_attention_bias_stride;
+        g.max_distance = p.max_distance;
+    }
     g.num_heads = c.num_heads;
     g.num_kv_heads = c.num_kv_heads;
     g.max_blocks_per_seq = p.max_blocks_per_sequence;
@@ -577,7 +585,7 @@ int enqueue_multi_token(dx_attn* h, const dx_attn_generation_params& p, int max_
     // the reference runs this mode on its XQA kernels only: beam width 1, no sliding window, no sink tokens
     // (decoderXQARunner.h:87-159), and asserts when they do not apply (gptAttentionCommon.cpp:1225-1228)
     const int64_t need = (int64_t) max_past + Q;
-    if (p.beam_width != 1 || p.sink_token_length > 0 || c.position_embedding_type >= POS_ALIBI
+    if (p.beam_width != 1 || p.sink_token_length > 0 || c.position_embedding_type >= POS_ALIBI // (ALiBi, relative)
         || p.cyclic_attention_window_size < need || p.max_attention_window < need)
         return DX_ERR_UNSUPPORTED;
     if (c.position_embedding_type != POS_LEARNED_ABSOLUTE && c.rotary_embedding_scale_type == ROT_SCALE_DYNAMIC)
@@ -671,7 +679,7 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
     memcpy(&full, config, config->struct_size);
     full.struct_size = sizeof(dx_attn_config);
     const dx_attn_config& c = full;
-    if (c.position_embedding_type < 0 || c.position_embedding_type > POS_ALIBI_WITH_SCALE)
+    if (c.position_embedding_type < 0 || c.position_embedding_type > POS_RELATIVE)
         return DX_ERR_UNSUPPORTED; // relative position bias is not implemented
     if (c.position_embedding_type == POS_ROPE_GPTJ || c.position_embedding_type == POS_ROPE_GPT_NEOX)
     {
@@ -889,9 +897,20 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
         return DX_ERR_BAD_ARG;
     if (p.beam_width < 1 || p.sink_token_length < 0 || p.cyclic_attention_window_size < 1)
         return DX_ERR_BAD_ARG;
-    const bool alibi = c.position_embedding_type >= POS_ALIBI && p.alibi_slopes != nullptr;
-    if (p.alibi_slopes != nullptr && c.position_embedding_type < POS_ALIBI)
+    const bool alibi_type = c.position_embedding_type == POS_ALIBI || c.position_embedding_type == POS_ALIBI_WITH_SCALE;
+    const bool alibi = alibi_type && p.alibi_slopes != nullptr;
+    if (p.alibi_slopes != nullptr && !alibi_type)
         return DX_ERR_BAD_ARG; // slopes need an ALiBi position embedding type at create time
+    const bool relative = c.position_embedding_type == POS_RELATIVE && p.relative_attention_bias != nullptr;
+    if (p.relative_attention_bias != nullptr)
+    {
+        // a bias table needs the relative position embedding type at create time; the implicit form needs at
+        // least four buckets (the bucket function divides by a quarter of their number)
+        if (c.position_embedding_type != POS_RELATIVE || ((uintptr_t) p.relative_attention_bias & 1)
+            || p.relative_attention_bias_stride <= 0 || p.max_distance < 0
+            || (p.max_distance > 0 && (p.relative_attention_bias_stride < 4 || p.max_distance <= p.relative_attention_bias_stride / 4)))
+            return DX_ERR_BAD_ARG;
+    }
 
     int max_past = p.past_kv_length;
     if (p.host_past_key_value_lengths)
@@ -907,12 +926,14 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     }
     if (max_past < 0)
         return DX_ERR_BAD_ARG;
+    if (relative && p.max_distance == 0 && p.relative_attention_bias_stride < max_past + 1)
+        return DX_ERR_BAD_ARG; // the explicit table must cover every position
     if (p.input_seq_length < 0 || p.reserved0 != 0)
         return DX_ERR_BAD_ARG;
     if (p.input_seq_length > 1)
         return enqueue_multi_token(h, p, max_past, cuda_stream);
     // Beam search, a window shorter than some sequence, sink tokens and ALiBi go to the feature-complete kernel.
-    const bool general = p.beam_width > 1 || p.sink_token_length > 0 || alibi
+    const bool general = p.beam_width > 1 || p.sink_token_length > 0 || alibi || relative
         || p.cyclic_attention_window_size < max_past + 1 || p.max_attention_window < max_past + 1;
     if (general)
         return enqueue_general(h, p, max_past, cuda_stream);

@@ -67,6 +67,10 @@ struct GeneralArgs
     // r / q_len; seq_len includes all q_len new tokens
     int32_t q_len;               // 1: the usual single token
     const int32_t* packed_mask;  // [B, q_len, (q_len + 31) / 32]: bit j of row t = token t attends new token j
+    // relative attention bias: T [H, stride, stride] (max_distance 0) or the bucket table T [H, stride]
+    const void* rel_bias;
+    int32_t rel_stride;
+    int32_t max_distance;
 };
 
 __host__ __device__ __forceinline__ int cyclic_slot(int tok, int sink, int cyclic_len)

@@ -10,6 +10,8 @@
 //   beams: slot s comes from sequence batch*beam_width + (s < context length ? 0 : cache_indir[bb][s]);
 //          a wrapped cache takes every slot through the table                                     (:1497-1498, :2063-2078)
 //   ALiBi: score += slope[head] * (s - tlength), nothing for the new token                              (:1797, :2026)
+//   relative attention bias: score += bias[head][tlength][s] (new token: s = tlength), or in the implicit form
+//          table[head][bucket(s - tlength)] with the T5 bucket function                     (:1773-1797, :1957-1985)
 // The new token is read "as stored" (quantised, then dequantised) and written to the cache by
 // kv_append_token_kernel, launched behind this kernel: every CTA sees the old content of the slot that is
 // about to be overwritten, as the reference's one-CTA-per-head kernel does for its own head.
@@ -49,6 +51,31 @@ __global__ void __launch_bounds__(128) general_decode_kernel(const GeneralArgs a
     float slope = 0.f;
     if (a.alibi_slopes != nullptr)
         slope = TypeOps<T>::to_float(reinterpret_cast<const T*>(a.alibi_slopes)[h]) * LOG2E;
+    // Relative attention bias of cache slot s (log2 units), 0 without a table.
+    const T* rel = reinterpret_cast<const T*>(a.rel_bias);
+    auto rel_bias_of = [&](int s) -> float
+    {
+        if (rel == nullptr)
+            return 0.f;
+        if (a.max_distance > 0)
+        {
+            // the reference's bucket of a relative position (bidirectional layout of the table, the decoder only
+            // ever sees positions <= 0)
+            int num_buckets = a.rel_stride / 2;
+            int relative_position = s - tlength;
+            int bucket = relative_position > 0 ? num_buckets : 0;
+            relative_position = abs(relative_position);
+            const int max_exact = num_buckets / 2;
+            const bool is_small = relative_position < max_exact;
+            int if_large = max_exact
+                + (int) (logf(relative_position * 1.0f / max_exact) / logf((float) a.max_distance / max_exact)
+                    * (num_buckets - max_exact));
+            if_large = min(if_large, num_buckets - 1);
+            bucket += is_small ? relative_position : if_large;
+            return TypeOps<T>::to_float(rel[(size_t) h * a.rel_stride + bucket]) * LOG2E;
+        }
+        return TypeOps<T>::to_float(rel[((size_t) h * a.rel_stride + tlength) * a.rel_stride + s]) * LOG2E;
+    };
 
     const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
     const T* qkv_b = reinterpret_cast<const T*>(a.qkv) + (size_t) bb * qkv_stride;
@@ -113,7 +140,8 @@ __global__ void __launch_bounds__(128) general_decode_kernel(const GeneralArgs a
         }
 #pragma unroll
         for (int u = 0; u < U; ++u)
-            accumulate(kraw[u], vraw[u], slope * (float) (slot[u] - tlength), slot[u] < kv_len);
+            accumulate(kraw[u], vraw[u],
+                slope * (float) (slot[u] - tlength) + rel_bias_of(min(slot[u], kv_len - 1)), slot[u] < kv_len);
     }
     // the new token, as it will be stored: one lane group of warp 0 (every lane runs the shuffles)
     {
@@ -124,7 +152,7 @@ __global__ void __launch_bounds__(128) general_decode_kernel(const GeneralArgs a
         const uint4 kq = make_cache_vec<T, CACHE, EPL>(kp, sc_f, sc_t);
         const uint4 vq = make_cache_vec<T, CACHE, EPL>(vp, sc_f, sc_t);
         if (warp == 0)
-            accumulate(kq, vq, 0.f, sub == 0);
+            accumulate(kq, vq, rel_bias_of(tlength), sub == 0);
     }
 
     // ---- merge the NSTATE running states ----

@@ -24,7 +24,8 @@ enum : int
     POS_ROPE_GPTJ = 1,
     POS_ROPE_GPT_NEOX = 2,
     POS_ALIBI = 3,           // no change of q / k; slopes are added to the scores
-    POS_ALIBI_WITH_SCALE = 4
+    POS_ALIBI_WITH_SCALE = 4,
+    POS_RELATIVE = 5         // no change of q / k; a bias table is added to the scores
 };
 
 enum : int

@@ -43,6 +43,10 @@ struct EnqueueGenerationParams
     // Medusa mode (gptAttentionCommon.h:162-165): input_seq_length > 1 new tokens per sequence under a packed mask
     int32_t const* medusa_packed_mask = nullptr;
     int32_t const* medusa_position_offsets = nullptr;
+    // relative position (gptAttentionCommon.h:156-158); max_distance is the plugin attribute of that name
+    T const* relative_attention_bias = nullptr;
+    int relative_attention_bias_stride = 0;
+    int max_distance = 0;
     T* context_buf = nullptr;
     void* key_value_cache = nullptr; // contiguous cache: not supported, must be nullptr
     void* block_pointers = nullptr;
@@ -161,6 +165,9 @@ public:
         p.input_seq_length = params.input_seq_length;
         p.medusa_packed_mask = params.medusa_packed_mask;
         p.medusa_position_offsets = params.medusa_position_offsets;
+        p.relative_attention_bias = params.relative_attention_bias;
+        p.relative_attention_bias_stride = params.relative_attention_bias_stride;
+        p.max_distance = params.max_distance;
         return dx_attn_enqueue_generation(mHandle, &p, stream);
     }
 

@@ -30,6 +30,7 @@ class PositionEmbeddingType:
     rope_gpt_neox = 2
     alibi = 3
     alibi_with_scale = 4
+    relative = 5
 
 
 class RotaryScalingType:
@@ -79,7 +80,9 @@ class _GenParams(ctypes.Structure):
                 ("cache_indir", ctypes.c_void_p), ("qkv_bias", ctypes.c_void_p),
                 ("context_lengths", ctypes.c_void_p), ("alibi_slopes", ctypes.c_void_p),
                 ("input_seq_length", ctypes.c_int32), ("reserved0", ctypes.c_int32),
-                ("medusa_packed_mask", ctypes.c_void_p), ("medusa_position_offsets", ctypes.c_void_p)]
+                ("medusa_packed_mask", ctypes.c_void_p), ("medusa_position_offsets", ctypes.c_void_p),
+                ("relative_attention_bias", ctypes.c_void_p), ("relative_attention_bias_stride", ctypes.c_int32),
+                ("max_distance", ctypes.c_int32)]
 
 
 EXPORTED_SYMBOLS = [
@@ -245,7 +248,8 @@ class GPTAttentionPlugin:
                 kv_orig_quant_scale, kv_quant_orig_scale, out, workspace, max_attention_window,
                 host_kv_cache_block_pointers=None, cache_indirection=None, beam_width=1, sink_token_length=0,
                 qkv_bias=None, cyclic_attention_window_size=None, context_lengths=None, alibi_slopes=None,
-                input_seq_length=1, medusa_packed_mask=None, medusa_position_offsets=None):
+                input_seq_length=1, medusa_packed_mask=None, medusa_position_offsets=None,
+                relative_attention_bias=None, max_distance=0):
         B = qkv.shape[0] // max(1, input_seq_length)
         M = kv_cache_block_pointers.shape[-1]
         hp = host_past_key_value_lengths
@@ -277,6 +281,9 @@ class GPTAttentionPlugin:
         p.input_seq_length = input_seq_length
         p.medusa_packed_mask = _ptr(medusa_packed_mask)
         p.medusa_position_offsets = _ptr(medusa_position_offsets)
+        p.relative_attention_bias = _ptr(relative_attention_bias)
+        p.relative_attention_bias_stride = 0 if relative_attention_bias is None else int(relative_attention_bias.shape[1])
+        p.max_distance = max_distance
         return p, max_past
 
     def _ensure_workspace(self, batch: int, max_past: int, device) -> Optional[torch.Tensor]:
@@ -301,6 +308,7 @@ class GPTAttentionPlugin:
                            alibi_slopes: Optional[torch.Tensor] = None,
                            medusa_packed_mask: Optional[torch.Tensor] = None,
                            medusa_position_offsets: Optional[torch.Tensor] = None,
+                           relative_attention_bias: Optional[torch.Tensor] = None, max_distance: int = 0,
                            stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
         """qkv: T [B, (H+2Hkv)*Dh] (device); sequence_length: int32 [B] (device, includes the new token);
         host_past_key_value_lengths: int32 [B] (host); kv_cache_block_pointers: int64 [B, 2, M] (device).
@@ -310,7 +318,9 @@ class GPTAttentionPlugin:
         sink_token_length).  ALiBi: alibi_slopes T [H] on the device (plugin built with an ALiBi type).
         Several new tokens per sequence (the reference's Medusa mode): medusa_packed_mask int32
         [B, Q, ceil(Q / 32)] on the device (and optionally medusa_position_offsets int32 [B, Q]); qkv and the
-        result then have B * Q rows and sequence_length includes all Q new tokens."""
+        result then have B * Q rows and sequence_length includes all Q new tokens.
+        Relative attention bias (plugin built with position_embedding_type 5): relative_attention_bias T
+        [H, max_seq_len, max_seq_len] on the device, or with max_distance > 0 the bucket table T [H, buckets]."""
         if not qkv.is_cuda:
             raise DecodeAttnError(DX_ERR_BAD_ARG, "enqueue_generation needs device tensors (no CPU path exists)")
         if qkv.dtype != self.dtype:
@@ -328,7 +338,9 @@ class GPTAttentionPlugin:
                             host_kv_cache_block_pointers, cache_indirection, beam_width, sink_token_length, qkv_bias,
                             cyclic_attention_window_size, context_lengths, alibi_slopes, q_len,
                             None if medusa_packed_mask is None else medusa_packed_mask.contiguous(),
-                            None if medusa_position_offsets is None else medusa_position_offsets.contiguous())
+                            None if medusa_position_offsets is None else medusa_position_offsets.contiguous(),
+                            None if relative_attention_bias is None else relative_attention_bias.contiguous(),
+                            max_distance)
         s = stream if stream is not None else torch.cuda.current_stream(qkv.device)
         st = self.lib.dx_attn_enqueue_generation(self._h, ctypes.byref(p), ctypes.c_void_p(s.cuda_stream))
         if st != DX_OK:

@@ -108,3 +108,42 @@ def test_features_off_is_the_plain_oracle():
     a = decode_attention_general_reference(qkv, seq, pa, offs, **kw)
     b = oracle.decode_attention_reference(qkv, seq, pb, offs, **kw)
     assert torch.equal(pa, pb) and (a - b).abs().max().item() < 1e-5
+
+
+def test_relative_bias_invariances():
+    """A bias that is constant along the key axis changes nothing (softmax is shift-invariant); a zero table equals
+    no table; the implicit form equals the explicit table built from the same buckets."""
+    import oracle.attention_general_ref as G
+    B, H, Hkv, Dh, tpb = 3, 4, 2, 64, 16
+    g = torch.Generator().manual_seed(2)
+    pasts = [5, 40, 77]
+    blocks = sum((p + 1 + tpb - 1) // tpb for p in pasts) + 1
+    offs = torch.full((B, 2, 6), -1, dtype=torch.int64)
+    blk = Hkv * tpb * Dh * 2
+    nxt = 0
+    for b, p in enumerate(pasts):
+        for i in range((p + 1 + tpb - 1) // tpb):
+            offs[b, 0, i] = nxt * blk
+            offs[b, 1, i] = (nxt + blocks) * blk
+            nxt += 1
+    pool = oracle.quantize_kv(torch.randn(2 * blocks * Hkv * tpb * Dh, generator=g).to(torch.float16), 1.0,
+                              oracle.CACHE_T).reshape(-1).contiguous()
+    qkv = torch.randn(B, (H + 2 * Hkv) * Dh, generator=g).to(torch.float16)
+    lens = torch.tensor([p + 1 for p in pasts], dtype=torch.int32)
+    kw = dict(num_heads=H, num_kv_heads=Hkv, head_size=Dh, tokens_per_block=tpb, cache_mode=oracle.CACHE_T)
+    run = lambda **x: G.decode_attention_general_reference(qkv, lens, pool.clone(), offs, **kw, **x)
+    plain = run()
+    S = 80
+    assert torch.equal(run(relative_attention_bias=torch.zeros(H, S, S, dtype=torch.float16)), plain)
+    const = torch.randn(H, S, 1, generator=g).expand(H, S, S).to(torch.float16)
+    assert (run(relative_attention_bias=const) - plain).abs().max().item() < 1e-5
+    table = torch.randn(H, 32, generator=g).to(torch.float16)
+    explicit = torch.zeros(H, S, S, dtype=torch.float16)
+    for t in range(S):
+        for s in range(t + 1):
+            explicit[:, t, s] = table[:, G.relative_bucket(s - t, 32, 100)]
+    a = run(relative_attention_bias=table, max_distance=100)
+    b = run(relative_attention_bias=explicit)
+    assert (a - b).abs().max().item() < 1e-6 and (a - plain).abs().max().item() > 1e-2
+    # buckets: exact below a quarter of the table, logarithmic and clamped above
+    assert [G.relative_bucket(-d, 32, 128) for d in (0, 1, 7, 8, 200)] == [0, 1, 7, 8, 15]
