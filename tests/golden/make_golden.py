@@ -1,5 +1,5 @@
 """Generates the committed golden fixtures of the oracle tests.  Run in a container that has the
-reference tree (default /root/reference) and the built checker (make -C oracle quant_check):
+reference tree (DX_REFERENCE_DIR) and the built checker (make -C oracle quant_check):
 
     python tests/golden/make_golden.py
 

@@ -2,9 +2,14 @@
 the CPU oracle on identical seeded inputs, and compare bytes and outputs."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 import oracle
+
+# Where the timing reports of the GPU tests go (the one folder a remote GPU run brings back).
+REPORT_DIR = os.environ.get("DX_TEST_REPORT_DIR", "gpurun_out")
 
 # Tolerances of the attention output against the fp32 oracle (bf16/fp16 outputs).
 MAX_ABS_TOL = 2e-2

@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import oracle
-from helpers import CACHE_MODE, MAX_ABS_TOL, MEAN_ABS_TOL
+from helpers import CACHE_MODE, MAX_ABS_TOL, MEAN_ABS_TOL, REPORT_DIR
 
 pytestmark = pytest.mark.gpu
 GOLDEN = Path(__file__).resolve().parent / "golden"
@@ -131,7 +131,7 @@ def test_prompt_then_decode_round_trip(pkg):
 
 def test_report_append_bandwidth(pkg):
     """Times the writer on a c4-shaped prompt batch (32 sequences x 4096 tokens, 8 kv heads, FP8) and records
-    bytes moved per second in gpurun_out/append_context.jsonl; asserts only that it ran."""
+    bytes moved per second in append_context.jsonl of the report directory; asserts only that it ran."""
     import json
     import os
     wl = pkg.workloads
@@ -157,8 +157,8 @@ def test_report_append_bandwidth(pkg):
         plugin.close()
     moved = 2 * k.numel() * (2 + 1)  # read 2 B, write 1 B per element, K and V
     rec = {"kernel": "kv_append_context_kernel", "us": us, "bytes": moved, "GBps": moved / us / 1e3}
-    os.makedirs("gpurun_out", exist_ok=True)
-    with open("gpurun_out/append_context.jsonl", "a") as f:
+    os.makedirs(REPORT_DIR, exist_ok=True)
+    with open(os.path.join(REPORT_DIR, "append_context.jsonl"), "a") as f:
         f.write(json.dumps(rec) + "\n")
     print(rec)
     assert us > 0

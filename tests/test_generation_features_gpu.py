@@ -11,7 +11,7 @@ import torch
 
 import oracle
 from oracle.attention_general_ref import decode_attention_general_reference
-from helpers import CACHE_MODE, MAX_ABS_TOL, MEAN_ABS_TOL
+from helpers import CACHE_MODE, MAX_ABS_TOL, MEAN_ABS_TOL, REPORT_DIR
 
 pytestmark = pytest.mark.gpu
 LIB = Path(__file__).resolve().parent.parent / "oracle" / "_ref" / "libref_mmha.so"
@@ -255,7 +255,7 @@ def test_beams_with_bias_and_rotary_embedding(pkg):
 
 
 def test_report_feature_path_time(pkg):
-    """Times the feature path on a beam-search batch of c4's shape (recorded in gpurun_out/feature_path.jsonl)."""
+    """Times the feature path on a beam-search batch of c4's shape (recorded in feature_path.jsonl of the report directory)."""
     import json
     import os
     c = Case((64, 8), 128, torch.bfloat16, "fp8", 64, 16, beam=4, past_lo=2048, past_hi=4096, seed=3)
@@ -284,8 +284,8 @@ def test_report_feature_path_time(pkg):
         kv = float((w_cpu.host_past_key_value_lengths.double().sum()) * 8 * 128 * 2)
         rec = {"case": "beam 4 x 16 requests, 64 q / 8 kv heads, Dh 128, FP8, past 2048-4096", "us": us,
                "unique_kv_GBps": kv / us / 1e3}
-        os.makedirs("gpurun_out", exist_ok=True)
-        with open("gpurun_out/feature_path.jsonl", "a") as f:
+        os.makedirs(REPORT_DIR, exist_ok=True)
+        with open(os.path.join(REPORT_DIR, "feature_path.jsonl"), "a") as f:
             f.write(json.dumps(rec) + "\n")
         print(rec)
     finally:

@@ -10,7 +10,7 @@ from pathlib import Path
 import pytest
 import torch
 
-from helpers import MAX_ABS_TOL, MEAN_ABS_TOL, oracle_step
+from helpers import MAX_ABS_TOL, MEAN_ABS_TOL, REPORT_DIR, oracle_step
 
 pytestmark = pytest.mark.gpu
 REF_MAX_ABS_TOL, REF_MEAN_ABS_TOL = 0.5, 0.05
@@ -77,7 +77,7 @@ def test_oracle_matches_reference_mmha_kernel(pkg, dtype, dh, cache, heads):
 @pytest.mark.parametrize("name,tp,tiles", [("c4", 8, 0), ("c2", 1, 0), ("c5", 8, 8)])
 def test_report_reference_kernel_time(pkg, name, tp, tiles):
     """Times the reference MMHA kernel (recompiled for sm_100a) beside this library on the same resident
-    inputs and records both in gpurun_out/ref_kernel_times.jsonl.  Asserts only agreement of results."""
+    inputs and records both in ref_kernel_times.jsonl of the report directory.  Asserts only agreement of results."""
     import json
     import os
     wl = pkg.workloads
@@ -110,8 +110,8 @@ def test_report_reference_kernel_time(pkg, name, tp, tiles):
     rec = {"config": cfg.name, "batch": cfg.batch, "ours_us": t_ours, "ref_mmha_sm100a_us": t_ref,
            "kv_GBps_ours": w.kv_bytes / t_ours / 1e3, "kv_GBps_ref": w.kv_bytes / t_ref / 1e3,
            "note": "same resident inputs for both; back-to-back calls, so a pool smaller than L2 is L2-warm"}
-    os.makedirs("gpurun_out", exist_ok=True)
-    with open("gpurun_out/ref_kernel_times.jsonl", "a") as f:
+    os.makedirs(REPORT_DIR, exist_ok=True)
+    with open(os.path.join(REPORT_DIR, "ref_kernel_times.jsonl"), "a") as f:
         f.write(json.dumps(rec) + "\n")
     print(rec)
     plugin.close()
