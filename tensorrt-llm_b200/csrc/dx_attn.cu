@@ -764,6 +764,8 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
     if (st == DX_OK && h->k_gqa[0].fn)
     {
         const char* w = getenv("DX_ATTN_SK_SIX_WARPS"); // "0": stream-K launches stay on the four-warp CTAs
+        if (const char* m = getenv("DX_ATTN_SK_SIX_MIN_TOKENS"))
+            h->six_min_tokens = std::max(1, atoi(m));
         if (!w || atoi(w) != 0)
         {
             h->k_gqa_six = gqa_streamk_kernel_info(c.type_id, h->cache_kind, c.head_size, false);

@@ -104,3 +104,20 @@ def test_token_major_kernel_boundary_lengths_and_long_row(pkg, monkeypatch):
     cfg = pkg.workloads.DecodeConfig("sktok1", 1, 8, 1, 128, torch.bfloat16, "fp8", 128, 30000, 30000, True, 5)
     r = gpu_step_and_compare(pkg, cfg)
     assert r["plan"].get("stream_k_ctas", 0) > 100
+
+
+@pytest.mark.parametrize("heads,tpb", [((8, 1), 64), ((64, 8), 128), ((16, 2), 32), ((6, 2), 64)])
+def test_six_warp_form_ragged_batches(pkg, monkeypatch, heads, tpb):
+    """The form with two six-warp CTAs per SM (FP8, Dh 128, up to 8 heads per kv head), which launches with long
+    ranges use: forced here on small ragged batches, boundary lengths and one long row."""
+    monkeypatch.setenv("DX_ATTN_SK_SIX_MIN_TOKENS", "1")
+    cfg = pkg.workloads.DecodeConfig("sk6", 7, heads[0], heads[1], 128, torch.bfloat16, "fp8", tpb, 20, 3000, True, 79)
+    r = gpu_step_and_compare(pkg, cfg)
+    assert r["plan"].get("stream_k_ctas", 0) > 0 and r["plan"]["stream_k_ctas"] <= 2 * 148, r["plan"]
+    lens = [0, 1, 31, 32, 33, 63, 64, 65, 95, 96, 127, 128, 129, 255, 256, 257, 517, 1023, 1024, 1025, 2047, 2048]
+    cfg = dataclasses.replace(pkg.workloads.CONFIGS["c4"], batch=len(lens), tokens_per_block=tpb if tpb >= 32 else 64)
+    r = gpu_step_and_compare(pkg, cfg, lengths=torch.tensor(lens, dtype=torch.int32))
+    assert 0 < r["plan"].get("stream_k_ctas", 0) <= 2 * 148
+    cfg = pkg.workloads.DecodeConfig("sk6l", 1, heads[0] // heads[1], 1, 128, torch.float16, "fp8", 128, 30000, 30000, True, 6)
+    r = gpu_step_and_compare(pkg, cfg)
+    assert 100 < r["plan"].get("stream_k_ctas", 0) <= 2 * 148
