@@ -223,9 +223,12 @@ int dx_attn_enqueue_generation_host(
  * image instead of params->workspace (which is ignored); every GPU that loads the library holds that
  * array until the process exits.  The call allocates nothing and calls no allocating routine.
  *  - A batch whose partials need more than DX_STATIC_SCRATCH_BYTES is refused with DX_ERR_WORKSPACE
- *    before anything is launched (dx_attn_workspace_size() tells the need).
- *  - The first call on a device looks the array's device address up (cudaGetSymbolAddress); make that
- *    first call before any stream capture.
+ *    before anything is launched (dx_attn_workspace_size() gives an upper bound of the need).  Calls that need
+ *    no partials - beam search, sliding window / sinks, ALiBi, several new tokens per sequence - are never
+ *    refused for their length.
+ *  - The first call on a device looks the array's device address up (cudaGetSymbolAddress), which may make the
+ *    driver load the library's device code (a driver-side allocation): make that first call before any stream
+ *    capture and before the allocator is frozen.  From the second call on a device nothing is allocated.
  *  - All calls on a device share the one array and it keeps the previous call's contents.  Nothing in
  *    it has to start at zero, but two calls that overlap on the GPU (different streams, no ordering)
  *    race on it: serialise them. */
@@ -280,8 +283,18 @@ int dx_attn_plan(const dx_attn_t* handle, int32_t batch, int32_t max_past_len, i
 int dx_attn_plan_lengths(const dx_attn_t* handle, const int32_t* host_past_key_value_lengths, int32_t batch,
     int32_t* num_partitions, int32_t* tokens_per_partition, int32_t* kernel_kind);
 
-/* Reads (synchronously) and clears the device status word: DX_OK or DX_ERR_TIMEOUT. */
+/* Reads (synchronously) and clears the device status word.  DX_OK; DX_ERR_TIMEOUT: a bounded device-side wait ran
+ * out; DX_ERR_BOUNDS: dx_kv_cache_step ran out of blocks, or a device sequence length needed more split-K
+ * partitions than the call was planned with (host_past_key_value_lengths smaller than the device lengths).
+ * The word is sticky: while it holds a report every later wait on the device gives up after a few hundred polls, so
+ * the steps enqueued after the failing one return quickly with undefined results.  After any report the caller
+ * must read it with this call (which clears it) before results are trusted again.  No reference counterpart (the
+ * reference's kernels wait without a limit). */
 int dx_attn_device_status(dx_attn_t* handle);
+/* Self-test of that reporting path, no reference counterpart: launches one warp that waits, for at most poll_limit
+ * polls (1 .. 2^20), on a barrier nothing ever arrives on, and then records a time-out exactly as the attention
+ * kernels would.  dx_attn_device_status() returns DX_ERR_TIMEOUT afterwards.  Nothing hangs or faults. */
+int dx_attn_selftest_wait_timeout(dx_attn_t* handle, int32_t poll_limit, void* cuda_stream);
 /* Last cudaError_t seen by this handle (0 if none). */
 int dx_attn_last_cuda_error(const dx_attn_t* handle);
 /* Kernels launched by this handle since creation (for launch accounting in benchmarks). */

@@ -6,8 +6,8 @@ The directory name contains a hyphen, so import it through ``__graft_entry__.loa
 """
 from .plugin import (DX_OK, DecodeAttnError, GPTAttentionPlugin, PositionEmbeddingType, QuantMode,  # noqa: F401
                      RotaryScalingType, gpt_attention, library_path, load_library)
-from . import kv_cache_manager, workloads  # noqa: F401
+from . import kv_cache_manager  # noqa: F401
 from .kv_cache_manager import GenerationSequence, KVCacheManager  # noqa: F401
 
 __all__ = ["GPTAttentionPlugin", "QuantMode", "gpt_attention", "DecodeAttnError", "load_library", "library_path",
-           "workloads", "DX_OK"]
+           "DX_OK"]

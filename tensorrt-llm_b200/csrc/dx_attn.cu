@@ -18,6 +18,7 @@
 #include "dx_launch.h"
 #include "dx_merge_kernel.cuh"
 #include "dx_prep_kernel.cuh"
+#include "dx_selftest_kernel.cuh"
 
 using namespace dx;
 
@@ -1241,7 +1242,11 @@ int dx_attn_device_status(dx_attn_t* h)
         if (st != DX_OK)
             return st;
     }
-    return v == 0 ? DX_OK : (v == STATUS_TIMEOUT ? DX_ERR_TIMEOUT : (v == STATUS_NO_BLOCKS ? DX_ERR_BOUNDS : DX_ERR_CUDA));
+    if (v == 0)
+        return DX_OK;
+    if (v == STATUS_TIMEOUT)
+        return DX_ERR_TIMEOUT;
+    return (v == STATUS_NO_BLOCKS || v == STATUS_PLAN_EXCEEDED) ? DX_ERR_BOUNDS : DX_ERR_CUDA;
 }
 
 int dx_kv_cache_step(dx_attn_t* h, int32_t* sequence_lengths, int64_t* block_pointers, int32_t num_requests,
@@ -1292,19 +1297,9 @@ int dx_attn_enqueue_generation_static_scratch(
     params = &full;
     if (params->num_requests <= 0)
         return params->num_requests == 0 ? DX_OK : DX_ERR_BAD_ARG;
-    // Size check first, on the host: the partials of this batch must fit the fixed array.
-    int max_past = params->past_kv_length;
-    if (params->host_past_key_value_lengths)
-    {
-        max_past = 0;
-        for (int i = 0; i < params->num_requests; ++i)
-            max_past = std::max(max_past, params->host_past_key_value_lengths[i]);
-    }
-    if (max_past < 0)
-        return DX_ERR_BAD_ARG;
-    const Plan plan = make_plan(h, params->num_requests, max_past, params->host_past_key_value_lengths);
-    if (prep_bytes(h, params->num_requests) + plan.workspace() > (size_t) DX_STATIC_SCRATCH_BYTES)
-        return DX_ERR_WORKSPACE;
+    // No size check of its own: the forwarded call plans the step (stream-K, classic partitions, the feature paths
+    // that need no partials at all) and returns DX_ERR_WORKSPACE before it launches anything when the fixed array
+    // is too small for that plan.
     int st = check_cuda(h, cudaSetDevice(h->cfg.device));
     if (st != DX_OK)
         return st;
@@ -1360,6 +1355,23 @@ int dx_attn_append_context(dx_attn_t* h, const void* k_src, const void* v_src, c
     void* args[] = {&a};
     dim3 grid((unsigned) ((threads + 255) / 256), batch, c.num_kv_heads);
     st = check_cuda(h, cudaLaunchKernel(h->k_append.fn, grid, dim3(256), args, 0, reinterpret_cast<cudaStream_t>(cuda_stream)));
+    if (st == DX_OK)
+        h->launches.fetch_add(1);
+    return st;
+}
+
+int dx_attn_selftest_wait_timeout(dx_attn_t* h, int32_t poll_limit, void* cuda_stream)
+{
+    if (!h || poll_limit < 1 || poll_limit > (1 << 20))
+        return DX_ERR_BAD_ARG;
+    int st = check_cuda(h, cudaSetDevice(h->cfg.device));
+    if (st != DX_OK)
+        return st;
+    int32_t* status = h->status_dev;
+    int limit = poll_limit;
+    void* args[] = {&status, &limit};
+    st = check_cuda(h, cudaLaunchKernel(reinterpret_cast<const void*>(&wait_timeout_selftest_kernel), dim3(1), dim3(32),
+                           args, 0, reinterpret_cast<cudaStream_t>(cuda_stream)));
     if (st == DX_OK)
         h->launches.fetch_add(1);
     return st;

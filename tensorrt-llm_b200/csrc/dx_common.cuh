@@ -78,7 +78,16 @@ __host__ __device__ __forceinline__ int cyclic_slot(int tok, int sink, int cycli
     return tok < sink ? tok : sink + (tok - sink) % cyclic_len;
 }
 
-static constexpr int32_t STATUS_TIMEOUT = 5;
+// Values of the device status word (0 = ok).  The first report of a step stays (atomicCAS from 0): later ones do
+// not overwrite it.
+static constexpr int32_t STATUS_TIMEOUT = 5;       // a bounded wait ran out
+static constexpr int32_t STATUS_NO_BLOCKS = 6;     // dx_kv_cache_step: free list or table row exhausted
+static constexpr int32_t STATUS_PLAN_EXCEEDED = 7; // a device length needs more partitions than the launch has
+
+__device__ __forceinline__ void report_status(int32_t* status, int32_t what)
+{
+    atomicCAS(status, 0, what);
+}
 
 // ----------------------------------------------------------------------------------------------
 // Stream-K schedule of the grouped-head kernels.  The rows of the batch - (sequence b, kv-head slice y), y fastest -
@@ -216,19 +225,32 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
 }
 
 // Bounded wait: every spin in this library has an iteration limit.  Returns false when it gave up,
-// either because the limit ran out or because another CTA already reported a time-out in the
-// status word (so that one stuck copy cannot add up to many serial time-outs).
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, const int32_t* status)
+// either because the limit ran out or (CHECK_STATUS) because the status word already holds a report
+// (so that one stuck copy cannot add up to many serial time-outs).
+template <bool CHECK_STATUS = true>
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, const int32_t* status, int limit)
 {
 #pragma unroll 1
-    for (int it = 0; it < (1 << 20); ++it)
+    for (int it = 0; it < limit; ++it)
     {
         if (mbar_try_wait(bar, parity))
             return true;
-        if ((it & 255) == 255 && *reinterpret_cast<const volatile int32_t*>(status) != 0)
+        if (CHECK_STATUS && (it & 255) == 255 && *reinterpret_cast<const volatile int32_t*>(status) != 0)
             return false;
     }
     return false;
+}
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, const int32_t* status)
+{
+    return mbar_wait_limit<true>(bar, parity, status, 1 << 20);
+}
+
+// After a wait gave up: waits once more, with a limit of its own and without looking at the status word, for a
+// copy that was already requested, so that nothing is in flight into this CTA's shared memory when it exits.
+__device__ __forceinline__ void mbar_drain(uint64_t* bar, uint32_t parity)
+{
+    (void) mbar_wait_limit<false>(bar, parity, nullptr, 1 << 22);
 }
 
 __device__ __forceinline__ void fence_mbar_init()

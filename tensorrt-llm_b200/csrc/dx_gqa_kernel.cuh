@@ -233,6 +233,8 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
     {
         int cs, ct, np;
         partition_of(a.seq_len[blockIdx.z], a.chunk_tokens, (int) blockIdx.x, cs, ct, np);
+        if (np > (int) gridDim.x && blockIdx.x == 0 && threadIdx.x == 0)
+            report_status(a.status, STATUS_PLAN_EXCEEDED); // the tokens beyond the last partition are not attended to
         if ((int) blockIdx.x >= np)
             return; // ragged batch: this sequence uses fewer partitions
     }
@@ -291,6 +293,8 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
         }
         const float deq = __ldg(a.scale_quant_orig);
         const int total = a.seq_len[b];
+        if (a.streamk && total > (int) cur.nb * TG && threadIdx.x == 0)
+            report_status(a.status, STATUS_PLAN_EXCEEDED); // longer than the host length the ranges were laid out for
         ctoks = max(0, min(ctoks, total - chunk_start)); // the schedule counts host lengths; the device length decides
         const int n_groups = (ctoks + TG - 1) / TG;
         const int new_pos = total - 1;
@@ -741,8 +745,12 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
         }
         fold();
 
-        if (timed_out && lane == 0)
-            atomicExch(a.status, STATUS_TIMEOUT);
+        if (timed_out)
+        {
+            if (lane == 0)
+                report_status(a.status, STATUS_TIMEOUT);
+            asm volatile("cp.async.wait_all;" ::: "memory"); // the ring is reused below and the CTA then exits
+        }
 
         // ---- per-warp results -> shared memory, then combine the 4 warps ----
 #pragma unroll

@@ -27,7 +27,6 @@ struct KvStepArgs
     int32_t n_free;
 };
 
-static constexpr int32_t STATUS_NO_BLOCKS = 6;
 
 __global__ void __launch_bounds__(1024) kv_cache_step_kernel(const KvStepArgs a)
 {
@@ -81,7 +80,7 @@ __global__ void __launch_bounds__(1024) kv_cache_step_kernel(const KvStepArgs a)
             }
             else
             {
-                atomicExch(a.status, STATUS_NO_BLOCKS);
+                report_status(a.status, STATUS_NO_BLOCKS);
             }
         }
         if (b < a.batch)

@@ -136,7 +136,10 @@ __global__ void __launch_bounds__(128) lse_merge_kernel(const AttnArgs a)
     const int b = row / a.num_heads;
     const int total = a.seq_len[b];
     griddep_wait(); // launched with programmatic stream serialisation: the partials are complete after this
-    const int n = (total + a.chunk_tokens - 1) / a.chunk_tokens; // partitions this sequence used (partition_of)
+    // partitions this sequence used (partition_of), never more than the launch had and never fewer than one: a
+    // device length beyond what the call was planned for was reported by the attention kernel, and the merge
+    // must not read another row's partials because of it
+    const int n = max(1, min((total + a.chunk_tokens - 1) / a.chunk_tokens, a.nsplit));
     merge_row<T, DH>(a, row, n, lane);
 }
 

@@ -52,6 +52,8 @@ __global__ void __launch_bounds__(128) mha_int8_decode_kernel(const AttnArgs a)
     const int total = a.seq_len[b];
     int chunk_start, ctoks, nparts;
     partition_of(total, a.chunk_tokens, chunk, chunk_start, ctoks, nparts);
+    if (nparts > (int) gridDim.x && chunk == 0 && threadIdx.x == 0)
+        report_status(a.status, STATUS_PLAN_EXCEEDED); // the tokens beyond the last partition are not attended to
     if (chunk >= nparts)
         return; // ragged batch: this sequence uses fewer partitions
     griddep_launch_dependents(); // the merge kernel may be scheduled; it waits for this grid to finish
@@ -170,7 +172,8 @@ __global__ void __launch_bounds__(128) mha_int8_decode_kernel(const AttnArgs a)
     };
 
     bool timed_out = false;
-    for (int i = 0; i < my_groups; ++i)
+    int i = 0;
+    for (; i < my_groups; ++i)
     {
         const int s = i % STAGES;
         const uint32_t parity = (i / STAGES) & 1;
@@ -295,8 +298,14 @@ __global__ void __launch_bounds__(128) mha_int8_decode_kernel(const AttnArgs a)
     }
     fold();
 
-    if (timed_out && lane == 0)
-        atomicExch(a.status, STATUS_TIMEOUT);
+    if (timed_out)
+    {
+        if (lane == 0)
+            report_status(a.status, STATUS_TIMEOUT);
+        // the copies already requested (groups i .. i + STAGES - 1) must have landed before the CTA exits
+        for (int j = i; j < min(i + STAGES, my_groups); ++j)
+            mbar_drain(&bars[j % STAGES], (j / STAGES) & 1);
+    }
 
     // ---- combine the row sub-groups of the warp ----
 #pragma unroll

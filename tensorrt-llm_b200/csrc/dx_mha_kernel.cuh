@@ -101,6 +101,8 @@ __global__ void __launch_bounds__(128) mha_decode_kernel(const AttnArgs a)
     const int total = a.seq_len[b]; // tokens to attend to, new token included
     int chunk_start, ctoks, nparts;
     partition_of(total, a.chunk_tokens, chunk, chunk_start, ctoks, nparts);
+    if (nparts > (int) gridDim.x && chunk == 0 && threadIdx.x == 0)
+        report_status(a.status, STATUS_PLAN_EXCEEDED); // the tokens beyond the last partition are not attended to
     if (chunk >= nparts)
         return;                                       // ragged batch: this sequence uses fewer partitions
     const int n_groups = (ctoks + TG - 1) / TG;
@@ -196,7 +198,8 @@ __global__ void __launch_bounds__(128) mha_decode_kernel(const AttnArgs a)
         acc[i] = 0.f;
 
     bool timed_out = false;
-    for (int i = 0; i < my_groups; ++i)
+    int i = 0;
+    for (; i < my_groups; ++i)
     {
         const int s = i % STAGES;
         const uint32_t parity = (i / STAGES) & 1;
@@ -306,7 +309,10 @@ __global__ void __launch_bounds__(128) mha_decode_kernel(const AttnArgs a)
     if (timed_out)
     {
         if (lane == 0)
-            atomicExch(a.status, STATUS_TIMEOUT);
+            report_status(a.status, STATUS_TIMEOUT);
+        // the copies already requested (groups i .. i + STAGES - 1) must have landed before the CTA exits
+        for (int j = i; j < min(i + STAGES, my_groups); ++j)
+            mbar_drain(&bars[j % STAGES], (j / STAGES) & 1);
         // fall through: the CTA still meets its barriers below and writes what it has.
     }
 

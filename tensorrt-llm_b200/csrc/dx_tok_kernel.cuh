@@ -101,6 +101,8 @@ __global__ void __launch_bounds__(128, TokTraits<GP>::MIN_BLOCKS)
     {
         int cs, ct, np;
         partition_of(a.seq_len[blockIdx.z], a.chunk_tokens, (int) blockIdx.x, cs, ct, np);
+        if (np > (int) gridDim.x && blockIdx.x == 0 && threadIdx.x == 0)
+            report_status(a.status, STATUS_PLAN_EXCEEDED); // the tokens beyond the last partition are not attended to
         if ((int) blockIdx.x >= np)
             return;
     }
@@ -116,6 +118,7 @@ __global__ void __launch_bounds__(128, TokTraits<GP>::MIN_BLOCKS)
     uint64_t* full_k0 = bars + NST;     // K(0) of a piece has landed
     uint64_t* bar_mma = bars + NST + 1; // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NST + 3);
+    uint64_t* bar_drain = bars + NST + 4; // only used after a time-out: the MMAs issued so far have completed
 
     if (warp == 0)
     {
@@ -131,6 +134,7 @@ __global__ void __launch_bounds__(128, TokTraits<GP>::MIN_BLOCKS)
         mbar_init(full_k0, 128);
         mbar_init(&bar_mma[0], 1);
         mbar_init(&bar_mma[1], 1);
+        mbar_init(bar_drain, 1);
         fence_mbar_init();
     }
     __syncthreads(); // barriers initialised, TMEM address published
@@ -177,6 +181,8 @@ __global__ void __launch_bounds__(128, TokTraits<GP>::MIN_BLOCKS)
             final_out = a.nsplit == 1;
         }
         const int total = a.seq_len[b];
+        if (a.streamk && total > (int) cur.nb * TT && threadIdx.x == 0)
+            report_status(a.status, STATUS_PLAN_EXCEEDED); // longer than the host length the ranges were laid out for
         ctoks = max(0, min(ctoks, total - chunk_start)); // the schedule counts host lengths; the device length decides
         const int n_tiles = (ctoks + TT - 1) / TT;
         const int new_pos = total - 1;
@@ -576,7 +582,11 @@ __global__ void __launch_bounds__(128, TokTraits<GP>::MIN_BLOCKS)
     if (fail)
     {
         if (tid == 0)
-            atomicExch(a.status, STATUS_TIMEOUT);
+        {
+            report_status(a.status, STATUS_TIMEOUT);
+            umma_commit(bar_drain); // no MMA may still be writing tensor memory when it is freed below
+            mbar_drain(bar_drain, 0);
+        }
         asm volatile("cp.async.wait_all;" ::: "memory");
     }
     // ---- free tensor memory (every path reaches this) ----

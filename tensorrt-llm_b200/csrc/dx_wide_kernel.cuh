@@ -93,6 +93,8 @@ __global__ void __launch_bounds__(128, WideTraits<DH>::MIN_BLOCKS) wide_decode_k
     const int total = a.seq_len[b];
     int chunk_start, ctoks, nparts;
     partition_of(total, a.chunk_tokens, chunk, chunk_start, ctoks, nparts);
+    if (nparts > (int) gridDim.x && chunk == 0 && threadIdx.x == 0)
+        report_status(a.status, STATUS_PLAN_EXCEEDED); // the tokens beyond the last partition are not attended to
     if (chunk >= nparts)
         return;
     griddep_launch_dependents();
@@ -109,6 +111,7 @@ __global__ void __launch_bounds__(128, WideTraits<DH>::MIN_BLOCKS) wide_decode_k
     uint64_t* full_k0 = bars + NST;     // K(0) has landed
     uint64_t* bar_mma = bars + NST + 1; // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NST + 3);
+    uint64_t* bar_drain = bars + NST + 4; // only used after a time-out: the MMAs issued so far have completed
 
     const int64_t* krow = a.block_ptrs + (int64_t) b * 2 * a.max_blocks_per_seq;
     const int64_t* vrow = krow + a.max_blocks_per_seq;
@@ -200,6 +203,7 @@ __global__ void __launch_bounds__(128, WideTraits<DH>::MIN_BLOCKS) wide_decode_k
         mbar_init(full_k0, 128);
         mbar_init(&bar_mma[0], 1);
         mbar_init(&bar_mma[1], 1);
+        mbar_init(bar_drain, 1);
         fence_mbar_init();
     }
     __syncthreads(); // barriers initialised, TMEM address published
@@ -445,7 +449,11 @@ __global__ void __launch_bounds__(128, WideTraits<DH>::MIN_BLOCKS) wide_decode_k
     if (fail)
     {
         if (tid == 0)
-            atomicExch(a.status, STATUS_TIMEOUT);
+        {
+            report_status(a.status, STATUS_TIMEOUT);
+            umma_commit(bar_drain); // no MMA may still be writing tensor memory when it is freed below
+            mbar_drain(bar_drain, 0);
+        }
         asm volatile("cp.async.wait_all;" ::: "memory");
     }
     else if (warp_active)

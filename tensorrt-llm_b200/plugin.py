@@ -90,6 +90,7 @@ EXPORTED_SYMBOLS = [
     "dx_attn_enqueue_generation", "dx_attn_enqueue_generation_host", "dx_attn_host_sync", "dx_kv_cache_step", "dx_attn_validate", "dx_attn_plan", "dx_attn_plan_lengths",
     "dx_attn_device_status", "dx_attn_last_cuda_error", "dx_attn_launch_count",
     "dx_attn_enqueue_generation_static_scratch", "dx_attn_static_scratch_bytes", "dx_attn_append_context",
+    "dx_attn_selftest_wait_timeout",
 ]
 
 
@@ -145,6 +146,8 @@ def load_library() -> ctypes.CDLL:
     lib.dx_attn_plan.restype = ctypes.c_int
     lib.dx_attn_plan.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(ctypes.c_int32),
                                  ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]
+    lib.dx_attn_selftest_wait_timeout.restype = ctypes.c_int
+    lib.dx_attn_selftest_wait_timeout.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]
     lib.dx_attn_device_status.restype = ctypes.c_int
     lib.dx_attn_device_status.argtypes = [ctypes.c_void_p]
     lib.dx_attn_last_cuda_error.restype = ctypes.c_int
@@ -309,7 +312,7 @@ class GPTAttentionPlugin:
                            medusa_packed_mask: Optional[torch.Tensor] = None,
                            medusa_position_offsets: Optional[torch.Tensor] = None,
                            relative_attention_bias: Optional[torch.Tensor] = None, max_distance: int = 0,
-                           stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+                           stream: Optional[torch.cuda.Stream] = None, static_scratch: bool = False) -> torch.Tensor:
         """qkv: T [B, (H+2Hkv)*Dh] (device); sequence_length: int32 [B] (device, includes the new token);
         host_past_key_value_lengths: int32 [B] (host); kv_cache_block_pointers: int64 [B, 2, M] (device).
         Appends the new token to the cache and returns the attention output T [B, H*Dh].  Asynchronous.
@@ -320,7 +323,9 @@ class GPTAttentionPlugin:
         [B, Q, ceil(Q / 32)] on the device (and optionally medusa_position_offsets int32 [B, Q]); qkv and the
         result then have B * Q rows and sequence_length includes all Q new tokens.
         Relative attention bias (plugin built with position_embedding_type 5): relative_attention_bias T
-        [H, max_seq_len, max_seq_len] on the device, or with max_distance > 0 the bucket table T [H, buckets]."""
+        [H, max_seq_len, max_seq_len] on the device, or with max_distance > 0 the bucket table T [H, buckets].
+        static_scratch: no workspace is allocated or passed; the step runs through
+        dx_attn_enqueue_generation_static_scratch on the fixed scratch array inside the library."""
         if not qkv.is_cuda:
             raise DecodeAttnError(DX_ERR_BAD_ARG, "enqueue_generation needs device tensors (no CPU path exists)")
         if qkv.dtype != self.dtype:
@@ -331,7 +336,7 @@ class GPTAttentionPlugin:
             out = torch.empty(B, self.num_heads * self.head_size, dtype=self.dtype, device=qkv.device)
         hp = host_past_key_value_lengths.to(torch.int32).contiguous()
         max_past = int(hp.max()) if hp.numel() else 0
-        if workspace is None:
+        if workspace is None and not static_scratch:
             workspace = self._ensure_workspace(B, max_past, qkv.device)
         p, _ = self._params(qkv, sequence_length, hp, kv_cache_block_pointers, kv_orig_quant_scale,
                             kv_quant_orig_scale, out, workspace, max_attention_window,
@@ -342,7 +347,9 @@ class GPTAttentionPlugin:
                             None if relative_attention_bias is None else relative_attention_bias.contiguous(),
                             max_distance)
         s = stream if stream is not None else torch.cuda.current_stream(qkv.device)
-        st = self.lib.dx_attn_enqueue_generation(self._h, ctypes.byref(p), ctypes.c_void_p(s.cuda_stream))
+        enqueue = (self.lib.dx_attn_enqueue_generation_static_scratch if static_scratch
+                   else self.lib.dx_attn_enqueue_generation)
+        st = enqueue(self._h, ctypes.byref(p), ctypes.c_void_p(s.cuda_stream))
         if st != DX_OK:
             raise DecodeAttnError(st, "dx_attn_enqueue_generation")
         return out

@@ -29,7 +29,9 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
-REF = Path(os.environ.get("DX_REFERENCE_DIR", "/root/reference"))
+if not os.environ.get("DX_REFERENCE_DIR"):
+    raise SystemExit("set DX_REFERENCE_DIR to the root of a TensorRT-LLM source tree")
+REF = Path(os.environ["DX_REFERENCE_DIR"])
 
 
 def load_ref_manager():

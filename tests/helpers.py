@@ -6,10 +6,12 @@ import os
 
 import torch
 
+import workloads
+
 import oracle
 
-# Where the timing reports of the GPU tests go (the one folder a remote GPU run brings back).
-REPORT_DIR = os.environ.get("DX_TEST_REPORT_DIR", "gpurun_out")
+# Where the timing reports of the GPU tests go.
+REPORT_DIR = os.environ.get("DX_TEST_REPORT_DIR", "test_reports")
 
 # Tolerances of the attention output against the fp32 oracle (bf16/fp16 outputs).
 MAX_ABS_TOL = 2e-2
@@ -46,7 +48,7 @@ def expected_changed_positions(w_cpu):
 
 
 def gpu_step_and_compare(pkg, cfg, *, lengths=None, multi_block_mode=None, device="cuda:0", check_twice=True):
-    wl = pkg.workloads
+    wl = workloads
     w_cpu = wl.build_workload(cfg, "cpu", lengths=lengths)
     w = wl.to_device(w_cpu, device)
     plugin = wl.make_plugin(cfg, torch.device(device).index or 0, multi_block_mode=multi_block_mode)

@@ -38,7 +38,8 @@ def test_library_exports_every_declared_symbol(pkg):
 def test_struct_layout_matches_ctypes_and_cpp_mirror_links(pkg, tmp_path):
     exe = tmp_path / "host_mirror_check"
     lib = pkg.library_path()
-    subprocess.run(["g++", "-std=c++17", "-O1", str(PKG / "csrc" / "host_mirror_check.cpp"), "-o", str(exe),
+    subprocess.run(["g++", "-std=c++17", "-O1", str(Path(__file__).parent / "host_mirror_check.cpp"),
+                    "-I", str(PKG / "csrc"), "-o", str(exe),
                     str(lib), f"-Wl,-rpath,{lib.parent}"], check=True)
     out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
     m = re.search(r"abi=(\d+) config=(\d+) params=(\d+)", out)

@@ -8,6 +8,8 @@ import numpy as np
 import pytest
 import torch
 
+import workloads
+
 import oracle
 from helpers import CACHE_MODE, MAX_ABS_TOL, MEAN_ABS_TOL, REPORT_DIR
 
@@ -16,7 +18,7 @@ GOLDEN = Path(__file__).resolve().parent / "golden"
 
 
 def _setup(pkg, cfg, lens, seed=11, scale=None):
-    wl = pkg.workloads
+    wl = workloads
     w = wl.build_workload(cfg, "cpu", lengths=lens)  # only for the pool geometry and the page table
     g = torch.Generator().manual_seed(seed)
     L = int(lens.max())
@@ -29,7 +31,7 @@ def _setup(pkg, cfg, lens, seed=11, scale=None):
 @pytest.mark.parametrize("cache", ["none", "int8", "fp8"])
 @pytest.mark.parametrize("dh,tpb", [(64, 16), (128, 64), (128, 128)])
 def test_append_matches_oracle_bit_exact(pkg, dtype, cache, dh, tpb):
-    wl = pkg.workloads
+    wl = workloads
     cfg = wl.DecodeConfig("ctx", 4, 6, 3, dh, dtype, cache, tpb, 1, 300, True, 17)
     lens = torch.tensor([1, tpb, tpb + 1, 300], dtype=torch.int32)
     w, k, v, L = _setup(pkg, cfg, lens)
@@ -52,7 +54,7 @@ def test_append_known_answer_inputs(pkg):
     cpp/tests/runtime/transposeKVKernelTest.cpp:152-225) through the product writer, fp16 activations:
     INT8 bytes equal the test's expectation exactly; FP8 bytes equal the kernel chain (oracle) exactly and the
     test's float-product expectation on all but a few ties of the half product."""
-    wl = pkg.workloads
+    wl = workloads
     qg = np.load(GOLDEN / "quant_golden.npz")
     x = torch.from_numpy(qg["kat_x"]).to(torch.float16)  # 4096 values = [B 2, H 1, L 16, Dh 128]
     for cache, key in (("int8", "kat_int8"), ("fp8", "kat_fp8")):
@@ -87,7 +89,7 @@ def test_append_known_answer_inputs(pkg):
 def test_prompt_then_decode_round_trip(pkg):
     """Fill the cache with the product writer from un-quantised K/V, then run a decode step and compare
     with attention computed directly from the prompt tensors (dequantised through the oracle's quantiser)."""
-    wl = pkg.workloads
+    wl = workloads
     cfg = wl.DecodeConfig("rt", 3, 16, 2, 128, torch.bfloat16, "fp8", 64, 90, 400, True, 23)
     lens = wl.draw_lengths(cfg)
     w, k, v, L = _setup(pkg, cfg, lens, seed=5)
@@ -134,7 +136,7 @@ def test_report_append_bandwidth(pkg):
     bytes moved per second in append_context.jsonl of the report directory; asserts only that it ran."""
     import json
     import os
-    wl = pkg.workloads
+    wl = workloads
     cfg = wl.DecodeConfig("ctxbw", 32, 64, 8, 128, torch.bfloat16, "fp8", 64, 4095, 4095, True, 9)
     lens = torch.full((32,), 4095, dtype=torch.int32)
     w = wl.build_workload(cfg, "cuda:0", lengths=lens)

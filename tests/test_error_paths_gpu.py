@@ -6,12 +6,14 @@ import dataclasses
 import pytest
 import torch
 
+import workloads
+
 pytestmark = pytest.mark.gpu
 
 
 @pytest.fixture()
 def setup(pkg):
-    wl = pkg.workloads
+    wl = workloads
     cfg = wl.DecodeConfig("err", 3, 16, 2, 128, torch.bfloat16, "fp8", 64, 2000, 3000, True, 1)
     w = wl.to_device(wl.build_workload(cfg, "cpu"), "cuda:0")
     plugin = wl.make_plugin(cfg, 0)
@@ -100,7 +102,7 @@ def test_validate_catches_corrupted_tables(setup):
 def test_guard_bytes_around_pool_and_workspace_stay_intact(pkg):
     """Poisoned guard regions before and after the KV pool, the output and the workspace: a step must
     not write outside its buffers (stand-in for compute-sanitizer, which is closed on this pool)."""
-    wl = pkg.workloads
+    wl = workloads
     cfg = wl.DecodeConfig("guard", 5, 8, 2, 128, torch.bfloat16, "int8", 32, 900, 1500, True, 12)
     w_cpu = wl.build_workload(cfg, "cpu")
     G = 4096
@@ -122,5 +124,95 @@ def test_guard_bytes_around_pool_and_workspace_stay_intact(pkg):
         assert bool((wsb[:G] == 0x5A).all()) and bool((wsb[-G:] == 0x5A).all())
         assert bool((outb[:G] == -7.0).all()) and bool((outb[-G:] == -7.0).all())
         assert torch.isfinite(outb[G:G + nout].float()).all()
+    finally:
+        plugin.close()
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Device-side failure reporting.  Every wait in the kernels has a poll limit; when one runs out the kernel
+# records a time-out in the handle's status word and returns.  The tests below make that happen without
+# hanging or faulting anything: a self-test kernel waits (a few hundred polls) on a barrier that nothing ever
+# arrives on, and the attention kernels are then launched while the word still holds that report, which makes
+# every wait in them give up after at most 256 polls.
+# ---------------------------------------------------------------------------------------------------------
+TIMEOUT_CONFIGS = {
+    "gqa_fp8": ("t_gqa", 4, 16, 2, 128, torch.bfloat16, "fp8", 64, 1500, 2500, True, 31),
+    "gqa_int8_16heads": ("t_gqa16h", 3, 32, 2, 128, torch.bfloat16, "int8", 128, 700, 1400, True, 32),
+    "gqa_bf16_cache": ("t_gqa16", 3, 8, 2, 128, torch.bfloat16, "none", 64, 600, 1200, True, 33),
+    "mha_int8": ("t_mha8", 4, 8, 8, 128, torch.bfloat16, "int8", 64, 500, 900, False, 34),
+    "mha_fp16": ("t_mha", 4, 6, 6, 64, torch.float16, "none", 64, 300, 800, True, 35),
+    "wide_mqa_fp8": ("t_wide", 4, 71, 1, 64, torch.float16, "fp8", 64, 300, 1200, True, 36),
+}
+
+
+@pytest.mark.parametrize("name", sorted(TIMEOUT_CONFIGS))
+def test_bounded_wait_expiry_is_reported_and_cleared(pkg, name):
+    from helpers import MAX_ABS_TOL, MEAN_ABS_TOL, oracle_step
+    wl, P = workloads, pkg.plugin
+    cfg = wl.DecodeConfig(*TIMEOUT_CONFIGS[name])
+    w_cpu = wl.build_workload(cfg, "cpu")
+    w = wl.to_device(w_cpu, "cuda:0")
+    plugin = wl.make_plugin(cfg, 0)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    try:
+        assert plugin.lib.dx_attn_selftest_wait_timeout(plugin._h, 0, stream) == P.DX_ERR_BAD_ARG
+        # (1) a wait that nothing satisfies runs out after 300 polls; the kernel records it and returns
+        assert plugin.lib.dx_attn_selftest_wait_timeout(plugin._h, 300, stream) == P.DX_OK
+        # (2) a real step enqueued while the report is pending: its waits give up early, the kernels take their
+        #     time-out exits (rings drained, tensor memory freed) and the stream stays usable
+        out_bad = wl.run_step(plugin, w)
+        torch.cuda.synchronize()
+        del out_bad  # undefined by contract
+        # (3) the report is read once, then the word is clear again
+        assert plugin.device_status() == P.DX_ERR_TIMEOUT
+        assert plugin.device_status() == P.DX_OK
+        # (4) the next step is a normal one: pool bytes and output as the oracle has them
+        w.pool.copy_(w_cpu.pool.cuda())
+        out = wl.run_step(plugin, w)
+        torch.cuda.synchronize()
+        assert plugin.device_status() == P.DX_OK
+        ref, pool_ref = oracle_step(w_cpu)
+        assert torch.equal(w.pool.cpu(), pool_ref)
+        err = (out.float().cpu() - ref).abs()
+        assert err.max().item() < MAX_ABS_TOL and err.mean().item() < MEAN_ABS_TOL
+    finally:
+        plugin.close()
+
+
+@pytest.mark.parametrize("streamk", [False, True])
+def test_device_length_beyond_the_planned_length_is_reported(pkg, streamk, monkeypatch):
+    """host_past_key_value_lengths are what a step is planned with.  A device length that needs more partitions
+    than that plan has cannot be served (the surplus tokens have no CTA); it is reported as DX_ERR_BOUNDS instead
+    of being dropped silently, the merge stays inside its own rows, and nothing outside the buffers is touched."""
+    wl, P = workloads, pkg.plugin
+    if streamk:
+        cfg = wl.DecodeConfig("exceed_sk", 32, 32, 8, 128, torch.bfloat16, "fp8", 64, 3800, 4000, True, 41)
+        host_len = 3000
+    else:
+        monkeypatch.setenv("DX_ATTN_STREAMK", "0")
+        monkeypatch.setenv("DX_ATTN_FORCE_CHUNK", "512")
+        cfg = wl.DecodeConfig("exceed", 3, 16, 2, 128, torch.bfloat16, "fp8", 64, 2800, 3000, True, 42)
+        host_len = 1000
+    w = wl.to_device(wl.build_workload(cfg, "cpu"), "cuda:0")   # tables and pool hold the (long) device lengths
+    plugin = wl.make_plugin(cfg, 0)
+    try:
+        short = torch.full((cfg.batch,), host_len, dtype=torch.int32)
+        plan = plugin.plan(cfg.batch, host_len, short)
+        assert ("stream_k_ctas" in plan) == streamk, plan
+        G = 4096
+        need = plugin.get_workspace_size(cfg.batch, host_len)
+        wsb = torch.full((need + 2 * G,), 0x5A, dtype=torch.uint8, device="cuda:0")
+        out = plugin.enqueue_generation(w.qkv, w.sequence_length, short, w.kv_cache_block_pointers,
+                                        w.kv_orig_quant_scale, w.kv_quant_orig_scale, workspace=wsb[G:G + need],
+                                        max_attention_window=w.max_blocks_per_seq * cfg.tokens_per_block)
+        torch.cuda.synchronize()
+        assert plugin.device_status() == P.DX_ERR_BOUNDS
+        assert plugin.device_status() == P.DX_OK
+        assert bool((wsb[:G] == 0x5A).all()) and bool((wsb[-G:] == 0x5A).all())
+        del out
+        # with the true lengths the same handle serves the step
+        out = wl.run_step(plugin, w)
+        torch.cuda.synchronize()
+        assert plugin.device_status() == P.DX_OK and torch.isfinite(out.float()).all()
     finally:
         plugin.close()

@@ -10,6 +10,8 @@ import dataclasses
 import pytest
 import torch
 
+import workloads
+
 import oracle
 from helpers import CACHE_MODE, MAX_ABS_TOL, MEAN_ABS_TOL
 
@@ -17,7 +19,7 @@ pytestmark = pytest.mark.gpu
 
 
 def _run(pkg, cfg, w, multi_block=None):
-    wl = pkg.workloads
+    wl = workloads
     plugin = wl.make_plugin(cfg, 0, multi_block_mode=multi_block)
     try:
         out = wl.run_step(plugin, w)
@@ -28,10 +30,15 @@ def _run(pkg, cfg, w, multi_block=None):
         plugin.close()
 
 
-@pytest.mark.parametrize("name", ["c2", "c3", "c4", "c5"])
-def test_full_size_properties(pkg, name, monkeypatch):
-    wl = pkg.workloads
-    cfg = wl.CONFIGS[name]
+# (config, tensor-parallel degree): the whole job on one GPU, and one rank's shard of the 4- and 8-way jobs (the
+# 8-way shards of c4 and c5 run classic equal partitions at full length, the others stream-K ranges)
+CASES = [("c2", 1), ("c3", 1), ("c4", 1), ("c5", 1), ("c4", 4), ("c4", 8), ("c5", 4), ("c5", 8)]
+
+
+@pytest.mark.parametrize("name,tp", CASES)
+def test_full_size_properties(pkg, name, tp, monkeypatch):
+    wl = workloads
+    cfg = wl.shard_config(wl.CONFIGS[name], tp)
     w = wl.build_workload(cfg, "cuda:0")
     B, H, Hkv, Dh, tpb = cfg.batch, cfg.num_heads, cfg.num_kv_heads, cfg.head_size, cfg.tokens_per_block
     row = Dh * cfg.elem_bytes
@@ -94,3 +101,40 @@ def test_full_size_properties(pkg, name, monkeypatch):
         o = out[b].float().cpu().view(Hkv, G, Dh)
         eps = 2e-2
         assert bool((o >= lo[:, None, :] - eps).all()) and bool((o <= hi[:, None, :] + eps).all())
+
+
+
+def test_c5_with_at_least_16_partitions_per_kv_head(pkg, monkeypatch):
+    """The long-context configuration with its sequences cut into 1024-token partitions (16 to 33 CTAs per
+    (sequence, kv head)) merged by the log-sum-exp kernel, at full size: pool bit-exact, three sequences against
+    the oracle at full length, and agreement with the default plan."""
+    wl = workloads
+    cfg = wl.CONFIGS["c5"]
+    w = wl.build_workload(cfg, "cuda:0")
+    pool_before = w.pool.clone()
+    out_default = _run(pkg, cfg, w)
+    pool_default = w.pool.clone()
+    w.pool.copy_(pool_before)
+    monkeypatch.setenv("DX_ATTN_STREAMK", "0")
+    monkeypatch.setenv("DX_ATTN_FORCE_CHUNK", "1024")
+    plugin = wl.make_plugin(cfg, 0)
+    try:
+        plan = plugin.plan(cfg.batch, int(w.host_past_key_value_lengths.max()), w.host_past_key_value_lengths)
+        assert plan["tokens_per_partition"] == 1024 and plan["num_partitions"] >= 16, plan
+        assert int(w.host_past_key_value_lengths.min()) + 1 >= 16 * 1024
+        out = wl.run_step(plugin, w)
+        torch.cuda.synchronize()
+        assert plugin.device_status() == 0
+    finally:
+        plugin.close()
+    assert torch.equal(w.pool, pool_default)
+    d = (out.float() - out_default.float()).abs()
+    assert d.max().item() < MAX_ABS_TOL and d.mean().item() < MEAN_ABS_TOL
+    idx = [0, cfg.batch // 2, cfg.batch - 1]
+    ref = oracle.decode_attention_reference(
+        w.qkv.cpu()[idx], w.sequence_length.cpu()[idx], w.pool.cpu(), w.offset_table[idx], num_heads=cfg.num_heads,
+        num_kv_heads=cfg.num_kv_heads, head_size=cfg.head_size, tokens_per_block=cfg.tokens_per_block,
+        cache_mode=CACHE_MODE[cfg.cache], kv_scale_orig_quant=w.scale_orig_quant,
+        kv_scale_quant_orig=w.scale_quant_orig, append=False)
+    err = (out[idx].float().cpu() - ref).abs()
+    assert err.max().item() < MAX_ABS_TOL and err.mean().item() < MEAN_ABS_TOL, (err.max().item(), err.mean().item())

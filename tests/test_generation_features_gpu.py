@@ -9,6 +9,8 @@ from pathlib import Path
 import pytest
 import torch
 
+import workloads
+
 import oracle
 from oracle.attention_general_ref import decode_attention_general_reference
 from helpers import CACHE_MODE, MAX_ABS_TOL, MEAN_ABS_TOL, REPORT_DIR
@@ -36,7 +38,7 @@ class Case:
 
 def _build(pkg, c: Case):
     """Workload with every cache slot filled; returns (cpu workload, extras dict)."""
-    wl = pkg.workloads
+    wl = workloads
     g = torch.Generator().manual_seed(c.seed)
     nseq = c.requests * c.beam
     past_req = torch.randint(c.past_lo, c.past_hi + 1, (c.requests,), generator=g, dtype=torch.int32)
@@ -78,14 +80,14 @@ def _oracle(w, ex, pool=None):
 def _plugin(pkg, c: Case):
     P = pkg.plugin
     return P.GPTAttentionPlugin(
-        num_heads=c.heads[0], num_kv_heads=c.heads[1], head_size=c.dh, kv_cache_quant_mode=pkg.workloads.DecodeConfig(
+        num_heads=c.heads[0], num_kv_heads=c.heads[1], head_size=c.dh, kv_cache_quant_mode=workloads.DecodeConfig(
             "q", 1, 1, 1, c.dh, c.dtype, c.cache, c.tpb, 1, 1, False, 0).quant_mode,
         tokens_per_block=c.tpb, multi_block_mode=True, type_id=c.dtype,
         position_embedding_type=P.PositionEmbeddingType.alibi if c.alibi else P.PositionEmbeddingType.learned_absolute)
 
 
 def _run_product(pkg, c, w_cpu, ex):
-    wl = pkg.workloads
+    wl = workloads
     w = wl.to_device(w_cpu, "cuda:0")
     plugin = _plugin(pkg, c)
     dev = lambda t: None if t is None else t.to("cuda:0")
@@ -211,7 +213,7 @@ def test_oracle_matches_reference_kernel_features(pkg, name):
     c, tol = REF_CASES[name]
     w_cpu, ex = _build(pkg, c)
     ref, pool_ref = _oracle(w_cpu, ex)
-    w = pkg.workloads.to_device(w_cpu, "cuda:0")
+    w = workloads.to_device(w_cpu, "cuda:0")
     out = _run_reference_ext(w, ex)
     # bit-exact: the bytes the reference kernel stored, and the (cyclic) slots it stored them in
     assert torch.equal(w.pool.cpu(), pool_ref)
@@ -233,7 +235,7 @@ def test_beams_with_bias_and_rotary_embedding(pkg):
     qkv_pre = oracle.apply_bias_rope(w_cpu.qkv, w_cpu.sequence_length, num_heads=cfg.num_heads,
                                      num_kv_heads=cfg.num_kv_heads, head_size=cfg.head_size, qkv_bias=bias, **rope)
     ref, pool_ref = _oracle(dataclasses.replace(w_cpu, qkv=qkv_pre), ex)
-    w = pkg.workloads.to_device(w_cpu, "cuda:0")
+    w = workloads.to_device(w_cpu, "cuda:0")
     plugin = P.GPTAttentionPlugin(num_heads=cfg.num_heads, num_kv_heads=cfg.num_kv_heads, head_size=cfg.head_size,
                                   kv_cache_quant_mode=cfg.quant_mode, tokens_per_block=cfg.tokens_per_block,
                                   multi_block_mode=True, type_id=cfg.dtype, qkv_bias=True, **rope)
@@ -260,7 +262,7 @@ def test_report_feature_path_time(pkg):
     import os
     c = Case((64, 8), 128, torch.bfloat16, "fp8", 64, 16, beam=4, past_lo=2048, past_hi=4096, seed=3)
     w_cpu, ex = _build(pkg, c)
-    w = pkg.workloads.to_device(w_cpu, "cuda:0")
+    w = workloads.to_device(w_cpu, "cuda:0")
     plugin = _plugin(pkg, c)
     try:
         ci, cl = ex["cache_indirection"].cuda(), ex["context_lengths"].cuda()

@@ -5,6 +5,8 @@ cost dominates small batches - the reference runtime pays it every step, generat
 import pytest
 import torch
 
+import workloads
+
 import oracle
 from helpers import MAX_ABS_TOL, MEAN_ABS_TOL
 
@@ -62,7 +64,7 @@ def test_prompt_and_twenty_decode_steps_with_block_manager(pkg):
 
 
 def test_step_replayed_from_a_cuda_graph(pkg):
-    wl = pkg.workloads
+    wl = workloads
     cfg = wl.DecodeConfig("graph", 6, 16, 2, 128, torch.bfloat16, "fp8", 64, 900, 2500, True, 31)
     w = wl.to_device(wl.build_workload(cfg, "cpu"), "cuda:0")
     plugin = wl.make_plugin(cfg, 0)

@@ -3,17 +3,19 @@
 import pytest
 import torch
 
+import workloads
+
 pytestmark = pytest.mark.gpu
 
 
 def _workloads(pkg, n):
-    wl = pkg.workloads
+    wl = workloads
     cfg = wl.DecodeConfig("host", 6, 16, 2, 128, torch.bfloat16, "fp8", 64, 200, 1500, True, 77)
     return cfg, [wl.build_workload(cfg, "cpu", seed_offset=i) for i in range(n)]
 
 
 def _device_result(pkg, cfg, w_cpu):
-    wl = pkg.workloads
+    wl = workloads
     w = wl.to_device(w_cpu, "cuda:0")
     plugin = wl.make_plugin(cfg, 0)
     out = wl.run_step(plugin, w)
@@ -24,7 +26,7 @@ def _device_result(pkg, cfg, w_cpu):
 
 @pytest.mark.parametrize("pipelined", [False, True])
 def test_host_path_matches_the_device_path(pkg, pipelined):
-    wl = pkg.workloads
+    wl = workloads
     cfg, cpu = _workloads(pkg, 5)
     want = [_device_result(pkg, cfg, w) for w in cpu]
     dev = [wl.to_device(w, "cuda:0") for w in cpu]   # pools and scales live on the device

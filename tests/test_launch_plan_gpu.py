@@ -6,6 +6,8 @@ import math
 import pytest
 import torch
 
+import workloads
+
 pytestmark = pytest.mark.gpu
 
 SMS, WAVES, MIN_CHUNK, FIXED, SLACK_FROM = 148, 8, 256, 400.0, 2.0
@@ -34,7 +36,7 @@ def _expected_bound(lengths, rows_per_seq, resident):
 @pytest.mark.parametrize("seed", range(6))
 @pytest.mark.parametrize("shape", ["mha_int8", "wide_fp8", "gqa_small_shard"])
 def test_partition_bound_matches_the_cost_model(pkg, monkeypatch, seed, shape):
-    wl = pkg.workloads
+    wl = workloads
     monkeypatch.setenv("DX_ATTN_STREAMK", "0")  # classic launches only: this is about the partition search
     if shape == "mha_int8":  # one CTA row per q head, 3 CTAs per SM
         cfg = wl.DecodeConfig("p", 1, 32, 32, 128, torch.bfloat16, "int8", 64, 1, 1, True, 1)

@@ -21,7 +21,7 @@ def _worker(rank, world, port, q):
         import __graft_entry__ as g
         import bench
         from helpers import oracle_step
-        wl = g.load_package().workloads
+        import workloads as wl
         cfg = wl.DecodeConfig("tp", 3, 16, 4, 64, torch.bfloat16, "fp8", 16, 20, 90, True, 8)
         w = wl.build_workload(cfg, "cpu")          # same seed on every rank -> same lengths and tables
         ws = wl.shard_workload(w, world, rank)     # this rank's heads only

@@ -8,6 +8,8 @@ from pathlib import Path
 import pytest
 import torch
 
+import workloads
+
 import oracle
 from helpers import CACHE_MODE, MAX_ABS_TOL, MEAN_ABS_TOL
 
@@ -18,7 +20,7 @@ GOLDEN = json.loads((Path(__file__).parent / "golden" / "medusa_mask_golden.json
 def _workload(pkg, cfg, q_len, pasts=None):
     """A single-token workload whose page tables have room for q_len new tokens, re-labelled: past lengths, lengths
     that include the new tokens, QKV of batch * q_len rows."""
-    wl = pkg.workloads
+    wl = workloads
     if pasts is None:
         pasts = wl.draw_lengths(cfg)
     pasts = torch.as_tensor(pasts, dtype=torch.int32)
@@ -47,7 +49,7 @@ def _oracle(w, packed, rope=None, offsets=None):
 
 def _run(pkg, w_cpu, packed, rope=None, offsets=None, **kw):
     cfg = w_cpu.cfg
-    w = pkg.workloads.to_device(w_cpu, "cuda:0")
+    w = workloads.to_device(w_cpu, "cuda:0")
     plugin = pkg.GPTAttentionPlugin(num_heads=cfg.num_heads, num_kv_heads=cfg.num_kv_heads, head_size=cfg.head_size,
                                     multi_block_mode=cfg.multi_block_mode, kv_cache_quant_mode=cfg.quant_mode,
                                     tokens_per_block=cfg.tokens_per_block, type_id=cfg.dtype, device=0, **(rope or {}))
@@ -79,10 +81,10 @@ def _tree(name, batch):
     (torch.bfloat16, "none", (8, 8), 128, 64),
 ])
 def test_draft_trees_against_oracle(pkg, tree, dtype, cache, heads, dh, tpb):
-    cfg = pkg.workloads.DecodeConfig("mt", 5, heads[0], heads[1], dh, dtype, cache, tpb, 0, 700, True, 301)
+    cfg = workloads.DecodeConfig("mt", 5, heads[0], heads[1], dh, dtype, cache, tpb, 0, 700, True, 301)
     packed, _ = _tree(tree, cfg.batch)
     q_len = packed.shape[1]
-    pasts = pkg.workloads.draw_lengths(cfg)
+    pasts = workloads.draw_lengths(cfg)
     pasts[0] = 0  # a sequence with nothing but the new tokens
     pasts[1] = tpb - 1  # the new tokens straddle a block boundary
     w = _workload(pkg, cfg, q_len, pasts)
@@ -96,7 +98,7 @@ def test_draft_trees_against_oracle(pkg, tree, dtype, cache, heads, dh, tpb):
 
 
 def test_masks_may_differ_between_sequences(pkg):
-    cfg = pkg.workloads.DecodeConfig("mtb", 4, 8, 2, 128, torch.bfloat16, "fp8", 64, 10, 300, True, 302)
+    cfg = workloads.DecodeConfig("mtb", 4, 8, 2, 128, torch.bfloat16, "fp8", 64, 10, 300, True, 302)
     q_len = 9
     g = torch.Generator().manual_seed(5)
     dense = torch.tril(torch.rand(cfg.batch, q_len, q_len, generator=g) > 0.5) | torch.eye(q_len, dtype=torch.bool)
@@ -118,7 +120,7 @@ def test_masks_may_differ_between_sequences(pkg):
 ])
 @pytest.mark.parametrize("with_offsets", [True, False])
 def test_rotary_positions_follow_the_tree_depth(pkg, rope, with_offsets):
-    cfg = pkg.workloads.DecodeConfig("mtr", 3, 8, 2, 128, torch.bfloat16, "fp8", 64, 10, 500, True, 303)
+    cfg = workloads.DecodeConfig("mtr", 3, 8, 2, 128, torch.bfloat16, "fp8", 64, 10, 500, True, 303)
     packed, offsets = _tree("small", cfg.batch)
     if not with_offsets:
         offsets = None  # the default: token t at offset t (a chain of draft tokens)
@@ -135,7 +137,7 @@ def test_rotary_positions_follow_the_tree_depth(pkg, rope, with_offsets):
 
 def test_what_the_mode_does_not_cover_is_refused(pkg):
     P = pkg.plugin
-    cfg = pkg.workloads.DecodeConfig("mtu", 2, 8, 2, 128, torch.bfloat16, "fp8", 64, 100, 200, True, 304)
+    cfg = workloads.DecodeConfig("mtu", 2, 8, 2, 128, torch.bfloat16, "fp8", 64, 100, 200, True, 304)
     packed, _ = _tree("chain3", cfg.batch)
     w = _workload(pkg, cfg, packed.shape[1], [150, 199])
     for kw in (dict(sink_token_length=64), dict(cyclic_attention_window_size=64)):

@@ -8,6 +8,8 @@ import numpy as np
 import pytest
 import torch
 
+import workloads
+
 import oracle
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
@@ -132,7 +134,7 @@ def _loop_reference(w, cache_mode):
 @pytest.mark.parametrize("cache,dtype", [("none", torch.float16), ("int8", torch.bfloat16), ("fp8", torch.float16),
                                          ("fp8", torch.bfloat16)])
 def test_oracle_against_loop_restatement(pkg, cache, dtype):
-    wl = pkg.workloads
+    wl = workloads
     cfg = wl.DecodeConfig("tiny", 3, 4, 2, 64, dtype, cache, 16, 1, 40, False, 31)
     w = wl.build_workload(cfg, "cpu")
     mode = {"none": oracle.CACHE_T, "int8": oracle.CACHE_INT8, "fp8": oracle.CACHE_FP8}[cache]
@@ -153,12 +155,12 @@ def test_workload_fill_uses_the_same_bytes_as_the_oracle(pkg, cache, dtype):
     x = (torch.randn(4096, generator=g) * 3).to(dtype)
     mode = {"none": oracle.CACHE_T, "int8": oracle.CACHE_INT8, "fp8": oracle.CACHE_FP8}[cache]
     s = 448.0 / 7.3 if cache == "fp8" else 127.0 / 7.3
-    assert torch.equal(pkg.workloads.quantize_for_cache(x, s, cache), oracle.quantize_kv(x, s, mode))
+    assert torch.equal(workloads.quantize_for_cache(x, s, cache), oracle.quantize_kv(x, s, mode))
 
 
 def test_tp_shards_concatenate_to_the_full_result(pkg):
     """Sharding by kv head needs no exchange: per-rank oracle outputs concatenate to the full output."""
-    wl = pkg.workloads
+    wl = workloads
     cfg = wl.DecodeConfig("tp", 3, 16, 4, 64, torch.bfloat16, "fp8", 16, 20, 90, True, 8)
     w = wl.build_workload(cfg, "cpu")
     from helpers import oracle_step

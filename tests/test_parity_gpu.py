@@ -4,13 +4,15 @@ import dataclasses
 import pytest
 import torch
 
+import workloads
+
 from helpers import gpu_step_and_compare
 
 pytestmark = pytest.mark.gpu
 
 
 def _cfg(pkg, name, **kw):
-    return dataclasses.replace(pkg.workloads.CONFIGS[name], **kw)
+    return dataclasses.replace(workloads.CONFIGS[name], **kw)
 
 
 @pytest.mark.parametrize("name,batch,len_div", [
@@ -21,7 +23,7 @@ def _cfg(pkg, name, **kw):
     ("c5", 2, 16),    # Mixtral long GQA INT8, split-K
 ])
 def test_config_shapes(pkg, name, batch, len_div):
-    cfg = pkg.workloads.scaled_config(pkg.workloads.CONFIGS[name], batch=batch, len_div=len_div)
+    cfg = workloads.scaled_config(workloads.CONFIGS[name], batch=batch, len_div=len_div)
     r = gpu_step_and_compare(pkg, cfg)
     print(name, r)
 
@@ -29,7 +31,7 @@ def test_config_shapes(pkg, name, batch, len_div):
 @pytest.mark.parametrize("tp", [2, 4, 8])
 @pytest.mark.parametrize("name", ["c4", "c5"])
 def test_tp_shards(pkg, name, tp):
-    wl = pkg.workloads
+    wl = workloads
     cfg = wl.scaled_config(wl.shard_config(wl.CONFIGS[name], tp), batch=3, len_div=16)
     gpu_step_and_compare(pkg, cfg)
 
@@ -37,7 +39,7 @@ def test_tp_shards(pkg, name, tp):
 @pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c5"])
 def test_block_boundary_lengths(pkg, name):
     """Past lengths around block and tile boundaries, including an empty past (first generated token)."""
-    base = pkg.workloads.CONFIGS[name]
+    base = workloads.CONFIGS[name]
     tpb = base.tokens_per_block
     lens = [0, 1, tpb - 1, tpb, tpb + 1, 2 * tpb - 1, 31, 32, 33, 127, 128, 129, 3 * tpb, 517]
     cfg = dataclasses.replace(base, batch=len(lens))
@@ -47,7 +49,7 @@ def test_block_boundary_lengths(pkg, name):
 @pytest.mark.parametrize("name", ["c2", "c4", "c5"])
 @pytest.mark.parametrize("multi_block", [False, True])
 def test_multi_block_on_off(pkg, name, multi_block):
-    cfg = pkg.workloads.scaled_config(pkg.workloads.CONFIGS[name], batch=2, len_div=4)
+    cfg = workloads.scaled_config(workloads.CONFIGS[name], batch=2, len_div=4)
     r = gpu_step_and_compare(pkg, cfg, multi_block_mode=multi_block)
     if not multi_block:
         assert r["plan"]["num_partitions"] == 1
@@ -58,14 +60,14 @@ def test_multi_block_on_off(pkg, name, multi_block):
 @pytest.mark.parametrize("heads", [(4, 4), (8, 2), (8, 1), (32, 2), (24, 2)])
 @pytest.mark.parametrize("dh", [64, 128])
 def test_dtype_cache_head_matrix(pkg, dtype, cache, heads, dh):
-    wl = pkg.workloads
+    wl = workloads
     cfg = wl.DecodeConfig("matrix", 3, heads[0], heads[1], dh, dtype, cache, 32, 40, 300, True, 4242)
     gpu_step_and_compare(pkg, cfg, check_twice=False)
 
 
 @pytest.mark.parametrize("tpb", [16, 32, 64, 128, 256])
 def test_tokens_per_block(pkg, tpb):
-    wl = pkg.workloads
+    wl = workloads
     cfg = wl.DecodeConfig("tpb", 3, 8, 2, 128, torch.bfloat16, "fp8", tpb, 100, 700, True, 77)
     gpu_step_and_compare(pkg, cfg, check_twice=False)
 
@@ -75,7 +77,7 @@ def test_eight_generation_steps(pkg):
     every step appends one token per sequence and must keep matching the oracle."""
     import oracle
     from helpers import CACHE_MODE, MAX_ABS_TOL, MEAN_ABS_TOL
-    wl = pkg.workloads
+    wl = workloads
     cfg = wl.DecodeConfig("steps", 4, 16, 2, 128, torch.bfloat16, "fp8", 64, 56, 70, True, 99)
     start = wl.draw_lengths(cfg)
     # blocks are allocated for 8 more tokens than the starting past lengths

@@ -10,6 +10,8 @@ from pathlib import Path
 import pytest
 import torch
 
+import workloads
+
 from helpers import MAX_ABS_TOL, MEAN_ABS_TOL, REPORT_DIR, oracle_step
 
 pytestmark = pytest.mark.gpu
@@ -57,7 +59,7 @@ def _run_reference(w, tiles=0, sync=True, out=None, ws=None, qkv_bias=None, rope
     (torch.float16, 64, "int8", (4, 2)),
 ])
 def test_oracle_matches_reference_mmha_kernel(pkg, dtype, dh, cache, heads):
-    wl = pkg.workloads
+    wl = workloads
     cfg = wl.DecodeConfig("refx", 4, heads[0], heads[1], dh, dtype, cache, 64, 30, 600, False, 2024)
     w_cpu = wl.build_workload(cfg, "cpu")
     w = wl.to_device(w_cpu, "cuda:0")
@@ -80,7 +82,7 @@ def test_report_reference_kernel_time(pkg, name, tp, tiles):
     inputs and records both in ref_kernel_times.jsonl of the report directory.  Asserts only agreement of results."""
     import json
     import os
-    wl = pkg.workloads
+    wl = workloads
     cfg = wl.shard_config(wl.CONFIGS[name], tp)
     if name == "c2":
         cfg = wl.scaled_config(cfg, batch=16)

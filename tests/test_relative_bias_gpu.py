@@ -7,6 +7,8 @@ from pathlib import Path
 import pytest
 import torch
 
+import workloads
+
 import oracle
 from helpers import CACHE_MODE, MAX_ABS_TOL, MEAN_ABS_TOL
 
@@ -33,7 +35,7 @@ def _oracle(w, bias, max_distance):
 
 def _product(pkg, w_cpu, bias, max_distance, position_embedding_type=5):
     cfg = w_cpu.cfg
-    w = pkg.workloads.to_device(w_cpu, "cuda:0")
+    w = workloads.to_device(w_cpu, "cuda:0")
     plugin = pkg.GPTAttentionPlugin(num_heads=cfg.num_heads, num_kv_heads=cfg.num_kv_heads, head_size=cfg.head_size,
                                     multi_block_mode=True, kv_cache_quant_mode=cfg.quant_mode,
                                     tokens_per_block=cfg.tokens_per_block, type_id=cfg.dtype, device=0,
@@ -60,8 +62,8 @@ SHAPES = [
 @pytest.mark.parametrize("implicit,max_distance", [(False, 0), (True, 100), (True, 50)])
 @pytest.mark.parametrize("heads,dh,dtype,cache,tpb", SHAPES)
 def test_relative_bias_against_oracle(pkg, heads, dh, dtype, cache, tpb, implicit, max_distance):
-    cfg = pkg.workloads.DecodeConfig("rel", 4, heads[0], heads[1], dh, dtype, cache, tpb, 0, 300, True, 41)
-    w = pkg.workloads.build_workload(cfg, "cpu")
+    cfg = workloads.DecodeConfig("rel", 4, heads[0], heads[1], dh, dtype, cache, tpb, 0, 300, True, 41)
+    w = workloads.build_workload(cfg, "cpu")
     stride = 32 if implicit else int(w.host_past_key_value_lengths.max()) + 3
     bias = _bias(cfg, stride, implicit, 7)
     ref, pool_ref = _oracle(w, bias, max_distance)
@@ -107,11 +109,11 @@ def test_oracle_and_product_match_the_reference_kernel(pkg, heads, dh, dtype, im
     lib = ctypes.CDLL(str(LIB))
     if not hasattr(lib, "ref_mmha_relbias_bf16_128"):
         pytest.skip("oracle/_ref/libref_mmha.so predates the relative-bias entry point")
-    cfg = pkg.workloads.DecodeConfig("relref", 3, heads[0], heads[1], dh, dtype, "int8", 64, 10, 300, False, 42)
-    w_cpu = pkg.workloads.build_workload(cfg, "cpu")
+    cfg = workloads.DecodeConfig("relref", 3, heads[0], heads[1], dh, dtype, "int8", 64, 10, 300, False, 42)
+    w_cpu = workloads.build_workload(cfg, "cpu")
     stride = 32 if implicit else int(w_cpu.host_past_key_value_lengths.max()) + 1
     bias = _bias(cfg, stride, implicit, 8)
-    w = pkg.workloads.to_device(w_cpu, "cuda:0")
+    w = workloads.to_device(w_cpu, "cuda:0")
     ref_kernel = _reference_kernel(w, bias, max_distance)
     out, pool = _product(pkg, w_cpu, bias, max_distance)
     assert torch.equal(w.pool.cpu(), pool)  # the same bytes stored at the same place
@@ -127,8 +129,8 @@ def test_oracle_and_product_match_the_reference_kernel(pkg, heads, dh, dtype, im
 
 def test_argument_errors(pkg):
     P = pkg.plugin
-    cfg = pkg.workloads.DecodeConfig("relerr", 2, 4, 4, 64, torch.float16, "none", 64, 50, 90, True, 43)
-    w = pkg.workloads.build_workload(cfg, "cpu")
+    cfg = workloads.DecodeConfig("relerr", 2, 4, 4, 64, torch.float16, "none", 64, 50, 90, True, 43)
+    w = workloads.build_workload(cfg, "cpu")
     bias = _bias(cfg, 128, False, 1)
     with pytest.raises(P.DecodeAttnError) as e:  # a table needs the relative position embedding type
         _product(pkg, w, bias, 0, position_embedding_type=0)

@@ -8,6 +8,8 @@ from pathlib import Path
 import pytest
 import torch
 
+import workloads
+
 import oracle
 from helpers import CACHE_MODE, MAX_ABS_TOL, MEAN_ABS_TOL
 
@@ -57,7 +59,7 @@ def _byte_agreement(a, b, changed_mask):
     (torch.float16, "fp8", (32, 2), False),
 ])
 def test_rope_bias_against_oracle(pkg, rope_name, dtype, cache, heads, with_bias):
-    wl = pkg.workloads
+    wl = workloads
     rope = ROPES[rope_name]
     dh = 128
     if rope["rotary_embedding_dim"] > dh:
@@ -94,7 +96,7 @@ def test_rope_bias_against_reference_kernel(pkg, rope_name, cache):
     """Same device math library on both sides: the K/V bytes the reference kernel appends after bias + RoPE
     must equal ours exactly."""
     from test_reference_kernel_gpu import _run_reference
-    wl = pkg.workloads
+    wl = workloads
     rope = ROPES[rope_name]
     cfg = wl.DecodeConfig("roperef", 4, 8, 2, 128, torch.bfloat16, cache, 64, 30, 700, False, 78)
     w_cpu = wl.build_workload(cfg, "cpu")

@@ -6,6 +6,8 @@ import dataclasses
 import pytest
 import torch
 
+import workloads
+
 import oracle
 from helpers import CACHE_MODE, MAX_ABS_TOL, MEAN_ABS_TOL, gpu_step_and_compare
 
@@ -22,7 +24,7 @@ def _force(monkeypatch):
 @pytest.mark.parametrize("cache", ["fp8", "int8", "none"])
 @pytest.mark.parametrize("heads,dh", [((8, 1), 128), ((64, 8), 128), ((16, 1), 128), ((24, 1), 64), ((8, 2), 64)])
 def test_ragged_batches(pkg, cache, heads, dh):
-    cfg = pkg.workloads.DecodeConfig("sk", 7, heads[0], heads[1], dh, torch.bfloat16, cache, 64, 20, 3000, True, 77)
+    cfg = workloads.DecodeConfig("sk", 7, heads[0], heads[1], dh, torch.bfloat16, cache, 64, 20, 3000, True, 77)
     r = gpu_step_and_compare(pkg, cfg)
     # (24 heads on one kv head with an FP8 cache run on the wide-group kernel, which has no stream-K form)
     if cache == "none":
@@ -32,13 +34,13 @@ def test_ragged_batches(pkg, cache, heads, dh):
 
 def test_many_short_rows_and_boundary_lengths(pkg):
     lens = [0, 1, 31, 32, 33, 63, 64, 65, 95, 96, 127, 128, 129, 255, 256, 257, 517, 1023, 1024, 1025, 2047, 2048]
-    cfg = dataclasses.replace(pkg.workloads.CONFIGS["c4"], batch=len(lens))
+    cfg = dataclasses.replace(workloads.CONFIGS["c4"], batch=len(lens))
     r = gpu_step_and_compare(pkg, cfg, lengths=torch.tensor(lens, dtype=torch.int32))
     assert r["plan"].get("stream_k_ctas", 0) > 0
 
 
 def test_one_long_row_cut_into_many_pieces(pkg):
-    cfg = pkg.workloads.DecodeConfig("sk1", 1, 8, 1, 128, torch.bfloat16, "fp8", 128, 30000, 30000, True, 5)
+    cfg = workloads.DecodeConfig("sk1", 1, 8, 1, 128, torch.bfloat16, "fp8", 128, 30000, 30000, True, 5)
     r = gpu_step_and_compare(pkg, cfg)
     assert r["plan"].get("stream_k_ctas", 0) > 100
 
@@ -46,7 +48,7 @@ def test_one_long_row_cut_into_many_pieces(pkg):
 def test_host_lengths_may_be_upper_bounds(pkg):
     """A captured graph replays with the host lengths it was planned with while the device lengths are the real
     (shorter) ones: pieces scheduled beyond the real length are empty, the result is that of the real length."""
-    wl = pkg.workloads
+    wl = workloads
     cfg = wl.DecodeConfig("skub", 6, 32, 4, 128, torch.bfloat16, "fp8", 64, 100, 1500, True, 9)
     w_cpu = wl.build_workload(cfg, "cpu")
     w = wl.to_device(w_cpu, "cuda:0")
@@ -74,7 +76,7 @@ def test_host_lengths_may_be_upper_bounds(pkg):
 
 
 def test_switch_and_threshold_keep_the_classic_plan(pkg, monkeypatch):
-    cfg = pkg.workloads.DecodeConfig("skoff", 4, 8, 1, 128, torch.bfloat16, "fp8", 64, 200, 900, True, 3)
+    cfg = workloads.DecodeConfig("skoff", 4, 8, 1, 128, torch.bfloat16, "fp8", 64, 200, 900, True, 3)
     monkeypatch.setenv("DX_ATTN_STREAMK", "0")
     r = gpu_step_and_compare(pkg, cfg, check_twice=False)
     assert "stream_k_ctas" not in r["plan"]
@@ -90,7 +92,7 @@ def test_switch_and_threshold_keep_the_classic_plan(pkg, monkeypatch):
 def test_token_major_kernel_ragged_batches(pkg, monkeypatch, heads, tpb):
     """The tcgen05 token-major kernel under the same schedule (unit: its 128-token tile)."""
     monkeypatch.setenv("DX_ATTN_TOK", "1")
-    cfg = pkg.workloads.DecodeConfig("sktok", 7, heads[0], heads[1], 128, torch.bfloat16, "fp8", tpb, 20, 3000, True, 78)
+    cfg = workloads.DecodeConfig("sktok", 7, heads[0], heads[1], 128, torch.bfloat16, "fp8", tpb, 20, 3000, True, 78)
     r = gpu_step_and_compare(pkg, cfg)
     assert r["plan"]["kernel"] == "token_major_tcgen05" and r["plan"].get("stream_k_ctas", 0) > 0, r["plan"]
 
@@ -98,10 +100,10 @@ def test_token_major_kernel_ragged_batches(pkg, monkeypatch, heads, tpb):
 def test_token_major_kernel_boundary_lengths_and_long_row(pkg, monkeypatch):
     monkeypatch.setenv("DX_ATTN_TOK", "1")
     lens = [0, 1, 31, 32, 33, 63, 64, 65, 95, 96, 127, 128, 129, 255, 256, 257, 517, 1023, 1024, 1025, 2047, 2048]
-    cfg = dataclasses.replace(pkg.workloads.CONFIGS["c4"], batch=len(lens))
+    cfg = dataclasses.replace(workloads.CONFIGS["c4"], batch=len(lens))
     r = gpu_step_and_compare(pkg, cfg, lengths=torch.tensor(lens, dtype=torch.int32))
     assert r["plan"].get("stream_k_ctas", 0) > 0
-    cfg = pkg.workloads.DecodeConfig("sktok1", 1, 8, 1, 128, torch.bfloat16, "fp8", 128, 30000, 30000, True, 5)
+    cfg = workloads.DecodeConfig("sktok1", 1, 8, 1, 128, torch.bfloat16, "fp8", 128, 30000, 30000, True, 5)
     r = gpu_step_and_compare(pkg, cfg)
     assert r["plan"].get("stream_k_ctas", 0) > 100
 
@@ -111,13 +113,13 @@ def test_six_warp_form_ragged_batches(pkg, monkeypatch, heads, tpb):
     """The form with two six-warp CTAs per SM (FP8, Dh 128, up to 8 heads per kv head), which launches with long
     ranges use: forced here on small ragged batches, boundary lengths and one long row."""
     monkeypatch.setenv("DX_ATTN_SK_SIX_MIN_TOKENS", "1")
-    cfg = pkg.workloads.DecodeConfig("sk6", 7, heads[0], heads[1], 128, torch.bfloat16, "fp8", tpb, 20, 3000, True, 79)
+    cfg = workloads.DecodeConfig("sk6", 7, heads[0], heads[1], 128, torch.bfloat16, "fp8", tpb, 20, 3000, True, 79)
     r = gpu_step_and_compare(pkg, cfg)
     assert r["plan"].get("stream_k_ctas", 0) > 0 and r["plan"]["stream_k_ctas"] <= 2 * 148, r["plan"]
     lens = [0, 1, 31, 32, 33, 63, 64, 65, 95, 96, 127, 128, 129, 255, 256, 257, 517, 1023, 1024, 1025, 2047, 2048]
-    cfg = dataclasses.replace(pkg.workloads.CONFIGS["c4"], batch=len(lens), tokens_per_block=tpb if tpb >= 32 else 64)
+    cfg = dataclasses.replace(workloads.CONFIGS["c4"], batch=len(lens), tokens_per_block=tpb if tpb >= 32 else 64)
     r = gpu_step_and_compare(pkg, cfg, lengths=torch.tensor(lens, dtype=torch.int32))
     assert 0 < r["plan"].get("stream_k_ctas", 0) <= 2 * 148
-    cfg = pkg.workloads.DecodeConfig("sk6l", 1, heads[0] // heads[1], 1, 128, torch.float16, "fp8", 128, 30000, 30000, True, 6)
+    cfg = workloads.DecodeConfig("sk6l", 1, heads[0] // heads[1], 1, 128, torch.float16, "fp8", 128, 30000, 30000, True, 6)
     r = gpu_step_and_compare(pkg, cfg)
     assert 100 < r["plan"].get("stream_k_ctas", 0) <= 2 * 148

@@ -5,6 +5,8 @@ import dataclasses
 import pytest
 import torch
 
+import workloads
+
 from helpers import gpu_step_and_compare
 
 pytestmark = pytest.mark.gpu
@@ -30,7 +32,7 @@ def _enable(monkeypatch):
 ])
 def test_token_major_cases(pkg, case):
     name, batch, heads, kv_heads, dtype, tpb, lo, hi, mb = case
-    cfg = pkg.workloads.DecodeConfig(name, batch, heads, kv_heads, 128, dtype, "fp8", tpb, lo, hi, mb, 7000 + heads)
+    cfg = workloads.DecodeConfig(name, batch, heads, kv_heads, 128, dtype, "fp8", tpb, lo, hi, mb, 7000 + heads)
     r = gpu_step_and_compare(pkg, cfg)
     assert r["plan"]["kernel"] == TOK
     print(name, r)
@@ -39,13 +41,13 @@ def test_token_major_cases(pkg, case):
 def test_token_major_boundary_lengths(pkg):
     """Past lengths around block (64), tile and partition (128) boundaries, and an empty past."""
     lens = [0, 1, 63, 64, 65, 127, 31, 32, 33, 126, 128, 129, 192, 517, 255, 256, 257, 1024]
-    cfg = dataclasses.replace(pkg.workloads.CONFIGS["c4"], batch=len(lens))
+    cfg = dataclasses.replace(workloads.CONFIGS["c4"], batch=len(lens))
     r = gpu_step_and_compare(pkg, cfg, lengths=torch.tensor(lens, dtype=torch.int32))
     assert r["plan"]["kernel"] == TOK
 
 
 def test_token_major_is_opt_in(pkg, monkeypatch):
     monkeypatch.delenv("DX_ATTN_TOK")
-    cfg = pkg.workloads.scaled_config(pkg.workloads.CONFIGS["c4"], batch=2, len_div=8)
+    cfg = workloads.scaled_config(workloads.CONFIGS["c4"], batch=2, len_div=8)
     r = gpu_step_and_compare(pkg, cfg, check_twice=False)
     assert r["plan"]["kernel"] == "gqa_tensor_core"

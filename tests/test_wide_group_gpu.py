@@ -5,6 +5,8 @@ import dataclasses
 import pytest
 import torch
 
+import workloads
+
 from helpers import gpu_step_and_compare
 
 pytestmark = pytest.mark.gpu
@@ -13,7 +15,7 @@ WIDE = "wide_group_tcgen05"
 
 
 def _cfg(pkg, name, batch, heads, kv_heads, dh, dtype, tpb, lo, hi, multi_block, seed):
-    return pkg.workloads.DecodeConfig(name, batch, heads, kv_heads, dh, dtype, "fp8", tpb, lo, hi, multi_block, seed)
+    return workloads.DecodeConfig(name, batch, heads, kv_heads, dh, dtype, "fp8", tpb, lo, hi, multi_block, seed)
 
 
 @pytest.mark.parametrize("case", [
@@ -38,7 +40,7 @@ def test_wide_group_cases(pkg, case):
 def test_wide_group_boundary_lengths(pkg):
     """Past lengths around tile (64 tokens), block and partition (128 tokens) boundaries, and an empty past."""
     lens = [0, 1, 62, 63, 64, 65, 126, 127, 128, 129, 191, 192, 255, 256, 257, 517, 1023, 1024]
-    cfg = dataclasses.replace(pkg.workloads.CONFIGS["c3"], batch=len(lens))
+    cfg = dataclasses.replace(workloads.CONFIGS["c3"], batch=len(lens))
     r = gpu_step_and_compare(pkg, cfg, lengths=torch.tensor(lens, dtype=torch.int32))
     assert r["plan"]["kernel"] == WIDE
 

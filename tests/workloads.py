@@ -14,9 +14,18 @@ import math
 from dataclasses import dataclass
 from typing import Dict, List, Optional
 
+import sys
+from pathlib import Path
+
 import torch
 
-from .plugin import QuantMode
+_ROOT = Path(__file__).resolve().parent.parent
+if str(_ROOT) not in sys.path:
+    sys.path.insert(0, str(_ROOT))
+import __graft_entry__ as _entry  # noqa: E402
+
+_pkg = _entry.load_package()
+QuantMode = _pkg.QuantMode
 
 
 @dataclass(frozen=True)
@@ -229,8 +238,7 @@ def shard_workload(w: DecodeWorkload, tp_size: int, tp_rank: int) -> DecodeWorkl
 
 def make_plugin(cfg: DecodeConfig, device_index: int = 0, *, tp_size: int = 1, tp_rank: int = 0,
                 multi_block_mode: Optional[bool] = None):
-    from .plugin import GPTAttentionPlugin
-    return GPTAttentionPlugin(num_heads=cfg.num_heads, num_kv_heads=cfg.num_kv_heads, head_size=cfg.head_size,
+    return _pkg.GPTAttentionPlugin(num_heads=cfg.num_heads, num_kv_heads=cfg.num_kv_heads, head_size=cfg.head_size,
                               q_scaling=1.0, tp_size=tp_size, tp_rank=tp_rank,
                               multi_block_mode=cfg.multi_block_mode if multi_block_mode is None else multi_block_mode,
                               kv_cache_quant_mode=cfg.quant_mode, tokens_per_block=cfg.tokens_per_block,
