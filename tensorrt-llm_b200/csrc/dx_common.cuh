@@ -106,8 +106,37 @@ struct SkSchedule
     uint32_t total_units;
     uint32_t rows_per_seq;
     uint32_t nseq;
+    // Two-level form (the persistent tcgen05 kernel): ranges 0 .. n1-1 are the static ones above, one per CTA,
+    // units [r * units_per_cta, (r+1) * units_per_cta); what they leave, units [n1 * units_per_cta, total_units), is
+    // cut into n2 short ranges of u2 units, numbered n1, n1+1, ..., that the CTAs take from a device counter as
+    // they finish.  Single-level schedules have n1 = number of CTAs, n2 = u2 = 0.
+    uint32_t n1, n2, u2;
     uint32_t prefix[DX_SK_MAX_SEQ + 1];
 };
+
+// Range that holds unit u.
+__host__ __device__ __forceinline__ uint32_t sk_range_of_unit(const SkSchedule& sk, uint32_t u)
+{
+    const uint32_t static_units = sk.n1 * sk.units_per_cta;
+    return u < static_units ? u / sk.units_per_cta : sk.n1 + (u - static_units) / sk.u2;
+}
+
+// Units [u0, u1) of range r.
+__host__ __device__ __forceinline__ void sk_range_units(const SkSchedule& sk, uint32_t r, uint32_t& u0, uint32_t& u1)
+{
+    if (r < sk.n1)
+    {
+        u0 = r * sk.units_per_cta;
+        u1 = u0 + sk.units_per_cta;
+    }
+    else
+    {
+        u0 = sk.n1 * sk.units_per_cta + (r - sk.n1) * sk.u2;
+        u1 = u0 + sk.u2;
+    }
+    u0 = u0 < sk.total_units ? u0 : sk.total_units;
+    u1 = u1 < sk.total_units ? u1 : sk.total_units;
+}
 
 struct SkCursor
 {
@@ -175,7 +204,28 @@ __device__ __forceinline__ int sk_pieces_of_row(const SkSchedule& sk, int b, int
 {
     const uint32_t nb = sk.prefix[b + 1] - sk.prefix[b];
     const uint32_t row_start = sk.rows_per_seq * sk.prefix[b] + (uint32_t) y * nb;
-    return (int) ((row_start + nb - 1) / sk.units_per_cta - row_start / sk.units_per_cta) + 1;
+    return (int) (sk_range_of_unit(sk, row_start + nb - 1) - sk_range_of_unit(sk, row_start)) + 1;
+}
+
+// Cursor on unit u0 of the line, range end u1 (u0 < u1 <= total_units).
+__device__ __forceinline__ void sk_seek(const SkSchedule& sk, uint32_t u0, uint32_t u1, SkCursor& c)
+{
+    c.u = u0;
+    c.u1 = u1;
+    uint32_t lo = 0, hi = sk.nseq - 1;
+    while (lo < hi) // largest b whose first unit is <= u
+    {
+        const uint32_t mid = (lo + hi + 1) >> 1;
+        if (sk.rows_per_seq * sk.prefix[mid] <= u0)
+            lo = mid;
+        else
+            hi = mid - 1;
+    }
+    c.b = lo;
+    c.nb = sk.prefix[lo + 1] - sk.prefix[lo];
+    const uint32_t rem = u0 - sk.rows_per_seq * sk.prefix[lo];
+    c.y = rem / c.nb;
+    c.g0 = rem - c.y * c.nb;
 }
 
 // Split-K partitioning of one sequence: `total` tokens are cut into the fewest partitions of at
