@@ -30,7 +30,8 @@ enum KernelKind : int
     KIND_MHA = 0, // CUDA-core kernel, one CTA per q head
     KIND_GQA = 1, // tensor-core kernel, one CTA per kv head (x 16-head slice)
     KIND_TOK = 3, // tcgen05 kernel, token-major, one CTA per kv head, FP8 cache, Dh 128, up to 16 heads per kv head
-    KIND_WIDE = 2 // tcgen05 kernel, one CTA per kv head (x 128-head slice), FP8 cache, more than 16 heads per kv head
+    KIND_WIDE = 2, // tcgen05 kernel, one CTA per kv head (x 128-head slice), FP8 cache, more than 16 heads per kv head
+    KIND_TOKWS = 4 // persistent warp-specialised tcgen05 kernel, token-major, one CTA per SM, two-level stream-K ranges
 };
 
 struct Plan
@@ -72,6 +73,12 @@ struct dx_attn
     KernelInfo k_gqa_six{}; // stream-K form of k_gqa[0] with two six-warp CTAs per SM (where built)
     bool wide = false;       // wide-group kernel usable for this configuration
     bool tok = false;        // token-major tcgen05 kernel usable for this configuration
+    KernelInfo k_tokws{};    // its persistent warp-specialised form
+    bool tokws = false;
+    int ws_tail_pct = 20;    // share of the tiles (per cent) handed out as short dynamic ranges
+    int ws_tail_div = 8;     // a dynamic range is 1/ws_tail_div of a static one ...
+    int ws_min_u2 = 2;       // ... but at least this many 128-token tiles
+    int ws_min_u1 = 8;       // below this many tiles per static range the schedule stays single-level
     GeneralKernels k_general{}; // beams / cyclic window / sinks / ALiBi
     const void* k_merge_sk = nullptr;
     bool streamk = true;        // grouped-head kernels: equal ranges of token groups per CTA instead of per-row partitions
@@ -308,8 +315,68 @@ bool build_streamk(const dx_attn* h, Plan& plan, const int32_t* host_past, int b
     sk.rows_per_seq = Y;
     sk.nseq = (uint32_t) batch;
     ctas = (int) ((total + U - 1) / U);
+    sk.n1 = (uint32_t) ctas;
+    sk.n2 = 0;
+    sk.u2 = 0;
     plan.nsplit = (int) pmax;
     plan.chunk_tokens = (int) (U * unit);
+    plan.part_o_bytes = align_up(qrows * pmax * c.head_size * sizeof(float), 128);
+    plan.part_ml_bytes = align_up(qrows * pmax * sizeof(float2), 128);
+    return true;
+}
+
+// Two-level schedule of the persistent tcgen05 kernel: one CTA per SM; the first (100 - tail) per cent of the tiles in
+// equal static ranges, the rest in short ranges the CTAs draw from a device counter as they finish.  On success
+// the plan is that of the persistent kernel.  False: the call stays with the other kernels.
+bool build_streamk_ws(const dx_attn* h, Plan& plan, const int32_t* host_past, int batch, SkSchedule& sk, int& ctas)
+{
+    const dx_attn_config& c = h->cfg;
+    if (!h->tokws || !c.multi_block_mode || !host_past || batch > DX_SK_MAX_SEQ || !h->k_merge_sk)
+        return false;
+    const uint32_t Y = (uint32_t) c.num_kv_heads;
+    uint64_t acc = 0;
+    uint32_t nmax = 1;
+    sk.prefix[0] = 0;
+    for (int i = 0; i < batch; ++i)
+    {
+        const uint32_t n = ((uint32_t) host_past[i] + 128) >> 7; // ceil((past + 1) / 128)
+        nmax = std::max(nmax, n);
+        acc += n;
+        sk.prefix[i + 1] = (uint32_t) acc;
+    }
+    const uint64_t total = acc * Y;
+    if (total >= (1ull << 31))
+        return false;
+    const uint64_t n1 = std::min<uint64_t>((uint64_t) h->sm_count, total);
+    uint64_t u1 = total * (uint64_t) (100 - h->ws_tail_pct) / 100 / n1, u2 = 0, n2 = 0;
+    if (h->ws_tail_pct <= 0 || u1 < (uint64_t) h->ws_min_u1)
+    {
+        u1 = (total + n1 - 1) / n1; // single level
+    }
+    else
+    {
+        u2 = std::max<uint64_t>((uint64_t) h->ws_min_u2, u1 / (uint64_t) std::max(1, h->ws_tail_div));
+        n2 = (total - n1 * u1 + u2 - 1) / u2;
+    }
+    const uint64_t umin = n2 ? std::min(u1, u2) : u1;
+    const uint64_t pmax = (nmax - 1) / umin + 2; // pieces of the longest row, at most
+    const size_t qrows = (size_t) batch * c.num_heads;
+    sk.units_per_cta = (uint32_t) u1;
+    sk.total_units = (uint32_t) total;
+    sk.rows_per_seq = Y;
+    sk.nseq = (uint32_t) batch;
+    sk.n1 = (uint32_t) n1;
+    sk.n2 = (uint32_t) n2;
+    sk.u2 = (uint32_t) u2;
+    ctas = (int) n1;
+    plan.kind = KIND_TOKWS;
+    plan.hgroups = 1;
+    plan.heads16 = false;
+    plan.six = false;
+    plan.resident = 1;
+    plan.rows = batch * c.num_kv_heads;
+    plan.nsplit = (int) pmax;
+    plan.chunk_tokens = (int) (u1 * 128);
     plan.part_o_bytes = align_up(qrows * pmax * c.head_size * sizeof(float), 128);
     plan.part_ml_bytes = align_up(qrows * pmax * sizeof(float2), 128);
     return true;
@@ -793,6 +860,24 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
             h->tok = h->k_tok.fn != nullptr && set_smem(h, h->k_tok) == DX_OK;
         }
     }
+    if (st == DX_OK && h->cache_kind == CACHE_FP8 && h->group > 1 && h->group <= 16 && c.head_size == 128
+        && c.tokens_per_block >= 32)
+    {
+        const char* w = getenv("DX_ATTN_TOKWS");
+        if (w && atoi(w) != 0)
+        {
+            h->k_tokws = tokws_kernel_info(c.type_id, c.head_size, h->group);
+            h->tokws = h->k_tokws.fn != nullptr && set_smem(h, h->k_tokws) == DX_OK;
+        }
+        if (const char* m = getenv("DX_ATTN_WS_TAIL_PCT"))
+            h->ws_tail_pct = std::max(0, std::min(90, atoi(m)));
+        if (const char* m = getenv("DX_ATTN_WS_TAIL_DIV"))
+            h->ws_tail_div = std::max(1, atoi(m));
+        if (const char* m = getenv("DX_ATTN_WS_MIN_U2"))
+            h->ws_min_u2 = std::max(1, atoi(m));
+        if (const char* m = getenv("DX_ATTN_WS_MIN_U1"))
+            h->ws_min_u1 = std::max(1, atoi(m));
+    }
     if (st == DX_OK)
         st = check_cuda(h, cudaMalloc(reinterpret_cast<void**>(&h->status_dev), 256));
     if (st == DX_OK)
@@ -866,7 +951,9 @@ int dx_attn_plan_lengths(const dx_attn_t* h, const int32_t* host_past_key_value_
     Plan p = plan_shape(h, batch, rows_per_seq);
     SkSchedule sk;
     int ctas = 0;
-    const bool streamk = plan_streamk(h, p, host_past_key_value_lengths, batch, sk, ctas);
+    bool streamk = build_streamk_ws(h, p, host_past_key_value_lengths, batch, sk, ctas);
+    if (!streamk)
+        streamk = plan_streamk(h, p, host_past_key_value_lengths, batch, sk, ctas);
     if (!streamk)
         plan_partitions(h, p, batch, rows_per_seq, max_past, host_past_key_value_lengths);
     if (num_partitions)
@@ -953,8 +1040,18 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     // the host lengths.  Used when the workspace given can hold one partial result per piece of a cut row.
     SkSchedule sk;
     int sk_ctas = 0;
-    bool use_sk = plan_streamk(h, plan, p.host_past_key_value_lengths, p.num_requests, sk, sk_ctas);
-    if (use_sk && !(p.workspace && !((uintptr_t) p.workspace & 127) && p.workspace_bytes >= prep + plan.workspace()))
+    const auto fits = [&](const Plan& pl)
+    { return p.workspace && !((uintptr_t) p.workspace & 127) && p.workspace_bytes >= prep + pl.workspace(); };
+    // first choice where it applies: the persistent tcgen05 kernel on a two-level schedule
+    bool use_sk = plan.kind == KIND_GQA && build_streamk_ws(h, plan, p.host_past_key_value_lengths, p.num_requests, sk, sk_ctas);
+    if (use_sk && !fits(plan))
+    {
+        use_sk = false;
+        plan = plan_shape(h, p.num_requests, rows_per_seq);
+    }
+    if (!use_sk)
+        use_sk = plan_streamk(h, plan, p.host_past_key_value_lengths, p.num_requests, sk, sk_ctas);
+    if (use_sk && !fits(plan))
     {
         use_sk = false;
         plan = plan_shape(h, p.num_requests, rows_per_seq);
@@ -989,6 +1086,7 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     a.nsplit = plan.nsplit;
     a.softmax_scale_log2 = 1.4426950408889634f / (sqrtf((float) c.head_size) * c.q_scaling);
     a.streamk = use_sk ? 1 : 0;
+    a.tickets = (use_sk && plan.kind == KIND_TOKWS && sk.n2 > 0) ? h->status_dev + 16 : nullptr;
 
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
     int st = check_cuda(h, cudaSetDevice(c.device));
@@ -1016,6 +1114,13 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
         void* args[] = {&a, &hgroups, use_sk ? &sk : &h->sk_zero};
         const dim3 grid = use_sk ? dim3(sk_ctas) : dim3(plan.nsplit, c.num_kv_heads, p.num_requests);
         st = check_cuda(h, cudaLaunchKernel(h->k_tok.fn, grid, dim3(128), args, (size_t) h->k_tok.smem, stream));
+    }
+    else if (plan.kind == KIND_TOKWS)
+    {
+        int hgroups = 1;
+        void* args[] = {&a, &hgroups, &sk};
+        st = check_cuda(h, cudaLaunchKernel(h->k_tokws.fn, dim3(sk_ctas), dim3(h->k_tokws.threads), args,
+                               (size_t) h->k_tokws.smem, stream));
     }
     else if (plan.kind == KIND_GQA)
     {

@@ -39,6 +39,7 @@ struct AttnArgs
     int32_t nsplit;       // grid.x; 1 => kernels write the final output themselves.  Stream-K: result slots per row
     float softmax_scale_log2; // log2(e) / (sqrt(Dh) * q_scaling)
     int32_t streamk;          // 1: the CTAs walk equal ranges of the batch's token groups (SkSchedule), see below
+    int32_t* tickets;         // device counter of the dynamic ranges of a two-level schedule (the merge kernel clears it)
 };
 
 // Arguments of the feature-complete path (beam search, cyclic window, sink tokens, ALiBi).

@@ -18,6 +18,7 @@ KernelInfo gqa_kernel_info(int dtype, int cache, int dh, bool heads16);
 KernelInfo gqa_streamk_kernel_info(int dtype, int cache, int dh, bool heads16); // 6-warp CTAs; empty where not built
 KernelInfo wide_kernel_info(int dtype, int dh); // FP8 cache only
 KernelInfo tok_kernel_info(int dtype, int dh, int group); // FP8 cache, Dh 128, group <= 16
+KernelInfo tokws_kernel_info(int dtype, int dh, int group); // the persistent warp-specialised form of it
 struct GeneralKernels
 {
     const void* attn = nullptr;   // general_decode_kernel: grid (H, B), 128 threads, `smem` dynamic bytes

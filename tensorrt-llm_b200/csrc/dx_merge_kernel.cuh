@@ -155,8 +155,10 @@ __global__ void __launch_bounds__(128) lse_merge_sk_kernel(const AttnArgs a, con
     const int b = row / a.num_heads, h = row % a.num_heads;
     const int G = a.num_heads / a.num_kv_heads;
     const int y = (h / G) * hgroups + (h % G) / 16;
-    const int n = sk_pieces_of_row(sk, b, y);
+    const int n = min(sk_pieces_of_row(sk, b, y), a.nsplit);
     griddep_wait();
+    if (a.tickets != nullptr && blockIdx.x == 0 && threadIdx.x == 0)
+        *a.tickets = 0; // the attention grid has finished: its ticket counter starts the next launch at zero
     if (n > 1)
         merge_row<T, DH>(a, row, n, lane);
 }

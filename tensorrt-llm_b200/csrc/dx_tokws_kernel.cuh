@@ -109,9 +109,11 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar)
 // dynamic range a ticket was drawn for.  Readers of a ticket (every role but the one that draws them) release its
 // slot once read.  False: no more work (or the kernel is aborting).
 template <int TT>
-__device__ __forceinline__ bool ws_next_piece(
-    const SkSchedule& sk, const AttnArgs& a, const WsShared& sh, WsWalker& w, WsPiece& p, bool is_aux, int lane)
+__device__ __forceinline__ bool ws_next_piece(const SkSchedule& sk, const AttnArgs& a, const WsShared& sh, WsWalker& w,
+    WsPiece& p, const bool is_aux, const bool warp_wide, const int lane)
 {
+    // warp_wide: all 32 lanes of the warp walk together (their decisions are made uniform); otherwise one thread
+    // walks alone and no warp-level synchronisation may be executed
     for (;;)
     {
         if (w.done)
@@ -151,13 +153,17 @@ __device__ __forceinline__ bool ws_next_piece(
                 return false;
             }
             const int j = w.k - 1, s = j & 3;
-            if (!is_aux && !ws_wait(&sh.tk_full[s], (j >> 2) & 1, sh))
+            bool got = is_aux || ws_wait(&sh.tk_full[s], (j >> 2) & 1, sh);
+            if (warp_wide)
+                got = __all_sync(0xffffffffu, got);
+            if (!got)
             {
                 w.done = true;
                 return false;
             }
             const int t = sh.tickets[s];
-            __syncwarp();
+            if (warp_wide)
+                __syncwarp();
             if (!is_aux && lane == 0)
                 mbar_arrive(&sh.tk_empty[s]);
             if (t < 0 || (uint32_t) t >= sk.n2)
@@ -176,6 +182,12 @@ __device__ __forceinline__ bool ws_next_piece(
         w.range_idx = ridx;
         w.open = true;
     }
+}
+
+// Warp-uniform form of ws_wait: every lane of the warp gets the same answer.
+__device__ __forceinline__ bool ws_wait_warp(uint64_t* bar, uint32_t parity, const WsShared& sh)
+{
+    return __all_sync(0xffffffffu, ws_wait(bar, parity, sh));
 }
 
 // OR over the 128 threads of the softmax warps (named barrier 1).
@@ -197,7 +209,7 @@ __device__ __forceinline__ void softmax_warps_sync()
 
 template <typename T, int GP>
 __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
-    tokws_decode_kernel(const AttnArgs a, int32_t* const ticket_counter, const __grid_constant__ SkSchedule sk)
+    tokws_decode_kernel(const AttnArgs a, const int hgroups_unused, const __grid_constant__ SkSchedule sk)
 {
     using Tr = TokWsTraits<GP>;
     constexpr int DH = Tr::DH, TT = Tr::TT, N = Tr::N, KV_TILE = Tr::KV_TILE, P_TILE = Tr::P_TILE, NST = Tr::NST;
@@ -299,7 +311,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
         const uint32_t rl = lane >> 3, cl = lane & 7;
         const uint32_t d_even = rl * 128 + ((cl ^ rl) << 4), d_odd = rl * 128 + ((cl ^ (4 + rl)) << 4);
         int g = 0; // tiles put through the ring so far
-        while (ws_next_piece<TT>(sk, a, sh, w, pc, false, lane))
+        while (ws_next_piece<TT>(sk, a, sh, w, pc, false, true, lane))
         {
             if (pc.n_tiles == 0)
                 continue;
@@ -340,7 +352,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
                     kp[q] = reinterpret_cast<const char*>(__ldg(krow + (t >> tpb_log2))) + off;
                     vp[q] = reinterpret_cast<const char*>(__ldg(vrow + (t >> tpb_log2))) + off;
                 }
-                ok = ws_wait(&empty[s], ((g / NST) & 1) ^ 1, sh);
+                ok = ws_wait_warp(&empty[s], ((g / NST) & 1) ^ 1, sh);
                 if (!ok)
                     break;
                 const bool whole = t0 + TT <= new_pos; // every row of the tile is in the cache
@@ -435,7 +447,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
                 pend = false;
                 return true;
             };
-            while (ok && ws_next_piece<TT>(sk, a, sh, w, pc, false, 0))
+            while (ok && ws_next_piece<TT>(sk, a, sh, w, pc, false, false, 0))
             {
                 if (pc.n_tiles == 0)
                     continue;
@@ -484,14 +496,14 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
             if (pub_done)
                 return;
             const int s = pub & 3;
-            if (!ws_wait(&tk_empty[s], ((pub >> 2) & 1) ^ 1, sh))
+            if (!ws_wait_warp(&tk_empty[s], ((pub >> 2) & 1) ^ 1, sh))
             {
                 pub_done = true;
                 return;
             }
             int t = 0;
             if (lane == 0)
-                t = atomicAdd(ticket_counter, 1);
+                t = atomicAdd(a.tickets, 1);
             t = __shfl_sync(0xffffffffu, t, 0);
             if (lane == 0)
             {
@@ -508,7 +520,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
         int np = 0, last_k = 0;
         const float deq = __ldg(a.scale_quant_orig);
         const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
-        while (ws_next_piece<TT>(sk, a, sh, w, pc, true, lane))
+        while (ws_next_piece<TT>(sk, a, sh, w, pc, true, true, lane))
         {
             while (last_k < w.k) // a new range was started: keep two tickets ahead
             {
@@ -525,7 +537,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
             for (int hh = 0; hh < GP; ++hh)
                 q_raw[hh] = (hh < G) ? *reinterpret_cast<const uint2*>(qkv_b + (size_t) (pc.hk * G + hh) * DH + lane * 4)
                                      : make_uint2(0u, 0u);
-            if (!ws_wait(&q_empty[qb], ((np >> 1) & 1) ^ 1, sh))
+            if (!ws_wait_warp(&q_empty[qb], ((np >> 1) & 1) ^ 1, sh))
                 break;
             unsigned char* qbuf = smem + Tr::OFF_Q + qb * Q_TILE;
 #pragma unroll
@@ -560,12 +572,18 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
     else
     {
         // =========================== softmax warps (threads 0 .. 127) ===========================
+        // The four warps meet at named barrier 1.  A thread only leaves this role right behind one of those
+        // barriers, on a decision all 128 threads share (no more work, or the abort flag): nobody is ever left
+        // waiting at a barrier for a thread that has gone.  A wait that gave up makes the thread skip its work
+        // (`ok`, made warp-uniform because the tensor-memory loads are warp-wide) until the next barrier.
         const uint32_t lane_sel = (uint32_t) (warp * 32) << 16;
         const float deq = __ldg(a.scale_quant_orig);
-        int g = 0, np = 0;
-        bool ok = true;
-        while (ok && ws_next_piece<TT>(sk, a, sh, w, pc, false, lane))
+        int g = 0, np = 0, pi = 0; // tiles, non-empty pieces, pieces so far
+        for (;;)
         {
+            const bool got = ws_next_piece<TT>(sk, a, sh, w, pc, false, true, lane);
+            if (softmax_warps_or(got ? 0 : 1))
+                break; // out of work (every thread sees the same tickets) or aborting
             const int head0 = pc.hk * G;
             float mref[GP], l[GP];
 #pragma unroll
@@ -579,11 +597,10 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
             for (int c = 0; c < N; ++c)
                 o[c] = 0.f;
             const int ob = np & 1;
+            bool ok = true, leave = false;
             if (pc.n_tiles > 0)
             {
-                ok = ws_wait(&q_full[ob], (np >> 1) & 1, sh);
-                if (!ok)
-                    break;
+                ok = ws_wait_warp(&q_full[ob], (np >> 1) & 1, sh);
                 float sfac[GP];
 #pragma unroll
                 for (int h = 0; h < GP; ++h)
@@ -591,38 +608,48 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
                 for (int i = 0; i < pc.n_tiles; ++i, ++g)
                 {
                     const int sb = g & 1;
-                    ok = ws_wait(&s_full[sb], (g >> 1) & 1, sh);
-                    if (!ok)
-                        break;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    ok = ok && ws_wait_warp(&s_full[sb], (g >> 1) & 1, sh);
                     float s[GP], p[GP];
+                    int exceed = 0;
+                    if (ok)
                     {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         float r[N];
                         tmem_ld_row<N>(tmem_base + sb * 32 + lane_sel, r);
 #pragma unroll
                         for (int h = 0; h < GP; ++h)
                             s[h] = fmaf(r[GP + h], LOW, r[h]) * sfac[h];
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        mbar_arrive(&s_empty[sb]); // S^T(g) is in registers: the buffer may take S^T(g + 2)
+                        const int t0 = pc.chunk_start + i * TT;
+                        if (t0 + tid >= pc.total) // rows beyond the sequence (last tile only)
+                        {
+#pragma unroll
+                            for (int h = 0; h < GP; ++h)
+                                s[h] = -INFINITY;
+                        }
+#pragma unroll
+                        for (int h = 0; h < GP; ++h)
+                        {
+                            const float d = s[h] - mref[h];
+                            exceed |= (d > PMAX);
+                            p[h] = fast_exp2(d);
+                        }
                     }
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    mbar_arrive(&s_empty[sb]); // S^T(g) is in registers: the buffer may take S^T(g + 2)
-                    const int t0 = pc.chunk_start + i * TT;
-                    if (t0 + tid >= pc.total) // rows beyond the sequence (last tile only)
+                    else
                     {
 #pragma unroll
                         for (int h = 0; h < GP; ++h)
-                            s[h] = -INFINITY;
+                            s[h] = 0.f, p[h] = 0.f;
                     }
-                    int exceed = 0;
-#pragma unroll
-                    for (int h = 0; h < GP; ++h)
-                    {
-                        const float d = s[h] - mref[h];
-                        exceed |= (d > PMAX);
-                        p[h] = fast_exp2(d);
-                    }
-                    const int slow = softmax_warps_or(exceed);
+                    const int slow = softmax_warps_or(exceed | (ok ? 0 : 1));
                     if (slow)
                     {
+                        if (softmax_warps_or(*sh.abort)) // (a reduction again: other roles raise the flag at any time)
+                        {
+                            leave = true;
+                            break;
+                        }
                         // Some score left the range the current reference covers (always on the first tile of a
                         // piece): take the tile's maximum, rescale O^T in tensor memory, recompute the tile's P.
                         float mx[GP];
@@ -656,26 +683,26 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
                         if (i > 0)
                         {
                             // O^T holds tiles 0 .. i-1 of the piece once the MMAs of tile i-1 have completed
-                            ok = ws_wait(&p_empty[(g - 1) & 1], ((g - 1) >> 1) & 1, sh);
-                            if (!ok)
-                                break;
-                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                            float oo[N];
-                            tmem_ld_row<N>(tmem_base + 64 + ob * 32 + lane_sel, oo);
-#pragma unroll
-                            for (int h = 0; h < GP; ++h)
+                            ok = ws_wait_warp(&p_empty[(g - 1) & 1], ((g - 1) >> 1) & 1, sh);
+                            if (ok)
                             {
-                                oo[h] *= f[h];
-                                oo[GP + h] *= f[h];
+                                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                                float oo[N];
+                                tmem_ld_row<N>(tmem_base + 64 + ob * 32 + lane_sel, oo);
+#pragma unroll
+                                for (int h = 0; h < GP; ++h)
+                                {
+                                    oo[h] *= f[h];
+                                    oo[GP + h] *= f[h];
+                                }
+                                tmem_st_row<N>(tmem_base + 64 + ob * 32 + lane_sel, oo);
+                                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                             }
-                            tmem_st_row<N>(tmem_base + 64 + ob * 32 + lane_sel, oo);
-                            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                         }
                     }
                     // the P buffer of this parity is free once the O^T MMAs of tile g - 2 have completed
-                    ok = ws_wait(&p_empty[sb], ((g >> 1) & 1) ^ 1, sh);
-                    if (!ok)
-                        break;
+                    ok = ok && ws_wait_warp(&p_empty[sb], ((g >> 1) & 1) ^ 1, sh);
+                    if (ok)
                     {
                         unsigned char* pbuf = smem + Tr::OFF_P + sb * P_TILE;
                         uint32_t hi[GP / 4], lo[GP / 4];
@@ -691,23 +718,25 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
                             *reinterpret_cast<uint4*>(pbuf + tid * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
                             *reinterpret_cast<uint4*>(pbuf + TT * 16 + tid * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                         }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        mbar_arrive(&p_full[sb]);
                     }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    mbar_arrive(&p_full[sb]);
 #pragma unroll
                     for (int h = 0; h < GP; ++h)
                         l[h] += p[h];
                 }
-                if (!ok)
+                if (leave)
                     break;
                 // ---- O^T of the piece ----
-                ok = ws_wait(&o_full[ob], (np >> 1) & 1, sh);
-                if (!ok)
-                    break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                tmem_ld_row<N>(tmem_base + 64 + ob * 32 + lane_sel, o);
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                mbar_arrive(&o_empty[ob]);
+                ok = ok && ws_wait_warp(&o_full[ob], (np >> 1) & 1, sh);
+                if (ok)
+                {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    tmem_ld_row<N>(tmem_base + 64 + ob * 32 + lane_sel, o);
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    mbar_arrive(&o_empty[ob]);
+                }
+                ++np;
             }
             // ---- result of the piece: thread = Dh channel ----
 #pragma unroll
@@ -717,16 +746,16 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
                 for (int x = 16; x >= 1; x >>= 1)
                     l[h] += __shfl_xor_sync(0xffffffffu, l[h], x);
             }
-            float* rl = red_l + (np & 1) * 4 * GP; // np counts non-empty pieces; empty ones share the buffer in turn
-            if (pc.n_tiles == 0)
-                softmax_warps_sync(); // (keeps the two-buffer rotation of red_l safe across empty pieces)
+            float* rl = red_l + (pi & 1) * 4 * GP; // two buffers in turn: one barrier per piece is enough
+            ++pi;
             if (lane == 0)
             {
 #pragma unroll
                 for (int h = 0; h < GP; ++h)
                     rl[warp * GP + h] = l[h];
             }
-            softmax_warps_sync();
+            if (softmax_warps_or((*sh.abort || !ok) ? 1 : 0))
+                break;
 #pragma unroll
             for (int h = 0; h < GP; ++h)
             {
@@ -747,10 +776,6 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
                     }
                 }
             }
-            if (pc.n_tiles == 0)
-                softmax_warps_sync();
-            else
-                ++np;
         }
     }
 
