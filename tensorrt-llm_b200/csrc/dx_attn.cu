@@ -347,7 +347,7 @@ bool build_streamk_ws(const dx_attn* h, Plan& plan, const int32_t* host_past, in
     const uint64_t total = acc * Y;
     if (total >= (1ull << 31))
         return false;
-    const uint64_t n1 = std::min<uint64_t>((uint64_t) h->sm_count, total);
+    const uint64_t n1 = std::min<uint64_t>((uint64_t) h->sm_count * (uint64_t) std::max(1, h->k_tokws.resident), total);
     uint64_t u1 = total * (uint64_t) (100 - h->ws_tail_pct) / 100 / n1, u2 = 0, n2 = 0;
     if (h->ws_tail_pct <= 0 || u1 < (uint64_t) h->ws_min_u1)
     {
@@ -373,7 +373,7 @@ bool build_streamk_ws(const dx_attn* h, Plan& plan, const int32_t* host_past, in
     plan.hgroups = 1;
     plan.heads16 = false;
     plan.six = false;
-    plan.resident = 1;
+    plan.resident = std::max(1, h->k_tokws.resident);
     plan.rows = batch * c.num_kv_heads;
     plan.nsplit = (int) pmax;
     plan.chunk_tokens = (int) (u1 * 128);
@@ -879,9 +879,9 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
             h->ws_min_u1 = std::max(1, atoi(m));
     }
     if (st == DX_OK)
-        st = check_cuda(h, cudaMalloc(reinterpret_cast<void**>(&h->status_dev), 256));
+        st = check_cuda(h, cudaMalloc(reinterpret_cast<void**>(&h->status_dev), 512));
     if (st == DX_OK)
-        st = check_cuda(h, cudaMemset(h->status_dev, 0, 256));
+        st = check_cuda(h, cudaMemset(h->status_dev, 0, 512));
     if (st != DX_OK)
     {
         if (h->status_dev)
@@ -1481,6 +1481,17 @@ int dx_attn_selftest_wait_timeout(dx_attn_t* h, int32_t poll_limit, void* cuda_s
         h->launches.fetch_add(1);
     return st;
 }
+
+#ifdef DX_TOKWS_TRACE
+// development builds only: reads and clears the 24 cycle counters behind the status word
+extern "C" int dx_attn_debug_counters(dx_attn_t* h, unsigned long long* out)
+{
+    cudaSetDevice(h->cfg.device);
+    cudaMemcpy(out, h->status_dev + 32, 24 * 8, cudaMemcpyDeviceToHost);
+    cudaMemset(h->status_dev + 32, 0, 24 * 8);
+    return 0;
+}
+#endif
 
 int dx_attn_last_cuda_error(const dx_attn_t* h)
 {

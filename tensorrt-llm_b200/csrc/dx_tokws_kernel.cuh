@@ -28,14 +28,24 @@
 #include "dx_tcgen05.cuh"
 #include "dx_tok_kernel.cuh" // split4_lo16
 
+// Optional cycle accounting of the roles (development builds only, -DDX_TOKWS_TRACE): every wait category adds the
+// cycles it spent to a counter behind the handle's status word.
+#ifdef DX_TOKWS_TRACE
+#define WS_T0() const long long ws_t0_ = clock64()
+#define WS_ACC(cat) ws_acc[cat] += clock64() - ws_t0_
+#define WS_TIMED(cat, expr) [&]() { const long long t0_ = clock64(); const bool r_ = (expr); ws_acc[cat] += clock64() - t0_; return r_; }()
+#else
+#define WS_TIMED(cat, expr) (expr)
+#endif
+
 namespace dx
 {
 
-template <int GP>
+template <int GP, int STAGES>
 struct TokWsTraits
 {
     static constexpr int DH = 128, TT = 128, N = 2 * GP;
-    static constexpr int NST = 6;            // ring stages (a K tile and a V tile each)
+    static constexpr int NST = STAGES;       // ring stages (a K tile and a V tile each)
     static constexpr int KV_TILE = TT * DH;  // bytes of a K (or V) tile
     static constexpr int Q_TILE = N * DH;
     static constexpr int P_TILE = TT * N;
@@ -207,11 +217,11 @@ __device__ __forceinline__ void softmax_warps_sync()
     asm volatile("bar.sync 1, 128;" ::: "memory");
 }
 
-template <typename T, int GP>
-__global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
+template <typename T, int GP, int STAGES, int MINB>
+__global__ void __launch_bounds__(TokWsTraits<GP, STAGES>::THREADS, MINB)
     tokws_decode_kernel(const AttnArgs a, const int hgroups_unused, const __grid_constant__ SkSchedule sk)
 {
-    using Tr = TokWsTraits<GP>;
+    using Tr = TokWsTraits<GP, STAGES>;
     constexpr int DH = Tr::DH, TT = Tr::TT, N = Tr::N, KV_TILE = Tr::KV_TILE, P_TILE = Tr::P_TILE, NST = Tr::NST;
     constexpr int Q_TILE = Tr::Q_TILE;
     constexpr int CACHE = CACHE_FP8;
@@ -301,6 +311,13 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
     w.done = false;
     w.range_idx = 0;
     WsPiece pc;
+#ifdef DX_TOKWS_TRACE
+    long long ws_acc[24];
+#pragma unroll
+    for (int i = 0; i < 24; ++i)
+        ws_acc[i] = 0;
+    const long long ws_start = clock64();
+#endif
 
     if (warp == 4)
     {
@@ -311,7 +328,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
         const uint32_t rl = lane >> 3, cl = lane & 7;
         const uint32_t d_even = rl * 128 + ((cl ^ rl) << 4), d_odd = rl * 128 + ((cl ^ (4 + rl)) << 4);
         int g = 0; // tiles put through the ring so far
-        while (ws_next_piece<TT>(sk, a, sh, w, pc, false, true, lane))
+        while (WS_TIMED(15, ws_next_piece<TT>(sk, a, sh, w, pc, false, true, lane)))
         {
             if (pc.n_tiles == 0)
                 continue;
@@ -352,7 +369,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
                     kp[q] = reinterpret_cast<const char*>(__ldg(krow + (t >> tpb_log2))) + off;
                     vp[q] = reinterpret_cast<const char*>(__ldg(vrow + (t >> tpb_log2))) + off;
                 }
-                ok = ws_wait_warp(&empty[s], ((g / NST) & 1) ^ 1, sh);
+                ok = WS_TIMED(0, ws_wait_warp(&empty[s], ((g / NST) & 1) ^ 1, sh));
                 if (!ok)
                     break;
                 const bool whole = t0 + TT <= new_pos; // every row of the tile is in the cache
@@ -427,7 +444,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
             auto issue_o = [&]() -> bool
             {
                 const int s = pend_g % NST, pb = pend_g & 1;
-                if (!ws_wait(&p_full[pb], (pend_g >> 1) & 1, sh) || !ws_wait(&full_v[s], (pend_g / NST) & 1, sh))
+                if (!WS_TIMED(4, ws_wait(&p_full[pb], (pend_g >> 1) & 1, sh)) || !WS_TIMED(5, ws_wait(&full_v[s], (pend_g / NST) & 1, sh)))
                     return false;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -447,16 +464,16 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
                 pend = false;
                 return true;
             };
-            while (ok && ws_next_piece<TT>(sk, a, sh, w, pc, false, false, 0))
+            while (ok && WS_TIMED(7, ws_next_piece<TT>(sk, a, sh, w, pc, false, false, 0)))
             {
                 if (pc.n_tiles == 0)
                     continue;
                 const int ob = np & 1; // Q buffer, O^T buffer of this piece
-                ok = ws_wait(&q_full[ob], (np >> 1) & 1, sh) && ws_wait(&o_empty[ob], ((np >> 1) & 1) ^ 1, sh);
+                ok = WS_TIMED(6, ws_wait(&q_full[ob], (np >> 1) & 1, sh) && ws_wait(&o_empty[ob], ((np >> 1) & 1) ^ 1, sh));
                 for (int i = 0; i < pc.n_tiles && ok; ++i, ++g)
                 {
                     const int s = g % NST;
-                    ok = ws_wait(&full_k[s], (g / NST) & 1, sh) && ws_wait(&s_empty[g & 1], ((g >> 1) & 1) ^ 1, sh);
+                    ok = WS_TIMED(2, ws_wait(&full_k[s], (g / NST) & 1, sh)) && WS_TIMED(3, ws_wait(&s_empty[g & 1], ((g >> 1) & 1) ^ 1, sh));
                     if (!ok)
                         break;
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -581,7 +598,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
         int g = 0, np = 0, pi = 0; // tiles, non-empty pieces, pieces so far
         for (;;)
         {
-            const bool got = ws_next_piece<TT>(sk, a, sh, w, pc, false, true, lane);
+            const bool got = WS_TIMED(12, ws_next_piece<TT>(sk, a, sh, w, pc, false, true, lane));
             if (softmax_warps_or(got ? 0 : 1))
                 break; // out of work (every thread sees the same tickets) or aborting
             const int head0 = pc.hk * G;
@@ -600,7 +617,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
             bool ok = true, leave = false;
             if (pc.n_tiles > 0)
             {
-                ok = ws_wait_warp(&q_full[ob], (np >> 1) & 1, sh);
+                ok = WS_TIMED(13, ws_wait_warp(&q_full[ob], (np >> 1) & 1, sh));
                 float sfac[GP];
 #pragma unroll
                 for (int h = 0; h < GP; ++h)
@@ -608,7 +625,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
                 for (int i = 0; i < pc.n_tiles; ++i, ++g)
                 {
                     const int sb = g & 1;
-                    ok = ok && ws_wait_warp(&s_full[sb], (g >> 1) & 1, sh);
+                    ok = ok && WS_TIMED(8, ws_wait_warp(&s_full[sb], (g >> 1) & 1, sh));
                     float s[GP], p[GP];
                     int exceed = 0;
                     if (ok)
@@ -642,7 +659,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
                         for (int h = 0; h < GP; ++h)
                             s[h] = 0.f, p[h] = 0.f;
                     }
-                    const int slow = softmax_warps_or(exceed | (ok ? 0 : 1));
+                    const int slow = WS_TIMED(11, softmax_warps_or(exceed | (ok ? 0 : 1)));
                     if (slow)
                     {
                         if (softmax_warps_or(*sh.abort)) // (a reduction again: other roles raise the flag at any time)
@@ -701,7 +718,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
                         }
                     }
                     // the P buffer of this parity is free once the O^T MMAs of tile g - 2 have completed
-                    ok = ok && ws_wait_warp(&p_empty[sb], ((g >> 1) & 1) ^ 1, sh);
+                    ok = ok && WS_TIMED(9, ws_wait_warp(&p_empty[sb], ((g >> 1) & 1) ^ 1, sh));
                     if (ok)
                     {
                         unsigned char* pbuf = smem + Tr::OFF_P + sb * P_TILE;
@@ -728,7 +745,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
                 if (leave)
                     break;
                 // ---- O^T of the piece ----
-                ok = ok && ws_wait_warp(&o_full[ob], (np >> 1) & 1, sh);
+                ok = ok && WS_TIMED(10, ws_wait_warp(&o_full[ob], (np >> 1) & 1, sh));
                 if (ok)
                 {
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -779,6 +796,16 @@ __global__ void __launch_bounds__(TokWsTraits<GP>::THREADS, 1)
         }
     }
 
+#ifdef DX_TOKWS_TRACE
+    if (lane == 0 && (warp == 0 || warp >= 4))
+    {
+        ws_acc[16 + (warp >= 4 ? warp - 3 : 0)] = clock64() - ws_start; // role life: 16 softmax, 17 producer, 18 MMA, 19 aux
+        unsigned long long* ctr = reinterpret_cast<unsigned long long*>(a.status + 32);
+        for (int i = 0; i < 24; ++i)
+            if (ws_acc[i])
+                atomicAdd(ctr + i, (unsigned long long) ws_acc[i]);
+    }
+#endif
     // ---- every role ends here: free tensor memory ----
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
