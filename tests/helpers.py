@@ -55,7 +55,8 @@ def gpu_step_and_compare(pkg, cfg, *, lengths=None, multi_block_mode=None, devic
     try:
         out = wl.run_step(plugin, w)
         torch.cuda.synchronize()
-        assert plugin.device_status() == 0
+        st = plugin.device_status()
+        assert st == 0, f"device status {st} ({pkg.plugin._strerror(st)})"
         ref, pool_ref = oracle_step(w_cpu)
         pool_gpu = w.pool.cpu()
         # (1) the KV bytes written and where: whole pool identical to the oracle's pool
