@@ -37,8 +37,12 @@
 // cycles it spent to a counter behind the handle's status word.
 #ifdef DX_TOKWS_TRACE
 #define WS_TIMED(cat, expr) [&]() { const long long t0_ = clock64(); const bool r_ = (expr); ws_acc[cat] += clock64() - t0_; return r_; }()
+#define WS_STAMP(var) const long long var = clock64()
+#define WS_SINCE(cat, var) ws_acc[cat] += clock64() - var
 #else
 #define WS_TIMED(cat, expr) (expr)
+#define WS_STAMP(var)
+#define WS_SINCE(cat, var)
 #endif
 
 namespace dx
@@ -818,6 +822,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP, UNITS>::THREADS, 1)
                     const int slow = WS_TIMED(11, group_or(wg, exceed | (ok ? 0 : 1)));
                     if (slow)
                     {
+                        WS_STAMP(t_slow);
                         // Some score left the range the current reference covers (always on the group's first tile of
                         // a piece): take the tile's maximum, rescale O^T in tensor memory, recompute the tile's P.
                         float mx[GP];
@@ -869,6 +874,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP, UNITS>::THREADS, 1)
                                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                             }
                         }
+                        WS_SINCE(23, t_slow);
                     }
                     // the P buffer of this parity is free once the O^T MMAs of the group's tile before last have completed
                     ok = ok && WS_TIMED(9, ws_wait_warp(&p_empty[si], ((c >> 1) & 1) ^ 1, sh));
@@ -911,6 +917,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP, UNITS>::THREADS, 1)
             // ---- result of the piece: thread = Dh channel.  With tiles in both groups the group that does not hold
             // the last tile (it is done first) takes the other one's share from the exchange buffer and writes;
             // the other group hands its share over and goes on with the next piece. ----
+            WS_STAMP(t_epi);
             const bool two = pc.n_tiles > 1;
             const int merger = two ? (pc.n_tiles & 1) : 0;
             if (!mine && wg != merger)
@@ -931,6 +938,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP, UNITS>::THREADS, 1)
                     rl[wl * GP + h] = l[h];
             }
             group_sync(wg);
+            WS_SINCE(1, t_epi); // (l reduction and group barrier)
             const int par = hx & 1;
             if (wg != merger)
             {
@@ -997,6 +1005,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP, UNITS>::THREADS, 1)
                 if (two)
                     mbar_arrive(&x_empty[par]);
             }
+            WS_SINCE(22, t_epi);
         }
     }
 
