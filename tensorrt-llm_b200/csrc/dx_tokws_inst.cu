@@ -5,32 +5,38 @@
 
 namespace dx
 {
-// Ring units (16 KB each) per CTA: what fits beside the Q / P / merge buffers.
+// CTAs per SM and ring stages per CTA.  Two CTAs with three stages each: two independent softmax / MMA pipelines per
+// SM hide each other's piece boundaries and synchronisation latencies; the ring memory per SM is the same.
 template <int GP>
 struct TokWsBuild
 {
-    static constexpr int UNITS = GP == 8 ? 12 : 10;
+    static constexpr int MINB = 2, NST = 3;
+};
+template <> // 16 padded heads: the Q and P buffers are twice as large and two CTAs no longer fit
+struct TokWsBuild<16>
+{
+    static constexpr int MINB = 1, NST = 6;
 };
 
-// One CTA per SM by shared memory, so the 256 tensor-memory columns it allocates are always there: tcgen05.alloc,
-// which has no bounded form, cannot block.
+// tcgen05.alloc has no bounded form: the CTAs that fit on one SM by shared memory must fit in its 512 columns.
 template <int GP>
 constexpr bool tokws_fits()
 {
-    using Tr = TokWsTraits<GP, TokWsBuild<GP>::UNITS>;
-    return Tr::SMEM_BYTES <= 227 * 1024 && 2 * Tr::SMEM_BYTES > 227 * 1024;
+    using Tr = TokWsTraits<GP, TokWsBuild<GP>::NST>;
+    const int by_smem = 227 * 1024 / Tr::SMEM_BYTES;
+    return by_smem >= TokWsBuild<GP>::MINB && by_smem * Tr::TMEM_COLS <= 512;
 }
-static_assert(tokws_fits<8>() && tokws_fits<16>(), "shared memory budget: exactly one CTA per SM");
+static_assert(tokws_fits<8>() && tokws_fits<16>(), "shared memory / tensor memory budget");
 
 template <typename T, int GP>
 static KernelInfo mk()
 {
-    constexpr int U = TokWsBuild<GP>::UNITS;
+    using B = TokWsBuild<GP>;
     KernelInfo k;
-    k.fn = reinterpret_cast<const void*>(&tokws_decode_kernel<T, GP, U>);
-    k.smem = TokWsTraits<GP, U>::SMEM_BYTES;
-    k.resident = 1;
-    k.threads = TokWsTraits<GP, U>::THREADS;
+    k.fn = reinterpret_cast<const void*>(&tokws_decode_kernel<T, GP, B::NST, B::MINB>);
+    k.smem = TokWsTraits<GP, B::NST>::SMEM_BYTES;
+    k.resident = B::MINB;
+    k.threads = TokWsTraits<GP, B::NST>::THREADS;
     return k;
 }
 
