@@ -75,7 +75,7 @@ struct dx_attn
     bool tok = false;        // token-major tcgen05 kernel usable for this configuration
     KernelInfo k_tokws{};    // its persistent warp-specialised form
     bool tokws = false;
-    int ws_tail_pct = 20;    // share of the tiles (per cent) handed out as short dynamic ranges
+    int ws_tail_pct = 0;     // share of the tiles (per cent) handed out as short dynamic ranges (0: static ranges only)
     int ws_tail_div = 8;     // a dynamic range is 1/ws_tail_div of a static one ...
     int ws_min_u2 = 2;       // ... but at least this many 128-token tiles
     int ws_min_u1 = 8;       // below this many tiles per static range the schedule stays single-level
@@ -1481,17 +1481,6 @@ int dx_attn_selftest_wait_timeout(dx_attn_t* h, int32_t poll_limit, void* cuda_s
         h->launches.fetch_add(1);
     return st;
 }
-
-#ifdef DX_TOKWS_TRACE
-// development builds only: reads and clears the 24 cycle counters behind the status word
-extern "C" int dx_attn_debug_counters(dx_attn_t* h, unsigned long long* out)
-{
-    cudaSetDevice(h->cfg.device);
-    cudaMemcpy(out, h->status_dev + 32, 24 * 8, cudaMemcpyDeviceToHost);
-    cudaMemset(h->status_dev + 32, 0, 24 * 8);
-    return 0;
-}
-#endif
 
 int dx_attn_last_cuda_error(const dx_attn_t* h)
 {

@@ -1,23 +1,40 @@
 // Grouped-head decode attention over an FP8 paged KV cache on the 5th-generation tensor cores: the persistent,
-// warp-specialised form of the token-major kernel (dx_tok_kernel.cuh).  One CTA per SM walks ranges of the batch's
-// 128-token tiles (SkSchedule: a long static range first, then short ranges taken from a device counter, so that
-// the SMs that stream faster take more of the tail) and the copy stream never stops at a row or range boundary:
+// warp-specialised form of the token-major kernel (dx_tok_kernel.cuh).  Opt-in (DX_ATTN_TOKWS=1).  A CTA walks a range of
+// the batch's 128-token tiles (SkSchedule: one static range per CTA and, optionally, short ranges taken from a device
+// counter afterwards) and its copy stream never stops at a row or range boundary:
 //
 //   warp 4  producer : walks the tiles, copies K and V tiles (16-byte cp.async into the 128-byte hardware swizzle)
-//                      into a ring of NST stages as soon as a stage is free; quantises and appends the new token
+//                      into a ring of NST stages as soon as the stage's K (or V) half is free; quantises and appends
+//                      the new token
 //   warp 5  MMA      : one thread issues  S^T(g) = K(g) Qx^T  and, one tile behind,  O^T += V(g-1)^T Px(g-1)
 //                      (tcgen05.mma kind::f8f6f4, cache bytes as stored, accumulators in tensor memory);
-//                      tcgen05.commit on mbarriers frees ring stages and publishes S^T / O^T
+//                      tcgen05.commit on mbarriers frees the K half behind S^T, the V half behind O^T, and
+//                      publishes S^T / O^T
 //   warp 6  aux      : prepares Qx (high / low e4m3 parts of the q rows) of the next piece into the other Q buffer,
-//                      and draws the tickets of the dynamic ranges
+//                      and draws the ticket of the next dynamic range when the range before it is used up
 //   warps 0-3 softmax: thread = token row of S^T (tensor-memory lane); lazy reference maximum, probabilities as
 //                      high / low e4m3 parts into the P buffer; at the end of a piece thread = Dh channel of O^T
 //
 // S^T, P and O^T are double-buffered (tile parity, piece parity), so the tensor core computes S^T(g+1) while the
-// softmax warps work on tile g, and the epilogue of a piece overlaps the first tiles of the next one.
+// softmax warps work on tile g, and the epilogue of a piece overlaps the first tiles of the next one.  Groups of up
+// to 8 heads run two such CTAs per SM (three ring stages each), so that one CTA's piece boundaries and
+// synchronisation latencies run beside the other's tiles; 16 padded heads run one CTA with six stages.
 // Operand layouts, descriptors and the high / low split are those of the token-major kernel.
 // Every wait is bounded; a wait that runs out raises a CTA-wide abort flag, records STATUS_TIMEOUT, and every role
 // leaves its loop; copies and MMAs in flight are drained and tensor memory is freed on every path.
+//
+// What was measured on B200 while building it (Llama-2-70B-shaped batch, 793 MB of FP8 KV, 148 SMs):
+//   * one thread issues a tcgen05.mma (M 128, K 32, any N up to 128) every ~60 cycles at best, ~107 cycles in
+//     groups of four: the eight MMAs of a tile cost the issuing thread 0.3-0.5 us, as much as the softmax of a tile;
+//   * one warp issues a 16-byte cp.async every ~35-40 cycles: 64 of them per tile and lane keep a producer warp busy
+//     for ~1.1 us per tile, so one producer warp feeds at most ~28 GB/s;
+//   * a piece boundary costs a softmax group 4-6 us (accumulator read-out behind the last MMAs, row-sum reduction,
+//     strided result stores behind the copy traffic, first-tile maximum of the next piece), which is why short
+//     dynamic ranges make this kernel slower, not faster;
+//   * this form: 150 us per step against 140 us for the mma.sync kernel in the same run; variants with one CTA per
+//     SM, two softmax groups sharing the tiles of a piece, four MMA-issuing threads and separate K / V producer
+//     warps reached 155 us; with tiled bulk-tensor copies through a tensor map of the KV pool 267 us (each copy
+//     instruction then held its issuing thread for ~0.25 us).  It therefore stays opt-in.
 //
 // Replaces what the reference runs as XQA (decoderXQAImplPrecompiled.cpp:223-374) or as one MMHA CTA per q head
 // (decoderMaskedMultiheadAttentionTemplate.h:1303) for grouped heads with an FP8 cache.
@@ -27,16 +44,6 @@
 #include "dx_mha_kernel.cuh" // make_cache_vec
 #include "dx_tcgen05.cuh"
 #include "dx_tok_kernel.cuh" // split4_lo16
-
-// Optional cycle accounting of the roles (development builds only, -DDX_TOKWS_TRACE): every wait category adds the
-// cycles it spent to a counter behind the handle's status word.
-#ifdef DX_TOKWS_TRACE
-#define WS_T0() const long long ws_t0_ = clock64()
-#define WS_ACC(cat) ws_acc[cat] += clock64() - ws_t0_
-#define WS_TIMED(cat, expr) [&]() { const long long t0_ = clock64(); const bool r_ = (expr); ws_acc[cat] += clock64() - t0_; return r_; }()
-#else
-#define WS_TIMED(cat, expr) (expr)
-#endif
 
 namespace dx
 {
@@ -320,13 +327,6 @@ __global__ void __launch_bounds__(TokWsTraits<GP, STAGES>::THREADS, MINB)
     w.done = false;
     w.range_idx = 0;
     WsPiece pc;
-#ifdef DX_TOKWS_TRACE
-    long long ws_acc[24];
-#pragma unroll
-    for (int i = 0; i < 24; ++i)
-        ws_acc[i] = 0;
-    const long long ws_start = clock64();
-#endif
 
     if (warp == 4)
     {
@@ -337,7 +337,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP, STAGES>::THREADS, MINB)
         const uint32_t rl = lane >> 3, cl = lane & 7;
         const uint32_t d_even = rl * 128 + ((cl ^ rl) << 4), d_odd = rl * 128 + ((cl ^ (4 + rl)) << 4);
         int g = 0; // tiles put through the ring so far
-        while (WS_TIMED(15, ws_next_piece<TT>(sk, a, sh, w, pc, false, true, lane)))
+        while (ws_next_piece<TT>(sk, a, sh, w, pc, false, true, lane))
         {
             if (pc.n_tiles == 0)
                 continue;
@@ -382,7 +382,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP, STAGES>::THREADS, MINB)
 #pragma unroll
                 for (int kv = 0; kv < 2; ++kv)
                 {
-                    ok = WS_TIMED(0, ws_wait_warp(kv ? &empty_v[s] : &empty_k[s], ((g / NST) & 1) ^ 1, sh));
+                    ok = ws_wait_warp(kv ? &empty_v[s] : &empty_k[s], ((g / NST) & 1) ^ 1, sh);
                     if (!ok)
                         break;
                     const uint32_t dst = kv ? vdst : kdst;
@@ -453,7 +453,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP, STAGES>::THREADS, MINB)
             auto issue_o = [&]() -> bool
             {
                 const int s = pend_g % NST, pb = pend_g & 1;
-                if (!WS_TIMED(4, ws_wait(&p_full[pb], (pend_g >> 1) & 1, sh)) || !WS_TIMED(5, ws_wait(&full_v[s], (pend_g / NST) & 1, sh)))
+                if (!ws_wait(&p_full[pb], (pend_g >> 1) & 1, sh) || !ws_wait(&full_v[s], (pend_g / NST) & 1, sh))
                     return false;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -473,16 +473,16 @@ __global__ void __launch_bounds__(TokWsTraits<GP, STAGES>::THREADS, MINB)
                 pend = false;
                 return true;
             };
-            while (ok && WS_TIMED(7, ws_next_piece<TT>(sk, a, sh, w, pc, false, false, 0)))
+            while (ok && ws_next_piece<TT>(sk, a, sh, w, pc, false, false, 0))
             {
                 if (pc.n_tiles == 0)
                     continue;
                 const int ob = np & 1; // Q buffer, O^T buffer of this piece
-                ok = WS_TIMED(6, ws_wait(&q_full[ob], (np >> 1) & 1, sh) && ws_wait(&o_empty[ob], ((np >> 1) & 1) ^ 1, sh));
+                ok = ws_wait(&q_full[ob], (np >> 1) & 1, sh) && ws_wait(&o_empty[ob], ((np >> 1) & 1) ^ 1, sh);
                 for (int i = 0; i < pc.n_tiles && ok; ++i, ++g)
                 {
                     const int s = g % NST;
-                    ok = WS_TIMED(2, ws_wait(&full_k[s], (g / NST) & 1, sh)) && WS_TIMED(3, ws_wait(&s_empty[g & 1], ((g >> 1) & 1) ^ 1, sh));
+                    ok = ws_wait(&full_k[s], (g / NST) & 1, sh) && ws_wait(&s_empty[g & 1], ((g >> 1) & 1) ^ 1, sh);
                     if (!ok)
                         break;
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -600,7 +600,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP, STAGES>::THREADS, MINB)
         int g = 0, np = 0, pi = 0; // tiles, non-empty pieces, pieces so far
         for (;;)
         {
-            const bool got = WS_TIMED(12, ws_next_piece<TT>(sk, a, sh, w, pc, false, true, lane));
+            const bool got = ws_next_piece<TT>(sk, a, sh, w, pc, false, true, lane);
             if (softmax_warps_or(got ? 0 : 1))
                 break; // out of work (every thread sees the same tickets) or aborting
             const int head0 = pc.hk * G;
@@ -619,7 +619,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP, STAGES>::THREADS, MINB)
             bool ok = true, leave = false;
             if (pc.n_tiles > 0)
             {
-                ok = WS_TIMED(13, ws_wait_warp(&q_full[ob], (np >> 1) & 1, sh));
+                ok = ws_wait_warp(&q_full[ob], (np >> 1) & 1, sh);
                 float sfac[GP];
 #pragma unroll
                 for (int h = 0; h < GP; ++h)
@@ -627,7 +627,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP, STAGES>::THREADS, MINB)
                 for (int i = 0; i < pc.n_tiles; ++i, ++g)
                 {
                     const int sb = g & 1;
-                    ok = ok && WS_TIMED(8, ws_wait_warp(&s_full[sb], (g >> 1) & 1, sh));
+                    ok = ok && ws_wait_warp(&s_full[sb], (g >> 1) & 1, sh);
                     float s[GP], p[GP];
                     int exceed = 0;
                     if (ok)
@@ -661,7 +661,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP, STAGES>::THREADS, MINB)
                         for (int h = 0; h < GP; ++h)
                             s[h] = 0.f, p[h] = 0.f;
                     }
-                    const int slow = WS_TIMED(11, softmax_warps_or(exceed | (ok ? 0 : 1)));
+                    const int slow = softmax_warps_or(exceed | (ok ? 0 : 1));
                     if (slow)
                     {
                         if (softmax_warps_or(*sh.abort)) // (a reduction again: other roles raise the flag at any time)
@@ -720,7 +720,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP, STAGES>::THREADS, MINB)
                         }
                     }
                     // the P buffer of this parity is free once the O^T MMAs of tile g - 2 have completed
-                    ok = ok && WS_TIMED(9, ws_wait_warp(&p_empty[sb], ((g >> 1) & 1) ^ 1, sh));
+                    ok = ok && ws_wait_warp(&p_empty[sb], ((g >> 1) & 1) ^ 1, sh);
                     if (ok)
                     {
                         unsigned char* pbuf = smem + Tr::OFF_P + sb * P_TILE;
@@ -747,7 +747,7 @@ __global__ void __launch_bounds__(TokWsTraits<GP, STAGES>::THREADS, MINB)
                 if (leave)
                     break;
                 // ---- O^T of the piece ----
-                ok = ok && WS_TIMED(10, ws_wait_warp(&o_full[ob], (np >> 1) & 1, sh));
+                ok = ok && ws_wait_warp(&o_full[ob], (np >> 1) & 1, sh);
                 if (ok)
                 {
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -798,16 +798,6 @@ __global__ void __launch_bounds__(TokWsTraits<GP, STAGES>::THREADS, MINB)
         }
     }
 
-#ifdef DX_TOKWS_TRACE
-    if (lane == 0 && (warp == 0 || warp >= 4))
-    {
-        ws_acc[16 + (warp >= 4 ? warp - 3 : 0)] = clock64() - ws_start; // role life: 16 softmax, 17 producer, 18 MMA, 19 aux
-        unsigned long long* ctr = reinterpret_cast<unsigned long long*>(a.status + 32);
-        for (int i = 0; i < 24; ++i)
-            if (ws_acc[i])
-                atomicAdd(ctr + i, (unsigned long long) ws_acc[i]);
-    }
-#endif
     // ---- every role ends here: free tensor memory ----
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
