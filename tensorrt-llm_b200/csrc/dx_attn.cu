@@ -163,7 +163,7 @@ Plan plan_shape(const dx_attn* h, int batch, int& rows_per_seq_out)
         p.hgroups = (h->group + 15) / 16;
         p.heads16 = h->group > 8;
         rows_per_seq = c.num_kv_heads * p.hgroups;
-        resident = std::max(1, h->k_gqa[p.heads16 ? 1 : 0].resident);
+        resident = (h->cache_kind == CACHE_FP8 && c.head_size == 128 && !p.heads16) ? 3 : 2;
     }
     else
     {
@@ -439,25 +439,13 @@ int check_cuda(dx_attn* h, cudaError_t e)
     return DX_ERR_CUDA;
 }
 
-// Opts the kernel into its dynamic shared memory.  k.resident (CTAs per SM the kernel was built for) is lowered to
-// what the device will really keep resident, so that the planner counts true waves.
-int set_smem(dx_attn* h, KernelInfo& k)
+int set_smem(dx_attn* h, const KernelInfo& k)
 {
     if (!k.fn)
         return DX_OK;
     if (k.smem > h->max_smem_optin)
         return DX_ERR_UNSUPPORTED;
-    int st = check_cuda(h, cudaFuncSetAttribute(k.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, k.smem));
-    if (st != DX_OK || k.resident <= 0)
-        return st;
-    int occ = 0;
-    st = check_cuda(h, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k.fn, k.threads, (size_t) k.smem));
-    if (st != DX_OK)
-        return st;
-    if (occ < 1)
-        return DX_ERR_UNSUPPORTED;
-    k.resident = std::min(k.resident, occ);
-    return DX_OK;
+    return check_cuda(h, cudaFuncSetAttribute(k.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, k.smem));
 }
 
 template <typename T, int DH>

@@ -13,7 +13,6 @@ static KernelInfo mk()
     KernelInfo k;
     k.fn = reinterpret_cast<const void*>(&gqa_decode_kernel<T, CACHE, DH, H16>);
     k.smem = GqaTraits<DH, gqa_min_blocks<CACHE, DH, H16>()>::SMEM_BYTES;
-    k.resident = gqa_min_blocks<CACHE, DH, H16>();
     return k;
 }
 
