@@ -241,11 +241,24 @@ size_t dx_attn_static_scratch_bytes(void);
  * [batch, num_kv_heads, seq_len, head_size], into the paged cache with the same quantise-on-write as the
  * decode step; tokens at or beyond sequence_lengths[b] are skipped.  Replaces invokeTranspose4dBatchMajor
  * (cpp/tensorrt_llm/kernels/unfusedAttentionKernels.cu:1638-1666), same argument meaning.
- * attention_window_size < seq_len (cyclic cache) is not implemented: DX_ERR_UNSUPPORTED. */
+ * attention_window_size < sequence_lengths[b]: the cache is cyclic, only the last attention_window_size tokens
+ * of the sequence are stored (:1591-1600), token t in slot t % attention_window_size - or, in a table with a spare
+ * block ((max_blocks_per_sequence - 1) * tokens_per_block >= attention_window_size), in slot
+ * t % (attention_window_size + tokens_per_block), as KVBlockArray::getKVTokenIdx lays it out
+ * (cpp/tensorrt_llm/kernels/kvCacheUtils.h:71-117). */
 int dx_attn_append_context(dx_attn_t* handle, const void* k_src, const void* v_src,
     const int32_t* sequence_lengths, int32_t batch, int32_t seq_len, int32_t attention_window_size,
     const int64_t* block_pointers, int32_t max_blocks_per_sequence, const float* kv_scale_orig_quant,
     void* cuda_stream);
+
+/* The same with sink tokens (the KVBlockArray the reference builds for the context phase carries
+ * params.sink_token_length, cpp/tensorrt_llm/plugins/gptAttentionCommon/gptAttentionCommon.cpp:659-660):
+ * tokens below sink_token_length keep their slots, the others cycle behind them; sink tokens that end inside
+ * a block leave the rest of that block unused.  0 <= sink_token_length < attention_window_size. */
+int dx_attn_append_context_cyclic(dx_attn_t* handle, const void* k_src, const void* v_src,
+    const int32_t* sequence_lengths, int32_t batch, int32_t seq_len, int32_t attention_window_size,
+    int32_t sink_token_length, const int64_t* block_pointers, int32_t max_blocks_per_sequence,
+    const float* kv_scale_orig_quant, void* cuda_stream);
 
 /* Waits until the outputs of all dx_attn_enqueue_generation_host calls made so far are in host memory.
  * No reference counterpart (the reference runtime synchronises the whole stream every step). */

@@ -19,6 +19,7 @@ these sums and is not reproduced.
 from __future__ import annotations
 
 import math
+from typing import Optional
 
 import torch
 
@@ -75,26 +76,50 @@ def decode_attention_reference(qkv: torch.Tensor, sequence_lengths: torch.Tensor
     return out
 
 
+def kv_slot_of_token(t: int, *, tokens_per_block: int, max_blocks_per_seq: int, attention_window_size: int,
+                     sink_token_length: int = 0) -> int:
+    """KVBlockArray::getKVTokenIdx with the constants its constructor derives
+    (cpp/tensorrt_llm/kernels/kvCacheUtils.h:71-90, :109-117): sink tokens keep their index; the others cycle
+    behind the sink block(s), skipping the unused rest (bubble) of a partly filled sink block; a table with a
+    spare block cycles over attention_window_size + tokens_per_block slots."""
+    in_last = sink_token_length % tokens_per_block
+    bubble = 0 if in_last == 0 else tokens_per_block - in_last
+    one_more = (max_blocks_per_seq - 1) * tokens_per_block >= attention_window_size + bubble
+    cyclic_len = attention_window_size + tokens_per_block - sink_token_length if one_more \
+        else attention_window_size - sink_token_length
+    if t < sink_token_length:
+        return t
+    return sink_token_length + bubble + (t - sink_token_length) % cyclic_len
+
+
 def append_context_reference(k: torch.Tensor, v: torch.Tensor, sequence_lengths: torch.Tensor, pool: torch.Tensor,
                              offset_table: torch.Tensor, *, tokens_per_block: int, cache_mode: int,
-                             kv_scale_orig_quant: float = 1.0) -> None:
+                             kv_scale_orig_quant: float = 1.0, attention_window_size: Optional[int] = None,
+                             sink_token_length: int = 0) -> None:
     """Context-phase KV write, restated from transpose4dBatchMajorKVCache
     (cpp/tensorrt_llm/kernels/unfusedAttentionKernels.cu:1565-1636): for every sequence b, head h and token
-    t < sequence_lengths[b], the (quantised) K[b, h, t, :] goes to block offset_table[b, 0, t // tpb] at local
-    index (h * tpb + t % tpb) * Dh (kvCacheUtils.h:144-152), V likewise through row 1.
+    t < sequence_lengths[b], the (quantised) K[b, h, t, :] goes to the block of slot s = getKVTokenIdx(t),
+    offset_table[b, 0, s // tpb], at local index (h * tpb + s % tpb) * Dh (kvCacheUtils.h:144-152), V likewise
+    through row 1.  Tokens below sequence_lengths[b] - attention_window_size are dropped (:1591-1600).  Tokens are
+    written in ascending order, so of two tokens that share a slot the later one stays (the reference leaves that
+    to thread timing).
     k, v: T [B, Hkv, seq_len, Dh] on CPU; pool: uint8, mutated in place."""
     B, Hkv, L, Dh = k.shape
     esz = 2 if cache_mode == CACHE_T else 1
     row = Dh * esz
     blk = Hkv * tokens_per_block * row
+    M = offset_table.shape[-1]
+    window = attention_window_size if attention_window_size is not None else M * tokens_per_block
     pool_blocks = pool.view(-1, Hkv, tokens_per_block, row)
     kq = quantize_kv(k, kv_scale_orig_quant, cache_mode)  # [B, Hkv, L, row]
     vq = quantize_kv(v, kv_scale_orig_quant, cache_mode)
     for b in range(B):
-        n = min(int(sequence_lengths[b]), L)
-        for t0 in range(0, n, tokens_per_block):
-            t1 = min(n, t0 + tokens_per_block)
-            ko, vo = int(offset_table[b, 0, t0 // tokens_per_block]), int(offset_table[b, 1, t0 // tokens_per_block])
+        n_all = int(sequence_lengths[b])
+        n = min(n_all, L)
+        for t in range(max(n_all - window, 0), n):
+            s = kv_slot_of_token(t, tokens_per_block=tokens_per_block, max_blocks_per_seq=M,
+                                 attention_window_size=window, sink_token_length=sink_token_length)
+            ko, vo = int(offset_table[b, 0, s // tokens_per_block]), int(offset_table[b, 1, s // tokens_per_block])
             assert ko >= 0 and vo >= 0 and ko % blk == 0 and vo % blk == 0
-            pool_blocks[ko // blk, :, : t1 - t0, :] = kq[b, :, t0:t1]
-            pool_blocks[vo // blk, :, : t1 - t0, :] = vq[b, :, t0:t1]
+            pool_blocks[ko // blk, :, s % tokens_per_block, :] = kq[b, :, t]
+            pool_blocks[vo // blk, :, s % tokens_per_block, :] = vq[b, :, t]

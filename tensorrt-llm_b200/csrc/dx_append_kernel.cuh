@@ -9,7 +9,8 @@
 //
 // Replaces transpose4dBatchMajorKVCache / invokeTranspose4dBatchMajor
 //   cpp/tensorrt_llm/kernels/unfusedAttentionKernels.cu:1565-1666
-// (same argument meaning; tokens beyond sequence_lengths[b] are skipped).
+// (same argument meaning; tokens beyond sequence_lengths[b] are skipped; with a window shorter than the prompt
+// the cache is cyclic and only the last `window` tokens are kept, :1591-1600).
 #pragma once
 
 #include "dx_common.cuh"
@@ -30,6 +31,12 @@ struct AppendArgs
     int32_t src_seq_len;          // row stride of the source, tokens
     int32_t max_blocks_per_seq;
     int32_t tpb_log2;
+    // cyclic cache (KVBlockArray::getKVTokenIdx, kvCacheUtils.h:109-117): token t >= sink lives in slot
+    // sink + bubble + (t - sink) % cyclic_len; only the last `window` tokens of a sequence are stored
+    int32_t window;
+    int32_t sink;
+    int32_t bubble;
+    int32_t cyclic_len;
 };
 
 template <typename T, int CACHE, int DH>
@@ -41,9 +48,17 @@ __global__ void __launch_bounds__(256) kv_append_context_kernel(const AppendArgs
     const int b = blockIdx.y, h = blockIdx.z;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     const int tok = idx / LPR, part = idx % LPR;
-    const int n = min(a.seq_len[b], a.src_seq_len);
-    if (tok >= n)
+    const int len = a.seq_len[b];
+    // tokens that left the window are dropped, as in the reference (the sink tokens too when the prompt is longer
+    // than the window: unfusedAttentionKernels.cu:1591-1600 tests the lower bound for every token)
+    if (tok >= min(len, a.src_seq_len) || tok < len - a.window)
         return;
+    // With sink tokens and no spare block the window holds more tokens than slots cycle: of the tokens that share a
+    // slot the latest stays (in the reference whichever thread stores last wins; this is the outcome that keeps
+    // the newest tokens, and it is deterministic).
+    if (tok >= a.sink && tok + a.cyclic_len < len)
+        return;
+    const int slot = tok < a.sink ? tok : a.sink + a.bubble + (tok - a.sink) % a.cyclic_len;
     float sc_f = 1.f;
     T sc_t = TypeOps<T>::from_float(1.f);
     if constexpr (CACHE != CACHE_T)
@@ -57,9 +72,9 @@ __global__ void __launch_bounds__(256) kv_append_context_kernel(const AppendArgs
     const int64_t* krow = a.block_ptrs + (int64_t) b * 2 * a.max_blocks_per_seq;
     const int64_t* vrow = krow + a.max_blocks_per_seq;
     const int tpb_mask = (1 << a.tpb_log2) - 1;
-    const size_t off = ((size_t) h * ((size_t) 1 << a.tpb_log2) + (tok & tpb_mask)) * (DH * ECB) + part * 16;
-    char* kb = reinterpret_cast<char*>(__ldg(krow + (tok >> a.tpb_log2))) + off;
-    char* vb = reinterpret_cast<char*>(__ldg(vrow + (tok >> a.tpb_log2))) + off;
+    const size_t off = ((size_t) h * ((size_t) 1 << a.tpb_log2) + (slot & tpb_mask)) * (DH * ECB) + part * 16;
+    char* kb = reinterpret_cast<char*>(__ldg(krow + (slot >> a.tpb_log2))) + off;
+    char* vb = reinterpret_cast<char*>(__ldg(vrow + (slot >> a.tpb_log2))) + off;
     *reinterpret_cast<uint4*>(kb) = kq;
     *reinterpret_cast<uint4*>(vb) = vq;
 }

@@ -1424,7 +1424,16 @@ int dx_attn_append_context(dx_attn_t* h, const void* k_src, const void* v_src, c
     int32_t batch, int32_t seq_len, int32_t attention_window_size, const int64_t* block_pointers,
     int32_t max_blocks_per_sequence, const float* kv_scale_orig_quant, void* cuda_stream)
 {
-    if (!h || batch < 0 || seq_len < 0 || max_blocks_per_sequence <= 0)
+    return dx_attn_append_context_cyclic(h, k_src, v_src, sequence_lengths, batch, seq_len, attention_window_size, 0,
+        block_pointers, max_blocks_per_sequence, kv_scale_orig_quant, cuda_stream);
+}
+
+int dx_attn_append_context_cyclic(dx_attn_t* h, const void* k_src, const void* v_src, const int32_t* sequence_lengths,
+    int32_t batch, int32_t seq_len, int32_t attention_window_size, int32_t sink_token_length,
+    const int64_t* block_pointers, int32_t max_blocks_per_sequence, const float* kv_scale_orig_quant, void* cuda_stream)
+{
+    if (!h || batch < 0 || seq_len < 0 || max_blocks_per_sequence <= 0 || attention_window_size < 1
+        || sink_token_length < 0 || sink_token_length >= attention_window_size)
         return DX_ERR_BAD_ARG;
     if (batch == 0 || seq_len == 0)
         return DX_OK;
@@ -1435,9 +1444,19 @@ int dx_attn_append_context(dx_attn_t* h, const void* k_src, const void* v_src, c
     const dx_attn_config& c = h->cfg;
     if (h->cache_kind != CACHE_T && !kv_scale_orig_quant)
         return DX_ERR_BAD_ARG;
-    if (attention_window_size < seq_len)
-        return DX_ERR_UNSUPPORTED; // cyclic cache (dropping the oldest tokens) is not implemented
-    if ((int64_t) seq_len > (int64_t) max_blocks_per_sequence * c.tokens_per_block)
+    // Slot arithmetic of KVBlockArray (kvCacheUtils.h:71-90): sink tokens that end inside a block leave the rest of
+    // that block unused (the bubble); a table with a spare block keeps window + tokens_per_block slots cycling.
+    const int tpb = c.tokens_per_block;
+    const int in_last = sink_token_length % tpb;
+    const int bubble = in_last == 0 ? 0 : tpb - in_last;
+    const bool one_more_block = (int64_t) (max_blocks_per_sequence - 1) * tpb >= (int64_t) attention_window_size + bubble;
+    const int64_t cyclic_len = one_more_block ? (int64_t) attention_window_size + tpb - sink_token_length
+                                              : (int64_t) attention_window_size - sink_token_length;
+    // the highest slot a prompt of seq_len tokens can touch has to be inside the table
+    const int64_t top_slot = seq_len <= sink_token_length
+        ? (int64_t) seq_len - 1
+        : (int64_t) sink_token_length + bubble + std::min<int64_t>((int64_t) seq_len - sink_token_length, cyclic_len) - 1;
+    if (top_slot >= (int64_t) max_blocks_per_sequence * tpb)
         return DX_ERR_BAD_ARG;
     if (!h->k_append.fn)
         return DX_ERR_UNSUPPORTED;
@@ -1452,6 +1471,10 @@ int dx_attn_append_context(dx_attn_t* h, const void* k_src, const void* v_src, c
     a.src_seq_len = seq_len;
     a.max_blocks_per_seq = max_blocks_per_sequence;
     a.tpb_log2 = h->tpb_log2;
+    a.window = attention_window_size;
+    a.sink = sink_token_length;
+    a.bubble = bubble;
+    a.cyclic_len = (int32_t) cyclic_len;
     int st = check_cuda(h, cudaSetDevice(c.device));
     if (st != DX_OK)
         return st;

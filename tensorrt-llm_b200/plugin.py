@@ -90,6 +90,7 @@ EXPORTED_SYMBOLS = [
     "dx_attn_enqueue_generation", "dx_attn_enqueue_generation_host", "dx_attn_host_sync", "dx_kv_cache_step", "dx_attn_validate", "dx_attn_plan", "dx_attn_plan_lengths",
     "dx_attn_device_status", "dx_attn_last_cuda_error", "dx_attn_launch_count",
     "dx_attn_enqueue_generation_static_scratch", "dx_attn_static_scratch_bytes", "dx_attn_append_context",
+    "dx_attn_append_context_cyclic",
     "dx_attn_selftest_wait_timeout",
 ]
 
@@ -136,6 +137,10 @@ def load_library() -> ctypes.CDLL:
     lib.dx_attn_append_context.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                            ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
                                            ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
+    lib.dx_attn_append_context_cyclic.restype = ctypes.c_int
+    lib.dx_attn_append_context_cyclic.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                                  ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                                  ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
     lib.dx_attn_validate.restype = ctypes.c_int
     lib.dx_attn_validate.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
                                      ctypes.c_int32, ctypes.c_void_p, ctypes.c_size_t]
@@ -357,10 +362,12 @@ class GPTAttentionPlugin:
     # --- reference: invokeTranspose4dBatchMajor (context-phase KV write) ---
     def append_context(self, k: torch.Tensor, v: torch.Tensor, sequence_length: torch.Tensor,
                        kv_cache_block_pointers: torch.Tensor, kv_orig_quant_scale: Optional[torch.Tensor] = None,
-                       *, attention_window_size: Optional[int] = None,
+                       *, attention_window_size: Optional[int] = None, sink_token_length: int = 0,
                        stream: Optional[torch.cuda.Stream] = None) -> None:
         """k, v: T [B, Hkv, seq_len, Dh] (device, contiguous); stores tokens < sequence_length[b] of every
-        sequence into the paged cache, quantising on write.  Asynchronous."""
+        sequence into the paged cache, quantising on write.  attention_window_size shorter than a sequence: the
+        cache is cyclic and keeps the last attention_window_size tokens (sink tokens keep their slots).
+        Asynchronous."""
         if not (k.is_cuda and v.is_cuda and k.is_contiguous() and v.is_contiguous()):
             raise DecodeAttnError(DX_ERR_BAD_ARG, "append_context needs contiguous device tensors")
         B, Hkv, L, Dh = k.shape
@@ -369,11 +376,12 @@ class GPTAttentionPlugin:
         M = kv_cache_block_pointers.shape[-1]
         window = attention_window_size if attention_window_size is not None else M * self.tokens_per_block
         s = stream if stream is not None else torch.cuda.current_stream(k.device)
-        st = self.lib.dx_attn_append_context(self._h, k.data_ptr(), v.data_ptr(), sequence_length.data_ptr(), B, L,
-                                             window, kv_cache_block_pointers.data_ptr(), M,
-                                             _ptr(kv_orig_quant_scale), ctypes.c_void_p(s.cuda_stream))
+        st = self.lib.dx_attn_append_context_cyclic(self._h, k.data_ptr(), v.data_ptr(), sequence_length.data_ptr(),
+                                                    B, L, window, sink_token_length,
+                                                    kv_cache_block_pointers.data_ptr(), M,
+                                                    _ptr(kv_orig_quant_scale), ctypes.c_void_p(s.cuda_stream))
         if st != DX_OK:
-            raise DecodeAttnError(st, "dx_attn_append_context")
+            raise DecodeAttnError(st, "dx_attn_append_context_cyclic")
 
     def bind_generation(self, qkv: torch.Tensor, sequence_length: torch.Tensor,
                         host_past_key_value_lengths: torch.Tensor, kv_cache_block_pointers: torch.Tensor,

@@ -146,8 +146,32 @@ def medusa_masks():
     (HERE / "medusa_mask_golden.json").write_text(json.dumps(out))
 
 
+def kv_slots():
+    """Slot of every token under the reference's KVBlockArray (kvCacheUtils.h:71-117), from the reference header
+    itself compiled as a host program (make -C oracle kv_slots REF=...)."""
+    import subprocess
+    exe = ROOT / "oracle" / "_ref" / "ref_kv_slots"
+    subprocess.run(["make", "-C", str(ROOT / "oracle"), "kv_slots", f"REF={REF}"], check=True, stdout=subprocess.DEVNULL)
+    cases = [  # tokens_per_block, max_blocks_per_seq, attention_window, sink_tokens, tokens listed
+        (64, 8, 512, 0, 1400),     # plain cyclic window, table exactly as long as the window
+        (64, 9, 512, 0, 1400),     # spare block: window + tokens_per_block slots cycle
+        (64, 8, 448, 64, 1200),    # whole sink block, no spare block... (8 - 1) * 64 >= 448: spare block
+        (64, 7, 448, 64, 1200),    # whole sink block, no spare block
+        (64, 8, 300, 4, 900),      # sink tokens end inside a block: bubble of 60
+        (16, 8, 100, 5, 400),      # bubble of 11, spare block or not by the constructor's rule
+        (128, 4, 384, 0, 1000),
+        (32, 40, 1024, 32, 3000),
+    ]
+    out = []
+    for c in cases:
+        res = subprocess.run([str(exe)] + [str(x) for x in c], check=True, capture_output=True, text=True)
+        out.append(json.loads(res.stdout))
+    (HERE / "kv_slot_golden.json").write_text(json.dumps(out))
+
+
 if __name__ == "__main__":
     page_tables()
     quant_vectors()
     medusa_masks()
+    kv_slots()
     print("written:", [p.name for p in HERE.iterdir()])

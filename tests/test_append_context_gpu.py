@@ -49,6 +49,64 @@ def test_append_matches_oracle_bit_exact(pkg, dtype, cache, dh, tpb):
         plugin.close()
 
 
+@pytest.mark.parametrize("cache", ["none", "int8", "fp8"])
+@pytest.mark.parametrize("tpb,blocks,window,sink", [
+    (64, 8, 512, 0),    # table exactly as long as the window: slot = t % 512
+    (64, 9, 512, 0),    # spare block: 576 slots cycle
+    (64, 7, 448, 64),   # one whole sink block kept in place, 384 slots cycle behind it
+    (64, 8, 300, 4),    # sink tokens end inside a block: the rest of that block stays unused
+    (16, 8, 100, 5),
+])
+def test_append_with_a_window_shorter_than_the_prompt(pkg, cache, tpb, blocks, window, sink):
+    """Cyclic cache in the context phase (unfusedAttentionKernels.cu:1591-1600 with the slots of
+    kvCacheUtils.h:109-117): only the last `window` tokens are stored, at their cyclic slots; bit-exact against the
+    oracle, whose slot arithmetic is pinned against the reference header (test_oracle_golden)."""
+    wl = workloads
+    cfg = wl.DecodeConfig("ctxw", 4, 6, 3, 128, torch.bfloat16, cache, tpb, 1, blocks * tpb, True, 19)
+    # shorter than the window, exactly the window, a little longer, several times around
+    lens = torch.tensor([max(1, window // 3), window, window + tpb + 3, 3 * window + 7], dtype=torch.int32)
+    w = wl.build_workload(cfg, "cpu", lengths=torch.full((4,), blocks * tpb - 1, dtype=torch.int32))
+    g = torch.Generator().manual_seed(23)
+    L = int(lens.max())
+    k = torch.randn(cfg.batch, cfg.num_kv_heads, L, cfg.head_size, generator=g).to(cfg.dtype)
+    v = torch.randn(cfg.batch, cfg.num_kv_heads, L, cfg.head_size, generator=g).to(cfg.dtype)
+    pool_ref = torch.zeros_like(w.pool)
+    oracle.append_context_reference(k, v, lens, pool_ref, w.offset_table, tokens_per_block=tpb,
+                                    cache_mode=CACHE_MODE[cache], kv_scale_orig_quant=w.scale_orig_quant,
+                                    attention_window_size=window, sink_token_length=sink)
+    wd = wl.to_device(w, "cuda:0")
+    wd.pool.zero_()
+    plugin = wl.make_plugin(cfg, 0)
+    try:
+        plugin.append_context(k.cuda(), v.cuda(), lens.cuda(), wd.kv_cache_block_pointers, wd.kv_orig_quant_scale,
+                              attention_window_size=window, sink_token_length=sink)
+        torch.cuda.synchronize()
+        assert torch.equal(wd.pool.cpu(), pool_ref)
+    finally:
+        plugin.close()
+
+
+def test_append_refuses_a_table_shorter_than_the_cycle(pkg):
+    wl = workloads
+    cfg = wl.DecodeConfig("ctxw", 1, 4, 2, 128, torch.bfloat16, "fp8", 64, 1, 256, True, 19)
+    w = wl.to_device(wl.build_workload(cfg, "cpu", lengths=torch.tensor([255], dtype=torch.int32)), "cuda:0")
+    k = torch.zeros(1, 2, 600, 128, dtype=torch.bfloat16, device="cuda:0")
+    lens = torch.tensor([600], dtype=torch.int32, device="cuda:0")
+    plugin = wl.make_plugin(cfg, 0)
+    try:
+        table = w.kv_cache_block_pointers  # 4 blocks = 256 slots
+        with pytest.raises(pkg.DecodeAttnError) as e:  # a window of 512 tokens cannot cycle in 256 slots
+            plugin.append_context(k, k, lens, table, w.kv_orig_quant_scale, attention_window_size=512)
+        assert e.value.status == pkg.plugin.DX_ERR_BAD_ARG
+        with pytest.raises(pkg.DecodeAttnError) as e:  # the sink tokens must leave room in the window
+            plugin.append_context(k, k, lens, table, w.kv_orig_quant_scale, attention_window_size=128, sink_token_length=128)
+        assert e.value.status == pkg.plugin.DX_ERR_BAD_ARG
+        plugin.append_context(k, k, lens, table, w.kv_orig_quant_scale, attention_window_size=256)  # fits exactly
+        torch.cuda.synchronize()
+    finally:
+        plugin.close()
+
+
 def test_append_known_answer_inputs(pkg):
     """Inputs of the reference known-answer test (srand(42), values in [0, 10], scale 0.1;
     cpp/tests/runtime/transposeKVKernelTest.cpp:152-225) through the product writer, fp16 activations:

@@ -173,3 +173,22 @@ def test_tp_shards_concatenate_to_the_full_result(pkg):
             o, _ = oracle_step(ws)
             parts.append(o.view(cfg.batch, cfg.num_heads // tp, cfg.head_size))
         assert torch.equal(torch.cat(parts, 1), full)
+
+
+def test_kv_slot_arithmetic_matches_the_reference_header():
+    """oracle.kv_slot_of_token against slots printed by the reference's own KVBlockArray::getKVTokenIdx
+    (kvCacheUtils.h, compiled from the reference tree by oracle/ref_kv_slots.cu; tests/golden/make_golden.py):
+    plain cyclic windows, tables with the spare block, whole sink blocks, sink tokens that end inside a block."""
+    import json
+    cases = json.loads((GOLDEN / "kv_slot_golden.json").read_text())
+    assert len(cases) >= 8
+    seen_bubble = seen_spare = False
+    for c in cases:
+        seen_bubble |= c["bubble_len"] > 0
+        seen_spare |= bool(c["one_more_block"])
+        got = [oracle.kv_slot_of_token(t, tokens_per_block=c["tokens_per_block"],
+                                       max_blocks_per_seq=c["max_blocks_per_seq"],
+                                       attention_window_size=c["attention_window"],
+                                       sink_token_length=c["sink_tokens"]) for t in range(len(c["slots"]))]
+        assert got == c["slots"], c
+    assert seen_bubble and seen_spare

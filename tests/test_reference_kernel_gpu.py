@@ -76,16 +76,20 @@ def test_oracle_matches_reference_mmha_kernel(pkg, dtype, dh, cache, heads):
 
 
 @pytest.mark.skipif(not LIB.exists(), reason="oracle/_ref/libref_mmha.so not built (needs the reference tree)")
-@pytest.mark.parametrize("name,tp,tiles", [("c4", 8, 0), ("c2", 1, 0), ("c5", 8, 8)])
-def test_report_reference_kernel_time(pkg, name, tp, tiles):
+@pytest.mark.parametrize("name,tp,tiles,batch", [
+    ("c4", 8, 0, None), ("c2", 1, 0, 16), ("c5", 8, 8, None),
+    # the full single-GPU sizes the bench quotes (the pools are larger than L2)
+    ("c4", 1, 0, None), ("c2", 1, 0, None), ("c5", 1, 8, None),
+])
+def test_report_reference_kernel_time(pkg, name, tp, tiles, batch):
     """Times the reference MMHA kernel (recompiled for sm_100a) beside this library on the same resident
     inputs and records both in ref_kernel_times.jsonl of the report directory.  Asserts only agreement of results."""
     import json
     import os
     wl = workloads
     cfg = wl.shard_config(wl.CONFIGS[name], tp)
-    if name == "c2":
-        cfg = wl.scaled_config(cfg, batch=16)
+    if batch is not None:
+        cfg = wl.scaled_config(cfg, batch=batch)
     w = wl.build_workload(cfg, "cuda:0")
     plugin = wl.make_plugin(cfg, 0)
     ours = wl.run_step(plugin, w)
