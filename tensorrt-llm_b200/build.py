@@ -18,7 +18,7 @@ BUILD_DIR = PKG_DIR / "build"
 LIB_PATH = PKG_DIR / "libdecode_attn.so"
 
 SOURCES = ["dx_attn.cu", "dx_mha_inst.cu", "dx_gqa_inst.cu", "dx_wide_inst.cu", "dx_tok_inst.cu", "dx_tokws_inst.cu",
-           "dx_general_inst.cu"]
+           "dx_general_inst.cu", "dx_general_more_inst.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

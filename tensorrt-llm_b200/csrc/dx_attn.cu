@@ -31,7 +31,8 @@ enum KernelKind : int
     KIND_GQA = 1, // tensor-core kernel, one CTA per kv head (x 16-head slice)
     KIND_TOK = 3, // tcgen05 kernel, token-major, one CTA per kv head, FP8 cache, Dh 128, up to 16 heads per kv head
     KIND_WIDE = 2, // tcgen05 kernel, one CTA per kv head (x 128-head slice), FP8 cache, more than 16 heads per kv head
-    KIND_TOKWS = 4 // persistent warp-specialised tcgen05 kernel, token-major, one CTA per SM, two-level stream-K ranges
+    KIND_TOKWS = 4, // persistent warp-specialised tcgen05 kernel, token-major, one CTA per SM, two-level stream-K ranges
+    KIND_GENERAL = 5 // feature-complete kernels (reported by the plan queries for head sizes other than 64 / 128)
 };
 
 struct Plan
@@ -93,6 +94,7 @@ struct dx_attn
     double wave_slack_from = 2.0; // waves beyond which 5 % of a wave of extra CTAs is not counted as a further wave
     bool prep = false; // bias / rotary embedding configured: QKV is pre-processed into the workspace
     int32_t* status_dev = nullptr;
+    bool general_only = false; // head size without streaming kernels: every step runs on the feature-complete kernels
     int last_cuda_error = 0;
     std::atomic<int64_t> launches{0};
     // staging for the host-buffer entry point
@@ -764,8 +766,17 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
         return DX_ERR_BAD_ARG;
     if (!(c.q_scaling > 0.f) || c.tokens_per_block <= 0 || (c.tokens_per_block & (c.tokens_per_block - 1)))
         return DX_ERR_BAD_ARG;
-    if (c.head_size != 64 && c.head_size != 128)
-        return DX_ERR_UNSUPPORTED;
+    // Head sizes of the reference's MMHA switch (decoderMaskedMultiheadAttention.cu:68-85).  64 and 128 run on the
+    // streaming kernels; the others on the feature-complete kernels (one CTA per sequence and q head).
+    const bool streaming_dh = c.head_size == 64 || c.head_size == 128;
+    {
+        static const int sizes[] = {32, 48, 64, 80, 96, 104, 112, 128, 144, 160, 192, 224, 256};
+        bool known = false;
+        for (int v : sizes)
+            known |= v == c.head_size;
+        if (!known)
+            return DX_ERR_UNSUPPORTED;
+    }
     if (c.type_id != DX_DTYPE_FP16 && c.type_id != DX_DTYPE_BF16)
         return DX_ERR_UNSUPPORTED;
     if (!c.paged_kv_cache || c.tokens_per_block < 16 || c.tokens_per_block > 256)
@@ -822,7 +833,15 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
             for (int h16 = 0; h16 < 2; ++h16)
                 h->k_gqa[h16] = gqa_kernel_info(c.type_id, h->cache_kind, c.head_size, h16 != 0);
         }
-        if (!h->k_mha.fn || !h->k_merge.fn)
+        if (!streaming_dh)
+        {
+            // (a cache row that is not a multiple of 16 bytes - head size 104 in an 8-bit cache - has no kernel)
+            if (!h->k_general.attn)
+                st = DX_ERR_UNSUPPORTED;
+            h->k_append.fn = h->k_general.context_append;
+            h->general_only = true;
+        }
+        else if (!h->k_mha.fn || !h->k_merge.fn)
             st = DX_ERR_UNSUPPORTED;
     }
     if (st == DX_OK)
@@ -917,7 +936,7 @@ size_t dx_attn_workspace_size(const dx_attn_t* h, int32_t batch, int32_t max_pas
 {
     if (!h || batch <= 0 || max_past_len < 0)
         return 0;
-    return prep_bytes(h, batch) + workspace_bound(h, batch, max_past_len);
+    return prep_bytes(h, batch) + (h->general_only ? 0 : workspace_bound(h, batch, max_past_len));
 }
 
 int dx_attn_plan(const dx_attn_t* h, int32_t batch, int32_t max_past_len, int32_t* num_partitions,
@@ -925,6 +944,16 @@ int dx_attn_plan(const dx_attn_t* h, int32_t batch, int32_t max_past_len, int32_
 {
     if (!h || batch <= 0 || max_past_len < 0)
         return DX_ERR_BAD_ARG;
+    if (h->general_only)
+    {
+        if (num_partitions)
+            *num_partitions = 1;
+        if (tokens_per_partition)
+            *tokens_per_partition = max_past_len + 1;
+        if (kernel_kind)
+            *kernel_kind = KIND_GENERAL;
+        return DX_OK;
+    }
     const Plan p = make_plan(h, batch, max_past_len);
     if (num_partitions)
         *num_partitions = p.nsplit;
@@ -947,6 +976,8 @@ int dx_attn_plan_lengths(const dx_attn_t* h, const int32_t* host_past_key_value_
             return DX_ERR_BAD_ARG;
         max_past = std::max(max_past, host_past_key_value_lengths[i]);
     }
+    if (h->general_only)
+        return dx_attn_plan(h, batch, max_past, num_partitions, tokens_per_partition, kernel_kind);
     int rows_per_seq = 1;
     Plan p = plan_shape(h, batch, rows_per_seq);
     SkSchedule sk;
@@ -1023,7 +1054,7 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     if (p.input_seq_length > 1)
         return enqueue_multi_token(h, p, max_past, cuda_stream);
     // Beam search, a window shorter than some sequence, sink tokens and ALiBi go to the feature-complete kernel.
-    const bool general = p.beam_width > 1 || p.sink_token_length > 0 || alibi || relative
+    const bool general = h->general_only || p.beam_width > 1 || p.sink_token_length > 0 || alibi || relative
         || p.cyclic_attention_window_size < max_past + 1 || p.max_attention_window < max_past + 1;
     if (general)
         return enqueue_general(h, p, max_past, cuda_stream);

@@ -12,7 +12,7 @@ static GeneralKernels mk()
     k.attn = reinterpret_cast<const void*>(&general_decode_kernel<T, CACHE, DH>);
     k.append = reinterpret_cast<const void*>(&kv_append_token_kernel<T, CACHE, DH>);
     k.multi = reinterpret_cast<const void*>(&multi_token_decode_kernel<T, CACHE, DH>);
-    k.smem = (4 * MhaTraits<CACHE, DH>::TPW * (DH + 2)) * (int) sizeof(float);
+    k.smem = (4 * GenTraits<CACHE, DH>::TPW * (DH + 2)) * (int) sizeof(float);
     return k;
 }
 
@@ -36,6 +36,8 @@ static GeneralKernels by_cache_dh(int cache, int dh)
 
 GeneralKernels general_kernel_info(int dtype, int cache, int dh)
 {
+    if (dh != 64 && dh != 128)
+        return general_kernel_info_other_head_sizes(dtype, cache, dh);
     return dtype == 0 ? by_cache_dh<__half>(cache, dh) : by_cache_dh<__nv_bfloat16>(cache, dh);
 }
 } // namespace dx

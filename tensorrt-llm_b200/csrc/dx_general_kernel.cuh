@@ -18,15 +18,31 @@
 #pragma once
 
 #include "dx_common.cuh"
-#include "dx_mha_kernel.cuh" // MhaTraits lane mapping, dequant_vec, make_cache_vec
+#include "dx_mha_kernel.cuh" // dequant_vec, make_cache_vec
 
 namespace dx
 {
 
+// Lane mapping of the kernels in this file for any head size whose cache row is a multiple of 16 bytes (the
+// reference's MMHA head sizes, decoderMaskedMultiheadAttention.cu:68-85): a row takes CHUNKS 16-byte pieces; LPR, the
+// next power of two, lanes form the group that owns a row, of which the first CHUNKS are active (the others hold
+// zeros and take part in the shuffles only).  For Dh 64 / 128 every lane is active.
+template <int CACHE, int DH>
+struct GenTraits
+{
+    static constexpr int ECB = (CACHE == CACHE_T) ? 2 : 1; // bytes per cache element
+    static constexpr int ROW_BYTES = DH * ECB;
+    static constexpr int EPL = 16 / ECB;                   // elements per lane
+    static constexpr int CHUNKS = ROW_BYTES / 16;
+    static constexpr int LPR = CHUNKS <= 1 ? 1 : CHUNKS <= 2 ? 2 : CHUNKS <= 4 ? 4 : CHUNKS <= 8 ? 8 : CHUNKS <= 16 ? 16 : 32;
+    static constexpr int TPW = 32 / LPR;                   // rows one warp-wide load covers
+    static_assert(ROW_BYTES % 16 == 0 && CHUNKS <= 32, "cache rows are moved in 16-byte pieces");
+};
+
 template <typename T, int CACHE, int DH>
 __global__ void __launch_bounds__(128) general_decode_kernel(const GeneralArgs a)
 {
-    using Tr = MhaTraits<CACHE, DH>;
+    using Tr = GenTraits<CACHE, DH>;
     constexpr int LPR = Tr::LPR, TPW = Tr::TPW, EPL = Tr::EPL, ROW_BYTES = Tr::ROW_BYTES;
     constexpr int U = 2;              // token passes in flight per warp
     constexpr int NSTATE = 4 * TPW;   // lane groups of the CTA, each with its own running softmax
@@ -35,6 +51,7 @@ __global__ void __launch_bounds__(128) general_decode_kernel(const GeneralArgs a
     const int h = blockIdx.x, bb = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane / LPR, sl = lane % LPR;
+    const bool active = sl < Tr::CHUNKS; // (always true for Dh 64 / 128)
     const int G = a.num_heads / a.num_kv_heads;
     const int hk = h / G;
     const int tpb_log2 = a.tpb_log2, tpb_mask = (1 << tpb_log2) - 1;
@@ -85,7 +102,7 @@ __global__ void __launch_bounds__(128) general_decode_kernel(const GeneralArgs a
 #pragma unroll
         for (int i = 0; i < EPL; i += 2)
         {
-            const float2 v = TypeOps<T>::unpack2(*reinterpret_cast<const uint32_t*>(qp + i));
+            const float2 v = active ? TypeOps<T>::unpack2(*reinterpret_cast<const uint32_t*>(qp + i)) : make_float2(0.f, 0.f);
             q[i] = v.x;
             q[i + 1] = v.y;
         }
@@ -135,8 +152,12 @@ __global__ void __launch_bounds__(128) general_decode_kernel(const GeneralArgs a
             const int seq = seq0 + ((beams && s >= ctx0) ? __ldg(indir + s) : 0);
             const int64_t* rowp = a.block_ptrs + (int64_t) seq * 2 * a.max_blocks_per_seq + (s >> tpb_log2);
             const size_t off = head_off + (size_t) (s & tpb_mask) * ROW_BYTES;
-            kraw[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(__ldg(rowp)) + off);
-            vraw[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(__ldg(rowp + a.max_blocks_per_seq)) + off);
+            kraw[u] = vraw[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (active)
+            {
+                kraw[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(__ldg(rowp)) + off);
+                vraw[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(__ldg(rowp + a.max_blocks_per_seq)) + off);
+            }
         }
 #pragma unroll
         for (int u = 0; u < U; ++u)
@@ -149,8 +170,12 @@ __global__ void __launch_bounds__(128) general_decode_kernel(const GeneralArgs a
         const T sc_t = TypeOps<T>::from_float(sc_f);
         const T* kp = qkv_b + (size_t) (a.num_heads + hk) * DH + sl * EPL;
         const T* vp = qkv_b + (size_t) (a.num_heads + a.num_kv_heads + hk) * DH + sl * EPL;
-        const uint4 kq = make_cache_vec<T, CACHE, EPL>(kp, sc_f, sc_t);
-        const uint4 vq = make_cache_vec<T, CACHE, EPL>(vp, sc_f, sc_t);
+        uint4 kq = make_uint4(0u, 0u, 0u, 0u), vq = kq;
+        if (active)
+        {
+            kq = make_cache_vec<T, CACHE, EPL>(kp, sc_f, sc_t);
+            vq = make_cache_vec<T, CACHE, EPL>(vp, sc_f, sc_t);
+        }
         if (warp == 0)
             accumulate(kq, vq, rel_bias_of(tlength), sub == 0);
     }
@@ -161,9 +186,12 @@ __global__ void __launch_bounds__(128) general_decode_kernel(const GeneralArgs a
     float* st_m = st_o + NSTATE * DH;                // [NSTATE]
     float* st_l = st_m + NSTATE;                     // [NSTATE]
     const int state = warp * TPW + sub;
+    if (active)
+    {
 #pragma unroll
-    for (int i = 0; i < EPL; ++i)
-        st_o[state * DH + sl * EPL + i] = o[i];
+        for (int i = 0; i < EPL; ++i)
+            st_o[state * DH + sl * EPL + i] = o[i];
+    }
     if (sl == 0)
     {
         st_m[state] = m;
@@ -192,10 +220,10 @@ __global__ void __launch_bounds__(128) general_decode_kernel(const GeneralArgs a
 template <typename T, int CACHE, int DH>
 __global__ void __launch_bounds__(32) kv_append_token_kernel(const GeneralArgs a)
 {
-    using Tr = MhaTraits<CACHE, DH>;
-    constexpr int LPR = Tr::LPR, EPL = Tr::EPL, ROW_BYTES = Tr::ROW_BYTES;
+    using Tr = GenTraits<CACHE, DH>;
+    constexpr int EPL = Tr::EPL, ROW_BYTES = Tr::ROW_BYTES;
     const int hk = blockIdx.x, bb = blockIdx.y, lane = threadIdx.x;
-    if (lane >= LPR)
+    if (lane >= Tr::CHUNKS)
         return;
     const int seq = bb / a.q_len, tok = bb % a.q_len;
     const int tlength = a.seq_len[seq] - a.q_len + tok;
@@ -222,7 +250,7 @@ __global__ void __launch_bounds__(32) kv_append_token_kernel(const GeneralArgs a
 template <typename T, int CACHE, int DH>
 __global__ void __launch_bounds__(128) multi_token_decode_kernel(const GeneralArgs a)
 {
-    using Tr = MhaTraits<CACHE, DH>;
+    using Tr = GenTraits<CACHE, DH>;
     constexpr int LPR = Tr::LPR, TPW = Tr::TPW, EPL = Tr::EPL, ROW_BYTES = Tr::ROW_BYTES;
     constexpr int U = 2;
     constexpr int NSTATE = 4 * TPW;
@@ -231,6 +259,7 @@ __global__ void __launch_bounds__(128) multi_token_decode_kernel(const GeneralAr
     const int seq = bb / a.q_len, tok = bb % a.q_len;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane / LPR, sl = lane % LPR;
+    const bool active = sl < Tr::CHUNKS; // (always true for Dh 64 / 128)
     const int G = a.num_heads / a.num_kv_heads;
     const int hk = h / G;
     const int tpb_log2 = a.tpb_log2, tpb_mask = (1 << tpb_log2) - 1;
@@ -248,7 +277,7 @@ __global__ void __launch_bounds__(128) multi_token_decode_kernel(const GeneralAr
 #pragma unroll
         for (int i = 0; i < EPL; i += 2)
         {
-            const float2 v = TypeOps<T>::unpack2(*reinterpret_cast<const uint32_t*>(qp + i));
+            const float2 v = active ? TypeOps<T>::unpack2(*reinterpret_cast<const uint32_t*>(qp + i)) : make_float2(0.f, 0.f);
             q[i] = v.x;
             q[i + 1] = v.y;
         }
@@ -275,8 +304,12 @@ __global__ void __launch_bounds__(128) multi_token_decode_kernel(const GeneralAr
                 valid[u] = (__ldg(mask_row + ((slot - past) >> 5)) >> ((slot - past) & 31)) & 1;
             const int64_t* rowp = krow + (s >> tpb_log2);
             const size_t off = head_off + (size_t) (s & tpb_mask) * ROW_BYTES;
-            kraw[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(__ldg(rowp)) + off);
-            vraw[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(__ldg(rowp + a.max_blocks_per_seq)) + off);
+            kraw[u] = vraw[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (active)
+            {
+                kraw[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(__ldg(rowp)) + off);
+                vraw[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(__ldg(rowp + a.max_blocks_per_seq)) + off);
+            }
         }
 #pragma unroll
         for (int u = 0; u < U; ++u)
@@ -311,9 +344,12 @@ __global__ void __launch_bounds__(128) multi_token_decode_kernel(const GeneralAr
     float* st_m = st_o + NSTATE * DH;                // [NSTATE]
     float* st_l = st_m + NSTATE;                     // [NSTATE]
     const int state = warp * TPW + sub;
+    if (active)
+    {
 #pragma unroll
-    for (int i = 0; i < EPL; ++i)
-        st_o[state * DH + sl * EPL + i] = o[i];
+        for (int i = 0; i < EPL; ++i)
+            st_o[state * DH + sl * EPL + i] = o[i];
+    }
     if (sl == 0)
     {
         st_m[state] = m;

@@ -24,9 +24,12 @@ struct GeneralKernels
     const void* attn = nullptr;   // general_decode_kernel: grid (H, B), 128 threads, `smem` dynamic bytes
     const void* append = nullptr; // kv_append_token_kernel: grid (Hkv, B * q_len), 32 threads
     const void* multi = nullptr;  // multi_token_decode_kernel: grid (H, B * q_len), 128 threads, `smem` dynamic bytes
+    const void* context_append = nullptr; // kv_append_context_kernel (set for the head sizes other than 64 / 128)
     int smem = 0;
 };
 GeneralKernels general_kernel_info(int dtype, int cache, int dh);
+// head sizes 32, 48, 80, 96, 104, 112, 144, 160, 192, 224, 256; empty where a cache row is not a multiple of 16 bytes
+GeneralKernels general_kernel_info_other_head_sizes(int dtype, int cache, int dh);
 KernelInfo merge_kernel_info(int dtype, int dh);
 KernelInfo append_kernel_info(int dtype, int cache, int dh);
 } // namespace dx

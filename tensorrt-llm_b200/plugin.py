@@ -233,7 +233,7 @@ class GPTAttentionPlugin:
         if st != DX_OK:
             raise DecodeAttnError(st, "dx_attn_plan")
         kernel = {0: "mha_cuda_core", 1: "gqa_tensor_core", 2: "wide_group_tcgen05",
-                  3: "token_major_tcgen05", 4: "token_major_tcgen05_persistent"}.get(k.value, "?")
+                  3: "token_major_tcgen05", 4: "token_major_tcgen05_persistent", 5: "general_cuda_core"}.get(k.value, "?")
         if n.value < 0:  # stream-K launch: equal token ranges per CTA
             return {"num_partitions": 0, "tokens_per_partition": c.value, "kernel": kernel,
                     "stream_k_ctas": -n.value}
