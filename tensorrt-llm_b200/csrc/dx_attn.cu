@@ -784,6 +784,8 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
     const int q = c.kv_cache_quant_mode & (DX_QUANT_INT8_KV_CACHE | DX_QUANT_FP8_KV_CACHE);
     if (q == (DX_QUANT_INT8_KV_CACHE | DX_QUANT_FP8_KV_CACHE))
         return DX_ERR_BAD_ARG;
+    if ((c.head_size * (q ? 1 : 2)) % 16 != 0)
+        return DX_ERR_UNSUPPORTED; // cache rows are moved in 16-byte pieces (head size 104 needs a 16-bit cache)
 
     dx_attn* h = new (std::nothrow) dx_attn;
     if (!h)

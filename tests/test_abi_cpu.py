@@ -68,7 +68,7 @@ def test_argument_checks_happen_before_any_cuda_call(pkg):
     lib = pkg.load_library()
     P = pkg.plugin
     h = ctypes.c_void_p()
-    bad = [dict(head_size=80), dict(num_heads=7, num_kv_heads=2), dict(tokens_per_block=48), dict(type_id=5),
+    bad = [dict(head_size=72), dict(head_size=104, kv_cache_quant_mode=1 << 6), dict(num_heads=7, num_kv_heads=2), dict(tokens_per_block=48), dict(type_id=5),
            dict(tokens_per_block=8), dict(q_scaling=0.0), dict(kv_cache_quant_mode=(1 << 6) | (1 << 7)),
            dict(paged_kv_cache=0)]
     for kw in bad:
