@@ -476,7 +476,7 @@ def run_own_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--config", default="c4", choices=["c1", "c2", "c3", "c4", "c5", "c4kv16"])
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
