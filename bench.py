@@ -51,12 +51,12 @@ def measured_peak_gbs():
 # summarised under profiles/ (gqa_decode_fp8_c4.md, gqa_decode_int8_c5.md, mha_int8_decode_c2.md,
 # wide_decode_fp8_c3.md, gqa_decode_fp8_c4_tp8_shard.md, gqa16_decode_bf16_c4kv16.md).  Captured at full size: each fits the capture rule.
 PROFILED_TRAFFIC = {
-    "c4_llama2_70b_gqa_fp8_tp1": 805277440,
-    "c5_mixtral_long_gqa_int8_tp1": 376647680,
-    "c2_llama2_7b_mha_int8_tp1": 813736448,
-    "c3_falcon_7b_mqa_fp8_tp1": 20090880,
-    "c4_llama2_70b_gqa_fp8_tp8": 103483904,
-    "c4kv16_llama2_70b_gqa_bf16_cache_tp1": 798216960,
+    "c4_llama2_70b_gqa_fp8_tp1": 805493504,
+    "c5_mixtral_long_gqa_int8_tp1": 379214080,
+    "c2_llama2_7b_mha_int8_tp1": 813841664,
+    "c3_falcon_7b_mqa_fp8_tp1": 20091392,
+    "c4_llama2_70b_gqa_fp8_tp8": 103479808,
+    "c4kv16_llama2_70b_gqa_bf16_cache_tp1": 799406592,
 }
 
 

@@ -311,6 +311,17 @@ int dx_attn_device_status(dx_attn_t* handle);
  * polls (1 .. 2^20), on a barrier nothing ever arrives on, and then records a time-out exactly as the attention
  * kernels would.  dx_attn_device_status() returns DX_ERR_TIMEOUT afterwards.  Nothing hangs or faults. */
 int dx_attn_selftest_wait_timeout(dx_attn_t* handle, int32_t poll_limit, void* cuda_stream);
+
+/* Bounds-checked build (compiled with -DDECODE_ATTN_BOUNDS_CHECK, libdecode_attn_checked.so; a debugging aid with no
+ * reference counterpart - the reference relies on compute-sanitizer runs): every block-table look-up of the kernels
+ * checks that the block index lies inside the table row and that the pointer is non-null, 16-byte aligned and, once
+ * a pool range is registered, inside that pool; the first violation is recorded (dx_attn_device_status() returns
+ * DX_ERR_BOUNDS) and the access goes to a spare block the handle owns, so nothing outside the caller's memory is
+ * read or written.  dx_build_has_bounds_check() tells which build is loaded; dx_attn_set_pool_range() registers
+ * [pool, pool + pool_bytes) as the only memory cache blocks may lie in (NULL, 0: no range; the regular build
+ * stores it and ignores it). */
+int dx_build_has_bounds_check(void);
+int dx_attn_set_pool_range(dx_attn_t* handle, const void* pool, size_t pool_bytes);
 /* Last cudaError_t seen by this handle (0 if none). */
 int dx_attn_last_cuda_error(const dx_attn_t* handle);
 /* Kernels launched by this handle since creation (for launch accounting in benchmarks). */

@@ -16,6 +16,8 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 BUILD_DIR = PKG_DIR / "build"
 LIB_PATH = PKG_DIR / "libdecode_attn.so"
+CHECKED_BUILD_DIR = PKG_DIR / "build_checked"
+CHECKED_LIB_PATH = PKG_DIR / "libdecode_attn_checked.so"
 
 SOURCES = ["dx_attn.cu", "dx_mha_inst.cu", "dx_gqa_inst.cu", "dx_wide_inst.cu", "dx_tok_inst.cu", "dx_tokws_inst.cu",
            "dx_general_inst.cu", "dx_general_more_inst.cu"]
@@ -41,33 +43,39 @@ def _newest_dep_mtime() -> float:
     return max(p.stat().st_mtime for p in deps)
 
 
-def _compile(src: str, force: bool) -> Path:
-    obj = BUILD_DIR / (Path(src).stem + ".o")
+def _compile(src: str, force: bool, build_dir: Path, extra: list) -> Path:
+    obj = build_dir / (Path(src).stem + ".o")
     srcp = CSRC / src
     if not force and obj.exists() and obj.stat().st_mtime >= max(srcp.stat().st_mtime, _newest_dep_mtime()):
         return obj
-    cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(srcp), "-o", str(obj)]
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-c", str(srcp), "-o", str(obj)]
     res = subprocess.run(cmd, capture_output=True, text=True)
-    (BUILD_DIR / (Path(src).stem + ".ptxas.log")).write_text(res.stderr)
+    (build_dir / (Path(src).stem + ".ptxas.log")).write_text(res.stderr)
     if res.returncode != 0:
         sys.stderr.write(res.stderr)
         raise RuntimeError(f"nvcc failed for {src}")
     return obj
 
 
-def build(force: bool = False) -> Path:
-    BUILD_DIR.mkdir(exist_ok=True)
+def build(force: bool = False, checked: bool = False) -> Path:
+    """checked: the bounds-checked variant (-DDECODE_ATTN_BOUNDS_CHECK, libdecode_attn_checked.so): every block-table
+    look-up of the kernels validates index and pointer, records the first violation in the status word and redirects
+    the access to a spare block.  A debugging build; the regular library has none of it."""
+    build_dir = CHECKED_BUILD_DIR if checked else BUILD_DIR
+    lib_path = CHECKED_LIB_PATH if checked else LIB_PATH
+    extra = ["-DDECODE_ATTN_BOUNDS_CHECK"] if checked else []
+    build_dir.mkdir(exist_ok=True)
     with ThreadPoolExecutor(max_workers=len(SOURCES)) as ex:
-        objs = list(ex.map(lambda s: _compile(s, force), SOURCES))
-    if force or not LIB_PATH.exists() or any(o.stat().st_mtime > LIB_PATH.stat().st_mtime for o in objs):
-        cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", str(LIB_PATH)]
+        objs = list(ex.map(lambda s: _compile(s, force, build_dir, extra), SOURCES))
+    if force or not lib_path.exists() or any(o.stat().st_mtime > lib_path.stat().st_mtime for o in objs):
+        cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", str(lib_path)]
         cmd += [str(o) for o in objs]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             sys.stderr.write(res.stderr)
             raise RuntimeError("link failed")
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv))
+    print(build(force="--force" in sys.argv, checked="--checked" in sys.argv))

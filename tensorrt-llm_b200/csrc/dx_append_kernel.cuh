@@ -37,6 +37,8 @@ struct AppendArgs
     int32_t sink;
     int32_t bubble;
     int32_t cyclic_len;
+    int32_t* status; // device status word (0 ok)
+    TableGuard guard;
 };
 
 template <typename T, int CACHE, int DH>
@@ -73,8 +75,8 @@ __global__ void __launch_bounds__(256) kv_append_context_kernel(const AppendArgs
     const int64_t* vrow = krow + a.max_blocks_per_seq;
     const int tpb_mask = (1 << a.tpb_log2) - 1;
     const size_t off = ((size_t) h * ((size_t) 1 << a.tpb_log2) + (slot & tpb_mask)) * (DH * ECB) + part * 16;
-    char* kb = reinterpret_cast<char*>(__ldg(krow + (slot >> a.tpb_log2))) + off;
-    char* vb = reinterpret_cast<char*>(__ldg(vrow + (slot >> a.tpb_log2))) + off;
+    char* kb = reinterpret_cast<char*>(table_entry(krow, slot >> a.tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
+    char* vb = reinterpret_cast<char*>(table_entry(vrow, slot >> a.tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
     *reinterpret_cast<uint4*>(kb) = kq;
     *reinterpret_cast<uint4*>(vb) = vq;
 }

@@ -94,6 +94,7 @@ struct dx_attn
     double wave_slack_from = 2.0; // waves beyond which 5 % of a wave of extra CTAs is not counted as a further wave
     bool prep = false; // bias / rotary embedding configured: QKV is pre-processed into the workspace
     int32_t* status_dev = nullptr;
+    TableGuard guard{}; // bounds-checked build: spare block and registered pool range (all zero otherwise)
     bool general_only = false; // head size without streaming kernels: every step runs on the feature-complete kernels
     int last_cuda_error = 0;
     std::atomic<int64_t> launches{0};
@@ -627,6 +628,8 @@ int enqueue_general(dx_attn* h, const dx_attn_generation_params& p, int max_past
     g.cyclic_len = cyclic_len;
     g.sink = sink;
     g.softmax_scale_log2 = 1.4426950408889634f / (sqrtf((float) c.head_size) * c.q_scaling);
+    g.status = h->status_dev;
+    g.guard = h->guard;
     g.q_len = 1;
     void* args[] = {&g};
     st = check_cuda(h, cudaLaunchKernel(h->k_general.attn, dim3(c.num_heads, nseq), dim3(128), args,
@@ -698,6 +701,8 @@ int enqueue_multi_token(dx_attn* h, const dx_attn_generation_params& p, int max_
     g.cyclic_len = p.max_blocks_per_sequence * c.tokens_per_block; // no wrap: slot = token index
     g.sink = 0;
     g.softmax_scale_log2 = 1.4426950408889634f / (sqrtf((float) c.head_size) * c.q_scaling);
+    g.status = h->status_dev;
+    g.guard = h->guard;
     g.q_len = Q;
     g.packed_mask = p.medusa_packed_mask;
     void* args[] = {&g};
@@ -903,6 +908,18 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
         st = check_cuda(h, cudaMalloc(reinterpret_cast<void**>(&h->status_dev), 512));
     if (st == DX_OK)
         st = check_cuda(h, cudaMemset(h->status_dev, 0, 512));
+#ifdef DECODE_ATTN_BOUNDS_CHECK
+    if (st == DX_OK)
+    {
+        // the spare block that out-of-bounds accesses are redirected to: one cache block of zeros
+        const size_t block_bytes = (size_t) c.num_kv_heads * c.tokens_per_block * c.head_size * (h->cache_kind == CACHE_T ? 2 : 1);
+        void* spare = nullptr;
+        st = check_cuda(h, cudaMalloc(&spare, block_bytes));
+        if (st == DX_OK)
+            st = check_cuda(h, cudaMemset(spare, 0, block_bytes));
+        h->guard.safe_block = reinterpret_cast<int64_t>(spare);
+    }
+#endif
     if (st != DX_OK)
     {
         if (h->status_dev)
@@ -921,6 +938,8 @@ void dx_attn_destroy(dx_attn_t* h)
     cudaSetDevice(h->cfg.device);
     if (h->status_dev)
         cudaFree(h->status_dev);
+    if (h->guard.safe_block)
+        cudaFree(reinterpret_cast<void*>(h->guard.safe_block));
     if (h->stage_dev)
         cudaFree(h->stage_dev);
     for (int i = 0; i < dx_attn::HOST_SLOTS; ++i)
@@ -1120,6 +1139,7 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     a.softmax_scale_log2 = 1.4426950408889634f / (sqrtf((float) c.head_size) * c.q_scaling);
     a.streamk = use_sk ? 1 : 0;
     a.tickets = (use_sk && plan.kind == KIND_TOKWS && sk.n2 > 0) ? h->status_dev + 16 : nullptr;
+    a.guard = h->guard;
 
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
     int st = check_cuda(h, cudaSetDevice(c.device));
@@ -1384,7 +1404,7 @@ int dx_attn_device_status(dx_attn_t* h)
         return DX_OK;
     if (v == STATUS_TIMEOUT)
         return DX_ERR_TIMEOUT;
-    return (v == STATUS_NO_BLOCKS || v == STATUS_PLAN_EXCEEDED) ? DX_ERR_BOUNDS : DX_ERR_CUDA;
+    return (v == STATUS_NO_BLOCKS || v == STATUS_PLAN_EXCEEDED || v == STATUS_BAD_TABLE) ? DX_ERR_BOUNDS : DX_ERR_CUDA;
 }
 
 int dx_kv_cache_step(dx_attn_t* h, int32_t* sequence_lengths, int64_t* block_pointers, int32_t num_requests,
@@ -1504,6 +1524,8 @@ int dx_attn_append_context_cyclic(dx_attn_t* h, const void* k_src, const void* v
     a.src_seq_len = seq_len;
     a.max_blocks_per_seq = max_blocks_per_sequence;
     a.tpb_log2 = h->tpb_log2;
+    a.status = h->status_dev;
+    a.guard = h->guard;
     a.window = attention_window_size;
     a.sink = sink_token_length;
     a.bubble = bubble;
@@ -1519,6 +1541,28 @@ int dx_attn_append_context_cyclic(dx_attn_t* h, const void* k_src, const void* v
     if (st == DX_OK)
         h->launches.fetch_add(1);
     return st;
+}
+
+int dx_build_has_bounds_check(void)
+{
+#ifdef DECODE_ATTN_BOUNDS_CHECK
+    return 1;
+#else
+    return 0;
+#endif
+}
+
+int dx_attn_set_pool_range(dx_attn_t* h, const void* pool, size_t pool_bytes)
+{
+    if (!h || (pool == nullptr) != (pool_bytes == 0))
+        return DX_ERR_BAD_ARG;
+    const dx_attn_config& c = h->cfg;
+    const size_t block_bytes = (size_t) c.num_kv_heads * c.tokens_per_block * c.head_size * (h->cache_kind == CACHE_T ? 2 : 1);
+    if (pool && pool_bytes < block_bytes)
+        return DX_ERR_BAD_ARG;
+    h->guard.pool_lo = pool ? reinterpret_cast<int64_t>(pool) : 0;
+    h->guard.pool_hi = pool ? reinterpret_cast<int64_t>(pool) + (int64_t) (pool_bytes - block_bytes) + 1 : 0;
+    return DX_OK;
 }
 
 int dx_attn_selftest_wait_timeout(dx_attn_t* h, int32_t poll_limit, void* cuda_stream)

@@ -18,6 +18,15 @@ enum CacheKind : int
     CACHE_FP8 = 2   // e4m3, per-tensor scale
 };
 
+// What the bounds-checked build (-DDECODE_ATTN_BOUNDS_CHECK) needs to validate a block pointer and to redirect a bad
+// access; all zero in the regular build, where table_entry() is a plain load.
+struct TableGuard
+{
+    int64_t safe_block; // device block of the handle (one cache block, zeros): target of redirected accesses
+    int64_t pool_lo;    // registered range of valid block start addresses [pool_lo, pool_hi); 0, 0: not registered
+    int64_t pool_hi;
+};
+
 // Arguments shared by every attention kernel.  Passed by value (fits the 4 KB parameter space).
 struct AttnArgs
 {
@@ -40,6 +49,7 @@ struct AttnArgs
     float softmax_scale_log2; // log2(e) / (sqrt(Dh) * q_scaling)
     int32_t streamk;          // 1: the CTAs walk equal ranges of the batch's token groups (SkSchedule), see below
     int32_t* tickets;         // device counter of the dynamic ranges of a two-level schedule (the merge kernel clears it)
+    TableGuard guard;
 };
 
 // Arguments of the feature-complete path (beam search, cyclic window, sink tokens, ALiBi).
@@ -72,6 +82,8 @@ struct GeneralArgs
     const void* rel_bias;
     int32_t rel_stride;
     int32_t max_distance;
+    int32_t* status; // device status word (0 ok)
+    TableGuard guard;
 };
 
 __host__ __device__ __forceinline__ int cyclic_slot(int tok, int sink, int cyclic_len)
@@ -84,10 +96,37 @@ __host__ __device__ __forceinline__ int cyclic_slot(int tok, int sink, int cycli
 static constexpr int32_t STATUS_TIMEOUT = 5;       // a bounded wait ran out
 static constexpr int32_t STATUS_NO_BLOCKS = 6;     // dx_kv_cache_step: free list or table row exhausted
 static constexpr int32_t STATUS_PLAN_EXCEEDED = 7; // a device length needs more partitions than the launch has
+static constexpr int32_t STATUS_BAD_TABLE = 8;     // bounds-checked build: block index or block pointer out of bounds
 
 __device__ __forceinline__ void report_status(int32_t* status, int32_t what)
 {
     atomicCAS(status, 0, what);
+}
+
+// Entry idx of a block-table row (K or V row of one sequence, max_blocks entries): the address of a cache block.
+// Regular build: a load.  Bounds-checked build: an index outside the row, a null or misaligned pointer, or one
+// outside the registered pool is recorded in the status word (STATUS_BAD_TABLE, first violation wins) and the
+// access goes to the handle's spare block instead, so that nothing outside the caller's memory is touched.
+__device__ __forceinline__ int64_t table_entry(
+    const int64_t* row, int idx, int max_blocks, int32_t* status, const TableGuard& g)
+{
+#ifdef DECODE_ATTN_BOUNDS_CHECK
+    if ((unsigned) idx >= (unsigned) max_blocks)
+    {
+        report_status(status, STATUS_BAD_TABLE);
+        return g.safe_block;
+    }
+    const int64_t p = __ldg(row + idx);
+    if (p == 0 || (p & 15) != 0 || (g.pool_hi != 0 && (p < g.pool_lo || p >= g.pool_hi)))
+    {
+        report_status(status, STATUS_BAD_TABLE);
+        return g.safe_block;
+    }
+    return p;
+#else
+    (void) max_blocks, (void) status, (void) g;
+    return __ldg(row + idx);
+#endif
 }
 
 // ----------------------------------------------------------------------------------------------

@@ -150,13 +150,15 @@ __global__ void __launch_bounds__(128) general_decode_kernel(const GeneralArgs a
             slot[u] = base + (warp * U + u) * TPW + sub;
             const int s = min(slot[u], kv_len - 1);
             const int seq = seq0 + ((beams && s >= ctx0) ? __ldg(indir + s) : 0);
-            const int64_t* rowp = a.block_ptrs + (int64_t) seq * 2 * a.max_blocks_per_seq + (s >> tpb_log2);
+            const int64_t* rowp = a.block_ptrs + (int64_t) seq * 2 * a.max_blocks_per_seq;
             const size_t off = head_off + (size_t) (s & tpb_mask) * ROW_BYTES;
             kraw[u] = vraw[u] = make_uint4(0u, 0u, 0u, 0u);
             if (active)
             {
-                kraw[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(__ldg(rowp)) + off);
-                vraw[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(__ldg(rowp + a.max_blocks_per_seq)) + off);
+                kraw[u] = *reinterpret_cast<const uint4*>(
+                    reinterpret_cast<const char*>(table_entry(rowp, s >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off);
+                vraw[u] = *reinterpret_cast<const uint4*>(
+                    reinterpret_cast<const char*>(table_entry(rowp + a.max_blocks_per_seq, s >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off);
             }
         }
 #pragma unroll
@@ -236,10 +238,11 @@ __global__ void __launch_bounds__(32) kv_append_token_kernel(const GeneralArgs a
     const uint4 kq = make_cache_vec<T, CACHE, EPL>(qkv_b + (size_t) (a.num_heads + hk) * DH + lane * EPL, sc_f, sc_t);
     const uint4 vq = make_cache_vec<T, CACHE, EPL>(
         qkv_b + (size_t) (a.num_heads + a.num_kv_heads + hk) * DH + lane * EPL, sc_f, sc_t);
-    const int64_t* rowp = a.block_ptrs + (int64_t) seq * 2 * a.max_blocks_per_seq + (slot >> tpb_log2);
+    const int64_t* rowp = a.block_ptrs + (int64_t) seq * 2 * a.max_blocks_per_seq;
     const size_t off = (size_t) hk * ((size_t) ROW_BYTES << tpb_log2) + (size_t) (slot & tpb_mask) * ROW_BYTES + lane * 16;
-    *reinterpret_cast<uint4*>(reinterpret_cast<char*>(__ldg(rowp)) + off) = kq;
-    *reinterpret_cast<uint4*>(reinterpret_cast<char*>(__ldg(rowp + a.max_blocks_per_seq)) + off) = vq;
+    *reinterpret_cast<uint4*>(reinterpret_cast<char*>(table_entry(rowp, slot >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off) = kq;
+    *reinterpret_cast<uint4*>(
+        reinterpret_cast<char*>(table_entry(rowp + a.max_blocks_per_seq, slot >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off) = vq;
 }
 
 // Several new tokens per sequence in one step (the reference's Medusa mode, which it serves with pre-compiled
@@ -302,13 +305,14 @@ __global__ void __launch_bounds__(128) multi_token_decode_kernel(const GeneralAr
             valid[u] = slot < past;
             if (slot >= past && slot < total)
                 valid[u] = (__ldg(mask_row + ((slot - past) >> 5)) >> ((slot - past) & 31)) & 1;
-            const int64_t* rowp = krow + (s >> tpb_log2);
             const size_t off = head_off + (size_t) (s & tpb_mask) * ROW_BYTES;
             kraw[u] = vraw[u] = make_uint4(0u, 0u, 0u, 0u);
             if (active)
             {
-                kraw[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(__ldg(rowp)) + off);
-                vraw[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(__ldg(rowp + a.max_blocks_per_seq)) + off);
+                kraw[u] = *reinterpret_cast<const uint4*>(
+                    reinterpret_cast<const char*>(table_entry(krow, s >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off);
+                vraw[u] = *reinterpret_cast<const uint4*>(
+                    reinterpret_cast<const char*>(table_entry(krow + a.max_blocks_per_seq, s >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off);
             }
         }
 #pragma unroll

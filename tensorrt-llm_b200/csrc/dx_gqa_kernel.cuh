@@ -318,8 +318,8 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
             const int rows = new_pos - t0; // rows already in the cache (>= TG for all but the last group)
             const uint32_t kdst = ring_u32 + ((ring_base + i) % STAGES) * Tr::STAGE_BYTES;
             const size_t off = head_off + (size_t) (t0 & tpb_mask) * DH + lane * 16;
-            const char* kb = reinterpret_cast<const char*>(__ldg(krow + (t0 >> tpb_log2))) + off;
-            const char* vb = reinterpret_cast<const char*>(__ldg(vrow + (t0 >> tpb_log2))) + off;
+            const char* kb = reinterpret_cast<const char*>(table_entry(krow, t0 >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
+            const char* vb = reinterpret_cast<const char*>(table_entry(vrow, t0 >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
             if (rows >= TG)
             {
 #pragma unroll
@@ -535,8 +535,8 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
                     if (hg == 0)
                     {
                         const size_t off = head_off + (size_t) (new_pos & tpb_mask) * DH + lane * 16;
-                        char* kb = reinterpret_cast<char*>(__ldg(krow + (new_pos >> tpb_log2))) + off;
-                        char* vb = reinterpret_cast<char*>(__ldg(vrow + (new_pos >> tpb_log2))) + off;
+                        char* kb = reinterpret_cast<char*>(table_entry(krow, new_pos >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
+                        char* vb = reinterpret_cast<char*>(table_entry(vrow, new_pos >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
                         *reinterpret_cast<uint4*>(kb) = kq;
                         *reinterpret_cast<uint4*>(vb) = vq;
                     }

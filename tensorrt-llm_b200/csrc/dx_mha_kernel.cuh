@@ -148,8 +148,8 @@ __global__ void __launch_bounds__(128) mha_decode_kernel(const AttnArgs a)
         if (bytes)
         {
             const size_t off = head_off + (size_t) (t0 & tpb_mask) * ROW_BYTES;
-            const char* kb = reinterpret_cast<const char*>(__ldg(krow + (t0 >> tpb_log2))) + off;
-            const char* vb = reinterpret_cast<const char*>(__ldg(vrow + (t0 >> tpb_log2))) + off;
+            const char* kb = reinterpret_cast<const char*>(table_entry(krow, t0 >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
+            const char* vb = reinterpret_cast<const char*>(table_entry(vrow, t0 >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
             bulk_g2s(dst, kb, bytes, bar);
             bulk_g2s(dst + SLAB, vb, bytes, bar);
         }
@@ -237,8 +237,8 @@ __global__ void __launch_bounds__(128) mha_decode_kernel(const AttnArgs a)
                 if (h == hk * G)
                 {
                     const size_t off = head_off + (size_t) (new_pos & tpb_mask) * ROW_BYTES + lane * 16;
-                    char* kb = reinterpret_cast<char*>(__ldg(krow + (new_pos >> tpb_log2))) + off;
-                    char* vb = reinterpret_cast<char*>(__ldg(vrow + (new_pos >> tpb_log2))) + off;
+                    char* kb = reinterpret_cast<char*>(table_entry(krow, new_pos >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
+                    char* vb = reinterpret_cast<char*>(table_entry(vrow, new_pos >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
                     *reinterpret_cast<uint4*>(kb) = kq;
                     *reinterpret_cast<uint4*>(vb) = vq;
                 }

@@ -231,16 +231,17 @@ __global__ void __launch_bounds__(128, TokTraits<GP>::MIN_BLOCKS)
                 const int t0 = chunk_start + i * TT;
                 if (i < n_tiles && t0 + TT <= new_pos && tpb_log2 >= 6)
                 {
-                    const int64_t* rowp = (is_v ? vrow : krow) + (t0 >> tpb_log2);
+                    const int64_t* rowp = is_v ? vrow : krow;
+                    const int bi = t0 >> tpb_log2;
                     if (tpb_log2 >= 7)
                     {
-                        r.lo = reinterpret_cast<const char*>(__ldg(rowp)) + src_thread + (size_t) (t0 & tpb_mask) * DH;
+                        r.lo = reinterpret_cast<const char*>(table_entry(rowp, bi, a.max_blocks_per_seq, a.status, a.guard)) + src_thread + (size_t) (t0 & tpb_mask) * DH;
                         r.hi = r.lo + 64 * DH;
                     }
                     else
                     {
-                        r.lo = reinterpret_cast<const char*>(__ldg(rowp)) + src_thread;
-                        r.hi = reinterpret_cast<const char*>(__ldg(rowp + 1)) + src_thread;
+                        r.lo = reinterpret_cast<const char*>(table_entry(rowp, bi, a.max_blocks_per_seq, a.status, a.guard)) + src_thread;
+                        r.hi = reinterpret_cast<const char*>(table_entry(rowp, bi + 1, a.max_blocks_per_seq, a.status, a.guard)) + src_thread;
                     }
                 }
                 return r;
@@ -266,7 +267,7 @@ __global__ void __launch_bounds__(128, TokTraits<GP>::MIN_BLOCKS)
                         const int tok = t0 + r0 + 16 * j;
                         const bool ok = tok < new_pos;
                         const int tk = ok ? tok : new_pos; // keeps the table look-up inside the allocated blocks
-                        const char* src = reinterpret_cast<const char*>(__ldg((is_v ? vrow : krow) + (tk >> tpb_log2)))
+                        const char* src = reinterpret_cast<const char*>(table_entry(is_v ? vrow : krow, tk >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard))
                             + head_off + (size_t) (tk & tpb_mask) * DH + col * 16;
                         cp_async16_zfill_u32(dst + j * 2048, src, ok ? 16u : 0u);
                     }
@@ -286,7 +287,7 @@ __global__ void __launch_bounds__(128, TokTraits<GP>::MIN_BLOCKS)
                     unsigned char* stage = smem + (is_v ? Tr::OFF_V : Tr::OFF_K) + ((tbase + i) % NST) * KV_TILE;
                     *reinterpret_cast<uint4*>(stage + hw_swz<128>((uint32_t) (new_pos - t0) * 128 + lane * 16)) = q;
                     const int64_t* rowp = is_v ? vrow : krow;
-                    char* dst = reinterpret_cast<char*>(__ldg(rowp + (new_pos >> tpb_log2))) + head_off
+                    char* dst = reinterpret_cast<char*>(table_entry(rowp, new_pos >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + head_off
                         + (size_t) (new_pos & tpb_mask) * DH + lane * 16;
                     *reinterpret_cast<uint4*>(dst) = q;
                 }

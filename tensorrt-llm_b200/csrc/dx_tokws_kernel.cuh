@@ -359,8 +359,8 @@ __global__ void __launch_bounds__(TokWsTraits<GP, STAGES>::THREADS, MINB)
                 vq = make_cache_vec<T, CACHE, 16>(
                     qkv_b + (size_t) (a.num_heads + a.num_kv_heads + pc.hk) * DH + lane * 16, sc_f, sc_t);
                 const size_t off = head_off + (size_t) (new_pos & tpb_mask) * DH + lane * 16;
-                *reinterpret_cast<uint4*>(reinterpret_cast<char*>(__ldg(krow + (new_pos >> tpb_log2))) + off) = kq;
-                *reinterpret_cast<uint4*>(reinterpret_cast<char*>(__ldg(vrow + (new_pos >> tpb_log2))) + off) = vq;
+                *reinterpret_cast<uint4*>(reinterpret_cast<char*>(table_entry(krow, new_pos >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off) = kq;
+                *reinterpret_cast<uint4*>(reinterpret_cast<char*>(table_entry(vrow, new_pos >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off) = vq;
             }
             bool ok = true;
             for (int i = 0; i < pc.n_tiles && ok; ++i, ++g)
@@ -375,8 +375,8 @@ __global__ void __launch_bounds__(TokWsTraits<GP, STAGES>::THREADS, MINB)
                 {
                     const int t = min(t0 + 32 * q, new_pos); // keeps the look-up inside the allocated blocks
                     const size_t off = head_off + (size_t) (t & tpb_mask) * DH + lane * 16;
-                    kp[q] = reinterpret_cast<const char*>(__ldg(krow + (t >> tpb_log2))) + off;
-                    vp[q] = reinterpret_cast<const char*>(__ldg(vrow + (t >> tpb_log2))) + off;
+                    kp[q] = reinterpret_cast<const char*>(table_entry(krow, t >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
+                    vp[q] = reinterpret_cast<const char*>(table_entry(vrow, t >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
                 }
                 const bool whole = t0 + TT <= new_pos; // every row of the tile is in the cache
 #pragma unroll

@@ -131,8 +131,8 @@ __global__ void __launch_bounds__(128, WideTraits<DH>::MIN_BLOCKS) wide_decode_k
         const int t0 = chunk_start + i * TT;
         if (i >= n_tiles || t0 + TT > new_pos)
             return nullptr;
-        const int64_t* rowp = (is_v ? vrow : krow) + (t0 >> tpb_log2);
-        return reinterpret_cast<const char*>(__ldg(rowp)) + src_thread + (size_t) (t0 & tpb_mask) * DH;
+        return reinterpret_cast<const char*>(table_entry(is_v ? vrow : krow, t0 >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + src_thread
+            + (size_t) (t0 & tpb_mask) * DH;
     };
     auto issue = [&](int i, bool is_v, const char* tp)
     {
@@ -146,8 +146,8 @@ __global__ void __launch_bounds__(128, WideTraits<DH>::MIN_BLOCKS) wide_decode_k
         }
         else
         {
-            const int64_t* rowp = (is_v ? vrow : krow) + (min(t0, new_pos) >> tpb_log2);
-            const char* base = reinterpret_cast<const char*>(__ldg(rowp)) + src_thread + (size_t) (t0 & tpb_mask) * DH;
+            const char* base = reinterpret_cast<const char*>(table_entry(is_v ? vrow : krow, min(t0, new_pos) >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard))
+                + src_thread + (size_t) (t0 & tpb_mask) * DH;
 #pragma unroll
             for (int j = 0; j < COPIES; ++j)
             {
@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(128, WideTraits<DH>::MIN_BLOCKS) wide_decode_k
             if (hg == 0)
             {
                 const int64_t* rowp = is_v ? vrow : krow;
-                char* dst = reinterpret_cast<char*>(__ldg(rowp + (new_pos >> tpb_log2))) + head_off
+                char* dst = reinterpret_cast<char*>(table_entry(rowp, new_pos >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + head_off
                     + (size_t) (new_pos & tpb_mask) * DH + lane * 16;
                 *reinterpret_cast<uint4*>(dst) = q;
             }

@@ -90,7 +90,7 @@ EXPORTED_SYMBOLS = [
     "dx_attn_enqueue_generation", "dx_attn_enqueue_generation_host", "dx_attn_host_sync", "dx_kv_cache_step", "dx_attn_validate", "dx_attn_plan", "dx_attn_plan_lengths",
     "dx_attn_device_status", "dx_attn_last_cuda_error", "dx_attn_launch_count",
     "dx_attn_enqueue_generation_static_scratch", "dx_attn_static_scratch_bytes", "dx_attn_append_context",
-    "dx_attn_append_context_cyclic",
+    "dx_attn_append_context_cyclic", "dx_build_has_bounds_check", "dx_attn_set_pool_range",
     "dx_attn_selftest_wait_timeout",
 ]
 
@@ -141,6 +141,9 @@ def load_library() -> ctypes.CDLL:
     lib.dx_attn_append_context_cyclic.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                                   ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
                                                   ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
+    lib.dx_build_has_bounds_check.restype = ctypes.c_int
+    lib.dx_attn_set_pool_range.restype = ctypes.c_int
+    lib.dx_attn_set_pool_range.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
     lib.dx_attn_validate.restype = ctypes.c_int
     lib.dx_attn_validate.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
                                      ctypes.c_int32, ctypes.c_void_p, ctypes.c_size_t]
@@ -238,6 +241,12 @@ class GPTAttentionPlugin:
             return {"num_partitions": 0, "tokens_per_partition": c.value, "kernel": kernel,
                     "stream_k_ctas": -n.value}
         return {"num_partitions": n.value, "tokens_per_partition": c.value, "kernel": kernel}
+
+    def set_pool_range(self, pool: Optional[torch.Tensor]) -> None:
+        """Bounds-checked build: the only memory cache blocks may lie in (None: no range)."""
+        st = self.lib.dx_attn_set_pool_range(self._h, _ptr(pool), 0 if pool is None else pool.numel() * pool.element_size())
+        if st != DX_OK:
+            raise DecodeAttnError(st, "dx_attn_set_pool_range")
 
     def launch_count(self) -> int:
         return int(self.lib.dx_attn_launch_count(self._h))
