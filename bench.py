@@ -334,6 +334,7 @@ def run_own_arm(args):
     # repetition.  The repetitions only make the figure rest on more GPU time (and give the clock sampler
     # something to sample); `steps` and `ms_per_step` mean what they always meant. ----
     est = m.repetition(min(args.steps, 20), barrier) / min(args.steps, 20)  # untimed: sizes the repetitions
+    est = max_over_ranks([est])[0]  # every rank must derive the same number of repetitions (they meet at barriers)
     repeats = args.repeats if args.repeats > 0 else int(min(400, max(25, -(-250.0 // max(1e-6, args.steps * est)))))
     sampler = ClockSampler(physical_gpu_index(local_rank), period_s=0.005)
     ev = []
