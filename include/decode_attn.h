@@ -227,8 +227,8 @@ int dx_attn_enqueue_generation_host(
  * array until the process exits.  The call allocates nothing and calls no allocating routine.
  *  - A batch whose partials need more than DX_STATIC_SCRATCH_BYTES is refused with DX_ERR_WORKSPACE
  *    before anything is launched (dx_attn_workspace_size() gives an upper bound of the need).  Calls that need
- *    no partials - beam search, sliding window / sinks, ALiBi, several new tokens per sequence - are never
- *    refused for their length.
+ *    no partials - a wrapped sliding window, sink tokens, relative attention bias, several new tokens per
+ *    sequence, head sizes other than 64 / 128 - are never refused for their length.
  *  - The first call on a device looks the array's device address up (cudaGetSymbolAddress), which may make the
  *    driver load the library's device code (a driver-side allocation): make that first call before any stream
  *    capture and before the allocator is frozen.  From the second call on a device nothing is allocated.

@@ -71,6 +71,8 @@ struct dx_attn
     int min_chunk = 256;         // smallest partition bound, tokens
     int fixed_cost_tokens = 400; // per-CTA fixed cost (prologue, pipeline fill, epilogue) in tokens of streaming time
     KernelInfo k_mha{}, k_gqa[2]{}, k_wide{}, k_tok{}, k_merge{}, k_append{}; // k_gqa[16 heads per CTA?]
+    KernelInfo k_gqa_feat[2]{}; // feature form of k_gqa (beam search, ALiBi), 8-bit caches
+    bool feature_gqa = true;    // beams / ALiBi on grouped heads run on it (0: on the per-head feature kernel)
     KernelInfo k_gqa_six{}; // stream-K form of k_gqa[0] with two six-warp CTAs per SM (where built)
     bool wide = false;       // wide-group kernel usable for this configuration
     bool tok = false;        // token-major tcgen05 kernel usable for this configuration
@@ -644,6 +646,100 @@ int enqueue_general(dx_attn* h, const dx_attn_generation_params& p, int max_past
     return DX_OK;
 }
 
+// Beam search and ALiBi on grouped heads with an 8-bit cache, when no window has wrapped: the feature form of the
+// tensor-core grouped-head kernel (the q heads of a kv head share every cache read; beams of a request are
+// sequences of their own whose shared context comes out of L2), classic split-K partitions, the usual merge.
+int enqueue_feature_gqa(dx_attn* h, const dx_attn_generation_params& p, int max_past, void* cuda_stream)
+{
+    const dx_attn_config& c = h->cfg;
+    const int nseq = p.num_requests * p.beam_width;
+    if (p.beam_width > 1)
+    {
+        if (!p.cache_indir || !p.context_lengths)
+            return DX_ERR_BAD_ARG;
+        if (((uintptr_t) p.cache_indir | (uintptr_t) p.context_lengths) & 3)
+            return DX_ERR_BAD_ARG;
+    }
+    if ((int64_t) max_past + 1 > (int64_t) p.max_blocks_per_sequence * c.tokens_per_block)
+        return DX_ERR_BAD_ARG; // the table cannot hold that many tokens
+    Plan plan;
+    plan.kind = KIND_GQA;
+    plan.hgroups = (h->group + 15) / 16;
+    plan.heads16 = h->group > 8;
+    const int rows_per_seq = c.num_kv_heads * plan.hgroups;
+    plan.rows = nseq * rows_per_seq;
+    plan.resident = std::max(1, h->k_gqa_feat[plan.heads16 ? 1 : 0].resident);
+    plan_partitions(h, plan, nseq, rows_per_seq, max_past, p.host_past_key_value_lengths);
+    const size_t prep = prep_bytes(h, nseq);
+    if (plan.nsplit > 1 || prep)
+    {
+        if (!p.workspace || ((uintptr_t) p.workspace & 127))
+            return p.workspace ? DX_ERR_BAD_ARG : DX_ERR_WORKSPACE;
+        if (p.workspace_bytes < prep + plan.workspace())
+            return DX_ERR_WORKSPACE;
+    }
+    char* const ws_partials = reinterpret_cast<char*>(p.workspace) + prep;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+    int st = check_cuda(h, cudaSetDevice(c.device));
+    if (st == DX_OK && prep)
+        st = launch_prep(h, p, nseq, stream);
+    if (st != DX_OK)
+        return st;
+
+    AttnArgs a{};
+    a.qkv = prep ? p.workspace : p.attention_input;
+    a.out = p.context_buf;
+    a.seq_len = p.sequence_lengths;
+    a.block_ptrs = p.block_pointers;
+    a.scale_orig_quant = p.kv_scale_orig_quant;
+    a.scale_quant_orig = p.kv_scale_quant_orig;
+    a.part_o = plan.nsplit > 1 ? reinterpret_cast<float*>(ws_partials) : nullptr;
+    a.part_ml = plan.nsplit > 1 ? reinterpret_cast<float2*>(ws_partials + plan.part_o_bytes) : nullptr;
+    a.status = h->status_dev;
+    a.batch = nseq;
+    a.num_heads = c.num_heads;
+    a.num_kv_heads = c.num_kv_heads;
+    a.max_blocks_per_seq = p.max_blocks_per_sequence;
+    a.tpb_log2 = h->tpb_log2;
+    a.chunk_tokens = plan.chunk_tokens;
+    a.nsplit = plan.nsplit;
+    a.softmax_scale_log2 = 1.4426950408889634f / (sqrtf((float) c.head_size) * c.q_scaling);
+    a.guard = h->guard;
+    a.cache_indir = p.beam_width > 1 ? p.cache_indir : nullptr;
+    a.context_lengths = p.context_lengths;
+    const bool alibi_type = c.position_embedding_type == POS_ALIBI || c.position_embedding_type == POS_ALIBI_WITH_SCALE;
+    a.alibi_slopes = alibi_type ? p.alibi_slopes : nullptr;
+    a.beam_width = p.beam_width;
+    a.max_attention_window = p.max_attention_window;
+
+    const KernelInfo& k = h->k_gqa_feat[plan.heads16 ? 1 : 0];
+    int hgroups = plan.hgroups;
+    void* args[] = {&a, &hgroups, &h->sk_zero};
+    st = check_cuda(h, cudaLaunchKernel(k.fn, dim3(plan.nsplit, c.num_kv_heads * plan.hgroups, nseq), dim3(k.threads), args,
+                           (size_t) k.smem, stream));
+    if (st != DX_OK)
+        return st;
+    h->launches.fetch_add(1);
+    if (plan.nsplit > 1)
+    {
+        void* margs[] = {&a};
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((nseq * c.num_heads + 3) / 4);
+        cfg.blockDim = dim3(128);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        st = check_cuda(h, cudaLaunchKernelExC(&cfg, h->k_merge.fn, margs));
+        if (st != DX_OK)
+            return st;
+        h->launches.fetch_add(1);
+    }
+    return DX_OK;
+}
+
 // Several new tokens per sequence (the reference's Medusa mode): append all of them, then one CTA per
 // (token, q head) reads the cache under the token's mask row.
 int enqueue_multi_token(dx_attn* h, const dx_attn_generation_params& p, int max_past, void* cuda_stream)
@@ -855,6 +951,19 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
         st = set_smem(h, h->k_mha);
     for (int i = 0; i < 2 && st == DX_OK; ++i)
         st = set_smem(h, h->k_gqa[i]);
+    if (st == DX_OK && h->cache_kind != CACHE_T && h->k_gqa[0].fn)
+    {
+        if (const char* w = getenv("DX_ATTN_FEATURE_GQA"))
+            h->feature_gqa = atoi(w) != 0;
+        for (int i = 0; i < 2 && h->feature_gqa; ++i)
+        {
+            h->k_gqa_feat[i] = gqa_feature_kernel_info(c.type_id, h->cache_kind, c.head_size, i != 0);
+            if (!h->k_gqa_feat[i].fn || set_smem(h, h->k_gqa_feat[i]) != DX_OK)
+                h->feature_gqa = false;
+        }
+    }
+    else
+        h->feature_gqa = false;
     if (st == DX_OK && h->k_gqa[0].fn)
     {
         const char* w = getenv("DX_ATTN_SK_SIX_WARPS"); // "0": stream-K launches stay on the four-warp CTAs
@@ -1077,6 +1186,11 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     // Beam search, a window shorter than some sequence, sink tokens and ALiBi go to the feature-complete kernel.
     const bool general = h->general_only || p.beam_width > 1 || p.sink_token_length > 0 || alibi || relative
         || p.cyclic_attention_window_size < max_past + 1 || p.max_attention_window < max_past + 1;
+    // beams / ALiBi over grouped heads with an 8-bit cache and no wrapped window share the cache reads of a kv head
+    if (general && h->feature_gqa && !h->general_only && h->group > 1 && c.tokens_per_block >= 32 && !relative
+        && p.sink_token_length == 0 && p.cyclic_attention_window_size >= max_past + 1
+        && p.max_attention_window >= max_past + 1)
+        return enqueue_feature_gqa(h, p, max_past, cuda_stream);
     if (general)
         return enqueue_general(h, p, max_past, cuda_stream);
     if ((int64_t) max_past + 1 > (int64_t) p.max_blocks_per_sequence * c.tokens_per_block)

@@ -50,6 +50,12 @@ struct AttnArgs
     int32_t streamk;          // 1: the CTAs walk equal ranges of the batch's token groups (SkSchedule), see below
     int32_t* tickets;         // device counter of the dynamic ranges of a two-level schedule (the merge kernel clears it)
     TableGuard guard;
+    // Feature form of the grouped-head 8-bit kernel (beam search, ALiBi); null / 0 on the plain path
+    const int32_t* cache_indir;     // int32 [B, max_attention_window]: beam a slot of sequence b comes from
+    const int32_t* context_lengths; // int32 [B]: slots below it come from beam 0 of the request
+    const void* alibi_slopes;       // T [H]
+    int32_t beam_width;
+    int32_t max_attention_window;
 };
 
 // Arguments of the feature-complete path (beam search, cyclic window, sink tokens, ALiBi).

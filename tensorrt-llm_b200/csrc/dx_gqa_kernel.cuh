@@ -199,7 +199,11 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr)
     return v;
 }
 
-template <typename T, int CACHE, int DH, bool H16, int WARPS = 4>
+// FEAT: the feature form (classic launches only).  Beam search: cache slot s of sequence b is read from sequence
+// request * beam_width + (s < context_lengths[b] ? 0 : cache_indir[b][s]), so every token row of a group has its own
+// source block (decoderMaskedMultiheadAttentionTemplate.h:1497-1498, :2063-2078); the new token goes to the
+// sequence's own blocks.  ALiBi: score += slope[head] * (s - past), nothing for the new token (:1797, :2026).
+template <typename T, int CACHE, int DH, bool H16, int WARPS = 4, bool FEAT = false>
 __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WARPS>())
     gqa_decode_kernel(const AttnArgs a, const int hgroups, const __grid_constant__ SkSchedule sk)
 {
@@ -302,6 +306,29 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
         const int64_t* krow = a.block_ptrs + (int64_t) b * 2 * a.max_blocks_per_seq;
         const int64_t* vrow = krow + a.max_blocks_per_seq;
         const size_t head_off = (size_t) hk * ((size_t) DH << tpb_log2);
+        // feature form: source of a slot (beam search) and ALiBi slopes of this thread's head rows (log2 units)
+        int seq0 = b, ctx0 = 0;
+        const int32_t* indir = nullptr;
+        float slope[NR];
+#pragma unroll
+        for (int r = 0; r < NR; ++r)
+            slope[r] = 0.f;
+        if constexpr (FEAT)
+        {
+            if (a.cache_indir != nullptr && a.beam_width > 1)
+            {
+                seq0 = (b / a.beam_width) * a.beam_width;
+                ctx0 = a.context_lengths[b];
+                indir = a.cache_indir + (size_t) b * a.max_attention_window;
+            }
+            if (a.alibi_slopes != nullptr)
+            {
+#pragma unroll
+                for (int r = 0; r < NR; ++r)
+                    slope[r] = TypeOps<T>::to_float(reinterpret_cast<const T*>(a.alibi_slopes)[head0 + min(g + 8 * r, nh - 1)])
+                        * 1.4426950408889634f;
+            }
+        }
 
         // Per-lane constant destination offsets of the 16-byte copies (copy j of a slab moves linear
         // bytes [(lane + 32 j) * 16, +16)).
@@ -317,6 +344,30 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
             const int t0 = chunk_start + gi * TG;
             const int rows = new_pos - t0; // rows already in the cache (>= TG for all but the last group)
             const uint32_t kdst = ring_u32 + ((ring_base + i) % STAGES) * Tr::STAGE_BYTES;
+            if constexpr (FEAT)
+            {
+                // every 16-byte piece looks up the block of its own token row
+#pragma unroll
+                for (int j = 0; j < SLAB / 512; ++j)
+                {
+                    const uint32_t d = (DH == 128) ? cdst[j & 1] + (j >> 1) * 1024 : cdst[j];
+                    const int lin = (lane + 32 * j) * 16;
+                    const int s = t0 + lin / DH;
+                    const bool ok = s < new_pos;
+                    const int sc = ok ? s : 0;
+                    const int seq = (indir != nullptr && sc >= ctx0) ? seq0 + __ldg(indir + sc) : seq0;
+                    const int64_t* srow = a.block_ptrs + (int64_t) seq * 2 * a.max_blocks_per_seq;
+                    const size_t o = head_off + (size_t) (sc & tpb_mask) * DH + lin % DH;
+                    const char* ks = reinterpret_cast<const char*>(
+                        table_entry(srow, sc >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + o;
+                    const char* vs = reinterpret_cast<const char*>(
+                        table_entry(srow + a.max_blocks_per_seq, sc >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + o;
+                    cp_async16_zfill_u32(kdst + d, ks, ok ? 16u : 0u);
+                    cp_async16_zfill_u32(kdst + SLAB + d, vs, ok ? 16u : 0u);
+                }
+                cp_async_mbar_arrive_noinc(&bars[(ring_base + i) % STAGES]);
+                return;
+            }
             const size_t off = head_off + (size_t) (t0 & tpb_mask) * DH + lane * 16;
             const char* kb = reinterpret_cast<const char*>(table_entry(krow, t0 >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
             const char* vb = reinterpret_cast<const char*>(table_entry(vrow, t0 >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
@@ -607,6 +658,8 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
                     else
                         sv = (float) (sacc[0][nt][c] * kLoWeight + sacc[0][nt][c + 2]);
                     p[nt][c] = sv * sfac[c >> 1];
+                    if constexpr (FEAT)
+                        p[nt][c] = fmaf(slope[c >> 1], (float) (t0 + sigma_row<DH>(nt, 2 * t + (c & 1)) - new_pos), p[nt][c]);
                 }
             }
             if (lim < TG)

@@ -16,6 +16,7 @@ struct KernelInfo
 KernelInfo mha_kernel_info(int dtype, int cache, int dh, int tokens_per_block);
 KernelInfo gqa_kernel_info(int dtype, int cache, int dh, bool heads16);
 KernelInfo gqa_streamk_kernel_info(int dtype, int cache, int dh, bool heads16); // 6-warp CTAs; empty where not built
+KernelInfo gqa_feature_kernel_info(int dtype, int cache, int dh, bool heads16); // beam search / ALiBi form, 8-bit caches
 KernelInfo wide_kernel_info(int dtype, int dh); // FP8 cache only
 KernelInfo tok_kernel_info(int dtype, int dh, int group); // FP8 cache, Dh 128, group <= 16
 KernelInfo tokws_kernel_info(int dtype, int dh, int group); // the persistent warp-specialised form of it

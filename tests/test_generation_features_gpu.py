@@ -118,6 +118,12 @@ CASES = {
     "alibi_gqa_int8": Case((8, 2), 64, torch.float16, "int8", 128, 3, alibi=True),
     "beam2_alibi_fp8": Case((4, 2), 128, torch.bfloat16, "fp8", 64, 2, beam=2, alibi=True),
     "beam2_window_wrapped": Case((4, 2), 64, torch.float16, "int8", 64, 2, beam=2, window=128, past_lo=100, past_hi=400),
+    # grouped heads over an 8-bit cache without a wrapped window: the feature form of the tensor-core kernel
+    "beam4_gqa_fp8_split": Case((16, 2), 128, torch.bfloat16, "fp8", 64, 2, beam=4, past_lo=3000, past_hi=5000, seed=7),
+    "beam2_group16_int8": Case((32, 2), 128, torch.bfloat16, "int8", 64, 2, beam=2, past_lo=200, past_hi=900, seed=8),
+    "alibi_group71_fp8": Case((71, 1), 64, torch.float16, "fp8", 64, 2, alibi=True, past_lo=100, past_hi=700, seed=9),
+    "beam3_alibi_group12_int8": Case((24, 2), 64, torch.float16, "int8", 32, 2, beam=3, alibi=True, past_lo=1, past_hi=300, seed=10),
+    "alibi_gqa_fp8_split": Case((8, 1), 128, torch.bfloat16, "fp8", 128, 2, alibi=True, past_lo=4000, past_hi=6000, seed=11),
 }
 
 
@@ -134,6 +140,20 @@ def test_features_against_oracle(pkg, name):
     print(name, "max", err.max().item(), "mean", err.mean().item())
     assert err.max().item() < MAX_ABS_TOL, f"max-abs {err.max().item():.3e}"
     assert err.mean().item() < MEAN_ABS_TOL, f"mean-abs {err.mean().item():.3e}"
+
+
+@pytest.mark.parametrize("name", ["beam4_gqa_fp8_split", "beam2_group16_int8", "beam2_alibi_fp8"])
+def test_grouped_feature_kernel_agrees_with_the_per_head_kernel(pkg, name, monkeypatch):
+    """The same call on the feature form of the grouped-head kernel (default) and, with DX_ATTN_FEATURE_GQA=0, on
+    the per-head feature kernel: identical pool bytes, outputs within the output tolerance of each other."""
+    c = CASES[name]
+    w_cpu, ex = _build(pkg, c)
+    out_a, pool_a = _run_product(pkg, c, w_cpu, ex)
+    monkeypatch.setenv("DX_ATTN_FEATURE_GQA", "0")
+    out_b, pool_b = _run_product(pkg, c, w_cpu, ex)
+    assert torch.equal(pool_a, pool_b)
+    err = (out_a - out_b).abs()
+    assert err.max().item() < MAX_ABS_TOL and err.mean().item() < MEAN_ABS_TOL, (err.max().item(), err.mean().item())
 
 
 def test_features_off_equals_plain_oracle(pkg):
