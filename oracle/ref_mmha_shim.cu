@@ -42,10 +42,16 @@ namespace mmha
 template void mmha_launch_kernel<RefT, KVBlockArray, Masked_multihead_attention_params<RefT>, REF_DH, false>(
     const Masked_multihead_attention_params<RefT>& params, const KVBlockArray& kv_cache_buffer,
     const KVLinearBuffer& shift_k_cache, const cudaStream_t& stream);
-// the variant that computes the relative-position bucket on the fly (chosen like decoderMaskedMultiheadAttention.cu:62)
+// the variant that computes the relative-position bucket on the fly (chosen like decoderMaskedMultiheadAttention.cu:62;
+// the reference instantiates it for head sizes 32, 64 and 128 only)
+#if REF_DH == 32 || REF_DH == 64 || REF_DH == 128
+#define REF_HAS_IMPLICIT_REL_BIAS 1
 template void mmha_launch_kernel<RefT, KVBlockArray, Masked_multihead_attention_params<RefT>, REF_DH, true>(
     const Masked_multihead_attention_params<RefT>& params, const KVBlockArray& kv_cache_buffer,
     const KVLinearBuffer& shift_k_cache, const cudaStream_t& stream);
+#else
+#define REF_HAS_IMPLICIT_REL_BIAS 0
+#endif
 } // namespace mmha
 } // namespace kernels
 } // namespace tensorrt_llm
@@ -153,8 +159,14 @@ static int ref_mmha_impl(const void* qkv, void* out, const int32_t* sequence_len
     try
     {
         if (p.max_distance > 0 && p.relative_attention_bias != nullptr)
+        {
+#if REF_HAS_IMPLICIT_REL_BIAS
             mmha::mmha_launch_kernel<RefT, KVBlockArray, Masked_multihead_attention_params<RefT>, REF_DH, true>(
                 p, kv, shift_k, stream);
+#else
+            return -2; // not instantiated by the reference for this head size
+#endif
+        }
         else
             mmha::mmha_launch_kernel<RefT, KVBlockArray, Masked_multihead_attention_params<RefT>, REF_DH, false>(
                 p, kv, shift_k, stream);

@@ -646,7 +646,7 @@ int enqueue_general(dx_attn* h, const dx_attn_generation_params& p, int max_past
     return DX_OK;
 }
 
-// Beam search and ALiBi on grouped heads with an 8-bit cache, when no window has wrapped: the feature form of the
+// Beam search, cyclic window / sink tokens and ALiBi on grouped heads with an 8-bit cache: the feature form of the
 // tensor-core grouped-head kernel (the q heads of a kv head share every cache read; beams of a request are
 // sequences of their own whose shared context comes out of L2), classic split-K partitions, the usual merge.
 int enqueue_feature_gqa(dx_attn* h, const dx_attn_generation_params& p, int max_past, void* cuda_stream)
@@ -660,8 +660,21 @@ int enqueue_feature_gqa(dx_attn* h, const dx_attn_generation_params& p, int max_
         if (((uintptr_t) p.cache_indir | (uintptr_t) p.context_lengths) & 3)
             return DX_ERR_BAD_ARG;
     }
-    if ((int64_t) max_past + 1 > (int64_t) p.max_blocks_per_sequence * c.tokens_per_block)
+    // window and sink arithmetic as in enqueue_general (KVBlockArray, kvCacheUtils.h:74-90)
+    const int tpb = c.tokens_per_block;
+    const int W = p.cyclic_attention_window_size, sink = p.sink_token_length;
+    if (p.max_attention_window < W || sink >= W)
+        return DX_ERR_BAD_ARG;
+    if (sink % tpb != 0)
+        return DX_ERR_UNSUPPORTED; // a partly filled sink block needs the reference's position shift
+    const bool one_more_block = (int64_t) (p.max_blocks_per_sequence - 1) * tpb >= W;
+    const int cyclic_len = one_more_block ? W + tpb - sink : W - sink;
+    if (max_past > W && one_more_block)
+        return DX_ERR_UNSUPPORTED; // the walked slots 0..W-1 are the live window only without the spare block
+    const int64_t slots_used = std::min<int64_t>((int64_t) max_past + 1, (int64_t) sink + cyclic_len);
+    if (slots_used > (int64_t) p.max_blocks_per_sequence * tpb)
         return DX_ERR_BAD_ARG; // the table cannot hold that many tokens
+    const bool wrapped = max_past > W; // some sequence walks W slots instead of its whole history
     Plan plan;
     plan.kind = KIND_GQA;
     plan.hgroups = (h->group + 15) / 16;
@@ -669,7 +682,8 @@ int enqueue_feature_gqa(dx_attn* h, const dx_attn_generation_params& p, int max_
     const int rows_per_seq = c.num_kv_heads * plan.hgroups;
     plan.rows = nseq * rows_per_seq;
     plan.resident = std::max(1, h->k_gqa_feat[plan.heads16 ? 1 : 0].resident);
-    plan_partitions(h, plan, nseq, rows_per_seq, max_past, p.host_past_key_value_lengths);
+    // (with a wrapped window the partitions are planned for W walked slots per sequence, an upper bound)
+    plan_partitions(h, plan, nseq, rows_per_seq, wrapped ? W : max_past, wrapped ? nullptr : p.host_past_key_value_lengths);
     const size_t prep = prep_bytes(h, nseq);
     if (plan.nsplit > 1 || prep)
     {
@@ -711,6 +725,7 @@ int enqueue_feature_gqa(dx_attn* h, const dx_attn_generation_params& p, int max_
     a.alibi_slopes = alibi_type ? p.alibi_slopes : nullptr;
     a.beam_width = p.beam_width;
     a.max_attention_window = p.max_attention_window;
+    a.cyclic_window = W;
 
     const KernelInfo& k = h->k_gqa_feat[plan.heads16 ? 1 : 0];
     int hgroups = plan.hgroups;
@@ -737,6 +752,26 @@ int enqueue_feature_gqa(dx_attn* h, const dx_attn_generation_params& p, int max_
             return st;
         h->launches.fetch_add(1);
     }
+    // the new token into its (cyclic) slot, behind every read of the old content of that slot
+    GeneralArgs g{};
+    g.qkv = a.qkv;
+    g.seq_len = p.sequence_lengths;
+    g.block_ptrs = p.block_pointers;
+    g.scale_orig_quant = p.kv_scale_orig_quant;
+    g.num_heads = c.num_heads;
+    g.num_kv_heads = c.num_kv_heads;
+    g.max_blocks_per_seq = p.max_blocks_per_sequence;
+    g.tpb_log2 = h->tpb_log2;
+    g.cyclic_len = cyclic_len;
+    g.sink = sink;
+    g.q_len = 1;
+    g.status = h->status_dev;
+    g.guard = h->guard;
+    void* gargs[] = {&g};
+    st = check_cuda(h, cudaLaunchKernel(h->k_general.append, dim3(c.num_kv_heads, nseq), dim3(32), gargs, 0, stream));
+    if (st != DX_OK)
+        return st;
+    h->launches.fetch_add(1);
     return DX_OK;
 }
 
@@ -1186,10 +1221,9 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     // Beam search, a window shorter than some sequence, sink tokens and ALiBi go to the feature-complete kernel.
     const bool general = h->general_only || p.beam_width > 1 || p.sink_token_length > 0 || alibi || relative
         || p.cyclic_attention_window_size < max_past + 1 || p.max_attention_window < max_past + 1;
-    // beams / ALiBi over grouped heads with an 8-bit cache and no wrapped window share the cache reads of a kv head
+    // beams / windows / sinks / ALiBi over grouped heads with an 8-bit cache share the cache reads of a kv head
     if (general && h->feature_gqa && !h->general_only && h->group > 1 && c.tokens_per_block >= 32 && !relative
-        && p.sink_token_length == 0 && p.cyclic_attention_window_size >= max_past + 1
-        && p.max_attention_window >= max_past + 1)
+        && h->k_general.append)
         return enqueue_feature_gqa(h, p, max_past, cuda_stream);
     if (general)
         return enqueue_general(h, p, max_past, cuda_stream);

@@ -56,6 +56,8 @@ struct AttnArgs
     const void* alibi_slopes;       // T [H]
     int32_t beam_width;
     int32_t max_attention_window;
+    int32_t cyclic_window; // > 0: the cache is cyclic; the kernels walk slots 0 .. min(past, cyclic_window) - 1 and the
+                           // new token is appended behind them by kv_append_token_kernel (0 on the plain path)
 };
 
 // Arguments of the feature-complete path (beam search, cyclic window, sink tokens, ALiBi).
@@ -91,6 +93,14 @@ struct GeneralArgs
     int32_t* status; // device status word (0 ok)
     TableGuard guard;
 };
+
+// Tokens a step attends to (cache slots walked + the new token) for a sequence of `total` tokens including the new
+// one: all of them, or with a cyclic cache min(past, window) + 1 (decoderMaskedMultiheadAttentionTemplate.h:1493).
+__host__ __device__ __forceinline__ int attended_tokens(int total, int cyclic_window)
+{
+    const int past = total - 1;
+    return cyclic_window > 0 && past > cyclic_window ? cyclic_window + 1 : total;
+}
 
 __host__ __device__ __forceinline__ int cyclic_slot(int tok, int sink, int cyclic_len)
 {

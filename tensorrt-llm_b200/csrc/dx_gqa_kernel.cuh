@@ -201,8 +201,9 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr)
 
 // FEAT: the feature form (classic launches only).  Beam search: cache slot s of sequence b is read from sequence
 // request * beam_width + (s < context_lengths[b] ? 0 : cache_indir[b][s]), so every token row of a group has its own
-// source block (decoderMaskedMultiheadAttentionTemplate.h:1497-1498, :2063-2078); the new token goes to the
-// sequence's own blocks.  ALiBi: score += slope[head] * (s - past), nothing for the new token (:1797, :2026).
+// source block (decoderMaskedMultiheadAttentionTemplate.h:1497-1498, :2063-2078).  Cyclic cache: the kernel walks
+// slots 0 .. min(past, window) - 1 as they are (:1493).  The new token is taken from the QKV row as it will be stored and
+// appended by kv_append_token_kernel behind this kernel (its slot may be one that is read in this step).  ALiBi: score += slope[head] * (s - past), nothing for the new token (:1797, :2026).
 template <typename T, int CACHE, int DH, bool H16, int WARPS = 4, bool FEAT = false>
 __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WARPS>())
     gqa_decode_kernel(const AttnArgs a, const int hgroups, const __grid_constant__ SkSchedule sk)
@@ -236,7 +237,8 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
     else
     {
         int cs, ct, np;
-        partition_of(a.seq_len[blockIdx.z], a.chunk_tokens, (int) blockIdx.x, cs, ct, np);
+        partition_of(FEAT ? attended_tokens(a.seq_len[blockIdx.z], a.cyclic_window) : a.seq_len[blockIdx.z], a.chunk_tokens,
+            (int) blockIdx.x, cs, ct, np);
         if (np > (int) gridDim.x && blockIdx.x == 0 && threadIdx.x == 0)
             report_status(a.status, STATUS_PLAN_EXCEEDED); // the tokens beyond the last partition are not attended to
         if ((int) blockIdx.x >= np)
@@ -276,7 +278,8 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
         {
             int np;
             chunk = blockIdx.x, hk = blockIdx.y / hgroups, hg = blockIdx.y % hgroups, b = blockIdx.z;
-            partition_of(a.seq_len[b], a.chunk_tokens, chunk, chunk_start, ctoks, np);
+            partition_of(FEAT ? attended_tokens(a.seq_len[b], a.cyclic_window) : a.seq_len[b], a.chunk_tokens, chunk,
+                chunk_start, ctoks, np);
             final_out = a.nsplit == 1;
         }
         const int nh = min(16, G - hg * 16); // q heads handled in this piece
@@ -296,7 +299,9 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
                 q_raw[r][i] = *reinterpret_cast<const uint4*>(qp + 8 * i);
         }
         const float deq = __ldg(a.scale_quant_orig);
-        const int total = a.seq_len[b];
+        // (feature form: `total` counts the cache slots walked plus the new token; past_true is the real history)
+        const int past_true = a.seq_len[b] - 1;
+        const int total = FEAT ? attended_tokens(past_true + 1, a.cyclic_window) : past_true + 1;
         if (a.streamk && total > (int) cur.nb * TG && threadIdx.x == 0)
             report_status(a.status, STATUS_PLAN_EXCEEDED); // longer than the host length the ranges were laid out for
         ctoks = max(0, min(ctoks, total - chunk_start)); // the schedule counts host lengths; the device length decides
@@ -318,7 +323,7 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
             if (a.cache_indir != nullptr && a.beam_width > 1)
             {
                 seq0 = (b / a.beam_width) * a.beam_width;
-                ctx0 = a.context_lengths[b];
+                ctx0 = (a.cyclic_window > 0 && past_true > a.cyclic_window) ? 0 : a.context_lengths[b]; // wrapped: all via the table
                 indir = a.cache_indir + (size_t) b * a.max_attention_window;
             }
             if (a.alibi_slopes != nullptr)
@@ -583,7 +588,7 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
                     unsigned char* stage = smem + warp * (STAGES * Tr::STAGE_BYTES) + s * Tr::STAGE_BYTES;
                     *reinterpret_cast<uint4*>(stage + lin) = kq;
                     *reinterpret_cast<uint4*>(stage + SLAB + lin) = vq;
-                    if (hg == 0)
+                    if (!FEAT && hg == 0) // (feature form: kv_append_token_kernel stores the token behind this kernel)
                     {
                         const size_t off = head_off + (size_t) (new_pos & tpb_mask) * DH + lane * 16;
                         char* kb = reinterpret_cast<char*>(table_entry(krow, new_pos >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
@@ -659,7 +664,10 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
                         sv = (float) (sacc[0][nt][c] * kLoWeight + sacc[0][nt][c + 2]);
                     p[nt][c] = sv * sfac[c >> 1];
                     if constexpr (FEAT)
-                        p[nt][c] = fmaf(slope[c >> 1], (float) (t0 + sigma_row<DH>(nt, 2 * t + (c & 1)) - new_pos), p[nt][c]);
+                    {
+                        const int tok = t0 + sigma_row<DH>(nt, 2 * t + (c & 1));
+                        p[nt][c] = fmaf(slope[c >> 1], tok == new_pos ? 0.f : (float) (tok - past_true), p[nt][c]);
+                    }
                 }
             }
             if (lim < TG)

@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(128) lse_merge_kernel(const AttnArgs a)
     if (row >= a.batch * a.num_heads)
         return;
     const int b = row / a.num_heads;
-    const int total = a.seq_len[b];
+    const int total = attended_tokens(a.seq_len[b], a.cyclic_window);
     griddep_wait(); // launched with programmatic stream serialisation: the partials are complete after this
     // partitions this sequence used (partition_of), never more than the launch had and never fewer than one: a
     // device length beyond what the call was planned for was reported by the attention kernel, and the merge

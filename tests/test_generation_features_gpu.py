@@ -124,6 +124,9 @@ CASES = {
     "alibi_group71_fp8": Case((71, 1), 64, torch.float16, "fp8", 64, 2, alibi=True, past_lo=100, past_hi=700, seed=9),
     "beam3_alibi_group12_int8": Case((24, 2), 64, torch.float16, "int8", 32, 2, beam=3, alibi=True, past_lo=1, past_hi=300, seed=10),
     "alibi_gqa_fp8_split": Case((8, 1), 128, torch.bfloat16, "fp8", 128, 2, alibi=True, past_lo=4000, past_hi=6000, seed=11),
+    "window_wrapped_fp8_split": Case((16, 2), 128, torch.bfloat16, "fp8", 64, 2, window=4096, past_lo=3000, past_hi=9000, seed=12),
+    "window_sink_alibi_int8": Case((8, 2), 64, torch.float16, "int8", 32, 3, window=256, sink=32, alibi=True, past_lo=100, past_hi=800, seed=13),
+    "beam2_window_sink_fp8": Case((8, 2), 128, torch.bfloat16, "fp8", 64, 2, beam=2, window=256, sink=64, past_lo=100, past_hi=700, seed=14),
 }
 
 
@@ -142,7 +145,8 @@ def test_features_against_oracle(pkg, name):
     assert err.mean().item() < MEAN_ABS_TOL, f"mean-abs {err.mean().item():.3e}"
 
 
-@pytest.mark.parametrize("name", ["beam4_gqa_fp8_split", "beam2_group16_int8", "beam2_alibi_fp8"])
+@pytest.mark.parametrize("name", ["beam4_gqa_fp8_split", "beam2_group16_int8", "beam2_alibi_fp8", "window_wrapped_int8",
+                                  "window_sink_fp8", "beam2_window_wrapped", "window_wrapped_fp8_split"])
 def test_grouped_feature_kernel_agrees_with_the_per_head_kernel(pkg, name, monkeypatch):
     """The same call on the feature form of the grouped-head kernel (default) and, with DX_ATTN_FEATURE_GQA=0, on
     the per-head feature kernel: identical pool bytes, outputs within the output tolerance of each other."""

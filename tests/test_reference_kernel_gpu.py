@@ -23,7 +23,8 @@ def _run_reference(w, tiles=0, sync=True, out=None, ws=None, qkv_bias=None, rope
     cfg = w.cfg
     rope = rope or {}
     lib = ctypes.CDLL(str(LIB))
-    fn = lib.ref_mmha_bf16_128 if (cfg.dtype == torch.bfloat16 and cfg.head_size == 128) else lib.ref_mmha_fp16_64
+    # one instantiation of the reference kernel per (T, Dh): bf16/128, fp16/64, bf16/256, fp16/80
+    fn = getattr(lib, f"ref_mmha_{'bf16' if cfg.dtype == torch.bfloat16 else 'fp16'}_{cfg.head_size}")
     fn.restype = ctypes.c_int
     if out is None:
         out = torch.empty(cfg.batch, cfg.num_heads * cfg.head_size, dtype=cfg.dtype, device=w.qkv.device)
@@ -57,6 +58,11 @@ def _run_reference(w, tiles=0, sync=True, out=None, ws=None, qkv_bias=None, rope
     (torch.float16, 64, "fp8", (8, 1)),
     (torch.float16, 64, "none", (4, 4)),
     (torch.float16, 64, "int8", (4, 2)),
+    # two of the head sizes served by the feature-complete kernels
+    (torch.bfloat16, 256, "fp8", (4, 2)),
+    (torch.bfloat16, 256, "none", (4, 4)),
+    (torch.float16, 80, "int8", (4, 4)),
+    (torch.float16, 80, "none", (6, 2)),
 ])
 def test_oracle_matches_reference_mmha_kernel(pkg, dtype, dh, cache, heads):
     wl = workloads
