@@ -280,23 +280,35 @@ def test_beams_with_bias_and_rotary_embedding(pkg):
         plugin.close()
 
 
-def test_report_feature_path_time(pkg):
-    """Times the feature path on a beam-search batch of c4's shape (recorded in feature_path.jsonl of the report directory)."""
+FEATURE_TIMING = {
+    "beam 4 x 16 requests, 64 q / 8 kv heads, Dh 128, FP8, past 2048-4096":
+        Case((64, 8), 128, torch.bfloat16, "fp8", 64, 16, beam=4, past_lo=2048, past_hi=4096, seed=3),
+    "sliding window 4096 wrapped, 64 sequences, 32 q / 8 kv heads, Dh 128, FP8, past 5000-12000":
+        Case((32, 8), 128, torch.bfloat16, "fp8", 64, 64, window=4096, past_lo=5000, past_hi=12000, seed=4),
+}
+
+
+@pytest.mark.parametrize("label", sorted(FEATURE_TIMING))
+def test_report_feature_path_time(pkg, label):
+    """Times the feature path on a beam-search batch of c4's shape and on a wrapped sliding window (recorded in
+    feature_path.jsonl of the report directory)."""
     import json
     import os
-    c = Case((64, 8), 128, torch.bfloat16, "fp8", 64, 16, beam=4, past_lo=2048, past_hi=4096, seed=3)
+    c = FEATURE_TIMING[label]
     w_cpu, ex = _build(pkg, c)
     w = workloads.to_device(w_cpu, "cuda:0")
     plugin = _plugin(pkg, c)
     try:
-        ci, cl = ex["cache_indirection"].cuda(), ex["context_lengths"].cuda()
-        out = torch.empty(w.cfg.batch, 64 * 128, dtype=torch.bfloat16, device="cuda:0")
+        dev = lambda t: None if t is None else t.cuda()
+        ci, cl = dev(ex.get("cache_indirection")), dev(ex.get("context_lengths"))
+        out = torch.empty(w.cfg.batch, c.heads[0] * c.dh, dtype=c.dtype, device="cuda:0")
 
         def step():
             plugin.enqueue_generation(w.qkv, w.sequence_length, w.host_past_key_value_lengths,
                                       w.kv_cache_block_pointers, w.kv_orig_quant_scale, w.kv_quant_orig_scale, out=out,
                                       max_attention_window=ex["max_attention_window"], cache_indirection=ci,
-                                      beam_width=4, context_lengths=cl)
+                                      beam_width=c.beam, context_lengths=cl,
+                                      cyclic_attention_window_size=ex["cyclic_attention_window_size"])
         for _ in range(3):
             step()
         torch.cuda.synchronize()
@@ -307,9 +319,9 @@ def test_report_feature_path_time(pkg):
         b.record()
         torch.cuda.synchronize()
         us = a.elapsed_time(b) / 10 * 1e3
-        kv = float((w_cpu.host_past_key_value_lengths.double().sum()) * 8 * 128 * 2)
-        rec = {"case": "beam 4 x 16 requests, 64 q / 8 kv heads, Dh 128, FP8, past 2048-4096", "us": us,
-               "unique_kv_GBps": kv / us / 1e3}
+        walked = torch.clamp(w_cpu.host_past_key_value_lengths, max=c.window) if c.window else w_cpu.host_past_key_value_lengths
+        kv = float(walked.double().sum() * c.heads[1] * c.dh * 2)
+        rec = {"case": label, "us": us, "unique_kv_GBps": kv / us / 1e3}
         os.makedirs(REPORT_DIR, exist_ok=True)
         with open(os.path.join(REPORT_DIR, "feature_path.jsonl"), "a") as f:
             f.write(json.dumps(rec) + "\n")
