@@ -72,6 +72,7 @@ struct dx_attn
     int fixed_cost_tokens = 400; // per-CTA fixed cost (prologue, pipeline fill, epilogue) in tokens of streaming time
     KernelInfo k_mha{}, k_gqa[2]{}, k_wide{}, k_tok{}, k_merge{}, k_append{}; // k_gqa[16 heads per CTA?]
     KernelInfo k_gqa_feat[2]{}; // feature form of k_gqa (beam search, ALiBi), 8-bit caches
+    KernelInfo k_gqa_multi[2]{}; // several-new-tokens form of k_gqa (rows = (token, head) pairs of a kv head)
     bool feature_gqa = true;    // beams / ALiBi on grouped heads run on it (0: on the per-head feature kernel)
     KernelInfo k_gqa_six{}; // stream-K form of k_gqa[0] with two six-warp CTAs per SM (where built)
     bool wide = false;       // wide-group kernel usable for this configuration
@@ -841,6 +842,77 @@ int enqueue_multi_token(dx_attn* h, const dx_attn_generation_params& p, int max_
     if (st != DX_OK)
         return st;
     h->launches.fetch_add(1);
+    // Grouped heads over an 8-bit cache, up to 64 new tokens: the (token, head) rows of a kv head share one pass
+    // over the cache on the tensor-core grouped-head kernel, 16 rows per CTA, split-K and merge as on the plain
+    // path.  Needs room for the partials behind the bias / rotary copy; without it the per-row kernel below runs.
+    const int QG = Q * h->group;
+    const KernelInfo& km = h->k_gqa_multi[QG > 8 ? 1 : 0];
+    if (h->feature_gqa && !h->general_only && h->group > 1 && Q <= 64 && c.tokens_per_block >= 32 && km.fn)
+    {
+        Plan plan;
+        plan.kind = KIND_GQA;
+        plan.hgroups = (QG + 15) / 16;
+        plan.heads16 = QG > 8;
+        const int rows_per_seq = c.num_kv_heads * plan.hgroups;
+        plan.rows = p.num_requests * rows_per_seq;
+        plan.resident = std::max(1, km.resident);
+        plan_partitions(h, plan, p.num_requests, rows_per_seq, (int) need - 1, nullptr);
+        const size_t qrows = (size_t) rows * c.num_heads;
+        plan.part_o_bytes = plan.nsplit > 1 ? align_up(qrows * plan.nsplit * c.head_size * sizeof(float), 128) : 0;
+        plan.part_ml_bytes = plan.nsplit > 1 ? align_up(qrows * plan.nsplit * sizeof(float2), 128) : 0;
+        const bool room = plan.nsplit == 1
+            || (p.workspace && !((uintptr_t) p.workspace & 127) && p.workspace_bytes >= prep + plan.workspace());
+        if (room && (int64_t) c.num_kv_heads * plan.hgroups <= 65535)
+        {
+            char* const ws_partials = reinterpret_cast<char*>(p.workspace) + prep;
+            AttnArgs a{};
+            a.qkv = g.qkv;
+            a.out = p.context_buf;
+            a.seq_len = p.sequence_lengths;
+            a.block_ptrs = p.block_pointers;
+            a.scale_orig_quant = p.kv_scale_orig_quant;
+            a.scale_quant_orig = p.kv_scale_quant_orig;
+            a.part_o = plan.nsplit > 1 ? reinterpret_cast<float*>(ws_partials) : nullptr;
+            a.part_ml = plan.nsplit > 1 ? reinterpret_cast<float2*>(ws_partials + plan.part_o_bytes) : nullptr;
+            a.status = h->status_dev;
+            a.batch = p.num_requests;
+            a.num_heads = c.num_heads;
+            a.num_kv_heads = c.num_kv_heads;
+            a.max_blocks_per_seq = p.max_blocks_per_sequence;
+            a.tpb_log2 = h->tpb_log2;
+            a.chunk_tokens = plan.chunk_tokens;
+            a.nsplit = plan.nsplit;
+            a.softmax_scale_log2 = g.softmax_scale_log2;
+            a.guard = h->guard;
+            a.q_len = Q;
+            a.packed_mask = p.medusa_packed_mask;
+            int hgroups = plan.hgroups;
+            void* kargs[] = {&a, &hgroups, &h->sk_zero};
+            st = check_cuda(h, cudaLaunchKernel(km.fn, dim3(plan.nsplit, c.num_kv_heads * plan.hgroups, p.num_requests),
+                                   dim3(km.threads), kargs, (size_t) km.smem, stream));
+            if (st != DX_OK)
+                return st;
+            h->launches.fetch_add(1);
+            if (plan.nsplit > 1)
+            {
+                void* margs[] = {&a};
+                cudaLaunchConfig_t cfg{};
+                cfg.gridDim = dim3((unsigned) ((qrows + 3) / 4));
+                cfg.blockDim = dim3(128);
+                cfg.stream = stream;
+                cudaLaunchAttribute attr[1];
+                attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+                attr[0].val.programmaticStreamSerializationAllowed = 1;
+                cfg.attrs = attr;
+                cfg.numAttrs = 1;
+                st = check_cuda(h, cudaLaunchKernelExC(&cfg, h->k_merge.fn, margs));
+                if (st != DX_OK)
+                    return st;
+                h->launches.fetch_add(1);
+            }
+            return DX_OK;
+        }
+    }
     st = check_cuda(h, cudaLaunchKernel(h->k_general.multi, dim3(c.num_heads, rows), dim3(128), args,
                            (size_t) h->k_general.smem, stream));
     if (st != DX_OK)
@@ -995,6 +1067,9 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
             h->k_gqa_feat[i] = gqa_feature_kernel_info(c.type_id, h->cache_kind, c.head_size, i != 0);
             if (!h->k_gqa_feat[i].fn || set_smem(h, h->k_gqa_feat[i]) != DX_OK)
                 h->feature_gqa = false;
+            h->k_gqa_multi[i] = gqa_multi_token_kernel_info(c.type_id, h->cache_kind, c.head_size, i != 0);
+            if (h->k_gqa_multi[i].fn && set_smem(h, h->k_gqa_multi[i]) != DX_OK)
+                h->k_gqa_multi[i] = KernelInfo{};
         }
     }
     else

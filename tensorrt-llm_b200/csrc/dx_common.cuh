@@ -56,6 +56,10 @@ struct AttnArgs
     const void* alibi_slopes;       // T [H]
     int32_t beam_width;
     int32_t max_attention_window;
+    // Several new tokens per sequence on the grouped-head kernel (q_len > 1): the rows of a kv head are (token, head)
+    // pairs, token-major; every new token is in the cache already; packed_mask as in GeneralArgs
+    int32_t q_len;
+    const int32_t* packed_mask;
     int32_t cyclic_window; // > 0: the cache is cyclic; the kernels walk slots 0 .. min(past, cyclic_window) - 1 and the
                            // new token is appended behind them by kv_append_token_kernel (0 on the plain path)
 };

@@ -16,29 +16,30 @@ static KernelInfo mk()
     return k;
 }
 
-// The feature form (beam search, ALiBi) of the same kernel: classic launches only.
-template <typename T, int CACHE, int DH, bool H16>
+// The feature forms of the same kernel (FEAT 1: beam search, cyclic window, ALiBi; FEAT 2: several new tokens per
+// sequence): classic launches only.
+template <typename T, int CACHE, int DH, bool H16, int FEAT>
 static KernelInfo mk_feature()
 {
     KernelInfo k;
-    k.fn = reinterpret_cast<const void*>(&gqa_decode_kernel<T, CACHE, DH, H16, 4, true>);
+    k.fn = reinterpret_cast<const void*>(&gqa_decode_kernel<T, CACHE, DH, H16, 4, FEAT>);
     k.smem = GqaTraits<DH, gqa_min_blocks<CACHE, DH, H16>()>::SMEM_BYTES;
     k.resident = gqa_min_blocks<CACHE, DH, H16>();
     return k;
 }
 
-template <typename T, bool H16>
+template <typename T, bool H16, int FEAT>
 static KernelInfo feature_by_cache_dh(int cache, int dh)
 {
     if (dh == 64)
     {
-        if (cache == CACHE_INT8) return mk_feature<T, CACHE_INT8, 64, H16>();
-        if (cache == CACHE_FP8) return mk_feature<T, CACHE_FP8, 64, H16>();
+        if (cache == CACHE_INT8) return mk_feature<T, CACHE_INT8, 64, H16, FEAT>();
+        if (cache == CACHE_FP8) return mk_feature<T, CACHE_FP8, 64, H16, FEAT>();
     }
     else if (dh == 128)
     {
-        if (cache == CACHE_INT8) return mk_feature<T, CACHE_INT8, 128, H16>();
-        if (cache == CACHE_FP8) return mk_feature<T, CACHE_FP8, 128, H16>();
+        if (cache == CACHE_INT8) return mk_feature<T, CACHE_INT8, 128, H16, FEAT>();
+        if (cache == CACHE_FP8) return mk_feature<T, CACHE_FP8, 128, H16, FEAT>();
     }
     return KernelInfo{};
 }
@@ -46,8 +47,15 @@ static KernelInfo feature_by_cache_dh(int cache, int dh)
 KernelInfo gqa_feature_kernel_info(int dtype, int cache, int dh, bool heads16)
 {
     if (dtype == 0)
-        return heads16 ? feature_by_cache_dh<__half, true>(cache, dh) : feature_by_cache_dh<__half, false>(cache, dh);
-    return heads16 ? feature_by_cache_dh<__nv_bfloat16, true>(cache, dh) : feature_by_cache_dh<__nv_bfloat16, false>(cache, dh);
+        return heads16 ? feature_by_cache_dh<__half, true, 1>(cache, dh) : feature_by_cache_dh<__half, false, 1>(cache, dh);
+    return heads16 ? feature_by_cache_dh<__nv_bfloat16, true, 1>(cache, dh) : feature_by_cache_dh<__nv_bfloat16, false, 1>(cache, dh);
+}
+
+KernelInfo gqa_multi_token_kernel_info(int dtype, int cache, int dh, bool heads16)
+{
+    if (dtype == 0)
+        return heads16 ? feature_by_cache_dh<__half, true, 2>(cache, dh) : feature_by_cache_dh<__half, false, 2>(cache, dh);
+    return heads16 ? feature_by_cache_dh<__nv_bfloat16, true, 2>(cache, dh) : feature_by_cache_dh<__nv_bfloat16, false, 2>(cache, dh);
 }
 
 // 16-bit cache: one kernel for any group size up to 16 heads per CTA

@@ -199,12 +199,16 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr)
     return v;
 }
 
-// FEAT: the feature form (classic launches only).  Beam search: cache slot s of sequence b is read from sequence
+// FEAT = 1: the feature form (classic launches only).  Beam search: cache slot s of sequence b is read from sequence
 // request * beam_width + (s < context_lengths[b] ? 0 : cache_indir[b][s]), so every token row of a group has its own
 // source block (decoderMaskedMultiheadAttentionTemplate.h:1497-1498, :2063-2078).  Cyclic cache: the kernel walks
 // slots 0 .. min(past, window) - 1 as they are (:1493).  The new token is taken from the QKV row as it will be stored and
 // appended by kv_append_token_kernel behind this kernel (its slot may be one that is read in this step).  ALiBi: score += slope[head] * (s - past), nothing for the new token (:1797, :2026).
-template <typename T, int CACHE, int DH, bool H16, int WARPS = 4, bool FEAT = false>
+// FEAT = 2: several new tokens per sequence (the reference's Medusa mode; classic launches only).  The new tokens are in
+// the cache already (kv_append_token_kernel runs first); the rows of a kv head are its q_len x G (token, head) pairs,
+// token-major, cut into 16-row slices (hg), so one pass over the cache serves 16 of them; row (t, h) attends to
+// the cache entries before the step and to new token j where bit j of its packed mask row is set.
+template <typename T, int CACHE, int DH, bool H16, int WARPS = 4, int FEAT = 0>
 __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WARPS>())
     gqa_decode_kernel(const AttnArgs a, const int hgroups, const __grid_constant__ SkSchedule sk)
 {
@@ -237,7 +241,7 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
     else
     {
         int cs, ct, np;
-        partition_of(FEAT ? attended_tokens(a.seq_len[blockIdx.z], a.cyclic_window) : a.seq_len[blockIdx.z], a.chunk_tokens,
+        partition_of(FEAT == 1 ? attended_tokens(a.seq_len[blockIdx.z], a.cyclic_window) : a.seq_len[blockIdx.z], a.chunk_tokens,
             (int) blockIdx.x, cs, ct, np);
         if (np > (int) gridDim.x && blockIdx.x == 0 && threadIdx.x == 0)
             report_status(a.status, STATUS_PLAN_EXCEEDED); // the tokens beyond the last partition are not attended to
@@ -278,12 +282,33 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
         {
             int np;
             chunk = blockIdx.x, hk = blockIdx.y / hgroups, hg = blockIdx.y % hgroups, b = blockIdx.z;
-            partition_of(FEAT ? attended_tokens(a.seq_len[b], a.cyclic_window) : a.seq_len[b], a.chunk_tokens, chunk,
+            partition_of(FEAT == 1 ? attended_tokens(a.seq_len[b], a.cyclic_window) : a.seq_len[b], a.chunk_tokens, chunk,
                 chunk_start, ctoks, np);
             final_out = a.nsplit == 1;
         }
-        const int nh = min(16, G - hg * 16); // q heads handled in this piece
-        const int head0 = hk * G + hg * 16;  // first of them
+        const int nh = min(16, (FEAT == 2 ? G * a.q_len : G) - hg * 16); // q rows handled in this piece
+        const int head0 = hk * G + hg * 16;  // first of them (FEAT = 2: see row_token / row_head)
+        // FEAT = 2: row hl of the slice is new token (hg * 16 + hl) / G, head (hg * 16 + hl) % G of the kv head
+        auto q_row_of = [&](int hl) -> size_t
+        {
+            if constexpr (FEAT == 2)
+            {
+                const int R = hg * 16 + hl, tk = R / G;
+                return ((size_t) b * a.q_len + tk) * (size_t) ((a.num_heads + 2 * a.num_kv_heads) * DH) + (size_t) (hk * G + R - tk * G) * DH;
+            }
+            else
+                return (size_t) b * (size_t) ((a.num_heads + 2 * a.num_kv_heads) * DH) + (size_t) (head0 + hl) * DH;
+        };
+        auto out_row_of = [&](int hl) -> size_t
+        {
+            if constexpr (FEAT == 2)
+            {
+                const int R = hg * 16 + hl, tk = R / G;
+                return ((size_t) b * a.q_len + tk) * a.num_heads + (size_t) (hk * G + R - tk * G);
+            }
+            else
+                return (size_t) b * a.num_heads + head0 + hl;
+        };
         // The q rows of this thread are requested before anything else of the piece: behind the first ring
         // stages of K / V (tens of KB per warp) the same loads would wait for all of those bytes.
         const int qkv_stride = (a.num_heads + 2 * a.num_kv_heads) * DH;
@@ -293,7 +318,7 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
         for (int r = 0; r < NR; ++r)
         {
             const int hl = g + 8 * r; // head within this CTA
-            const T* qp = qkv_b + (size_t) (head0 + min(hl, nh - 1)) * DH + t * QV;
+            const T* qp = reinterpret_cast<const T*>(a.qkv) + q_row_of(min(hl, nh - 1)) + t * QV;
 #pragma unroll
             for (int i = 0; i < QV / 8; ++i)
                 q_raw[r][i] = *reinterpret_cast<const uint4*>(qp + 8 * i);
@@ -301,12 +326,29 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
         const float deq = __ldg(a.scale_quant_orig);
         // (feature form: `total` counts the cache slots walked plus the new token; past_true is the real history)
         const int past_true = a.seq_len[b] - 1;
-        const int total = FEAT ? attended_tokens(past_true + 1, a.cyclic_window) : past_true + 1;
+        const int total = FEAT == 1 ? attended_tokens(past_true + 1, a.cyclic_window) : past_true + 1;
         if (a.streamk && total > (int) cur.nb * TG && threadIdx.x == 0)
             report_status(a.status, STATUS_PLAN_EXCEEDED); // longer than the host length the ranges were laid out for
         ctoks = max(0, min(ctoks, total - chunk_start)); // the schedule counts host lengths; the device length decides
         const int n_groups = (ctoks + TG - 1) / TG;
-        const int new_pos = total - 1;
+        // (FEAT = 2: nothing is staged, every token up to `total` is read from the cache)
+        const int new_pos = FEAT == 2 ? total : total - 1;
+        // FEAT = 2: packed mask words of this thread's rows (q_len <= 64) and the first new token
+        uint32_t mw[NR][2];
+        int first_new = 0;
+        if constexpr (FEAT == 2)
+        {
+            first_new = total - a.q_len;
+            const int words = (a.q_len + 31) >> 5;
+#pragma unroll
+            for (int r = 0; r < NR; ++r)
+            {
+                const int tk = (hg * 16 + min(g + 8 * r, nh - 1)) / G;
+                const int32_t* mrow = a.packed_mask + ((size_t) b * a.q_len + tk) * words;
+                mw[r][0] = (uint32_t) __ldg(mrow);
+                mw[r][1] = words > 1 ? (uint32_t) __ldg(mrow + 1) : 0u;
+            }
+        }
 
         const int64_t* krow = a.block_ptrs + (int64_t) b * 2 * a.max_blocks_per_seq;
         const int64_t* vrow = krow + a.max_blocks_per_seq;
@@ -318,7 +360,7 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
 #pragma unroll
         for (int r = 0; r < NR; ++r)
             slope[r] = 0.f;
-        if constexpr (FEAT)
+        if constexpr (FEAT == 1)
         {
             if (a.cache_indir != nullptr && a.beam_width > 1)
             {
@@ -349,7 +391,7 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
             const int t0 = chunk_start + gi * TG;
             const int rows = new_pos - t0; // rows already in the cache (>= TG for all but the last group)
             const uint32_t kdst = ring_u32 + ((ring_base + i) % STAGES) * Tr::STAGE_BYTES;
-            if constexpr (FEAT)
+            if constexpr (FEAT == 1)
             {
                 // every 16-byte piece looks up the block of its own token row
 #pragma unroll
@@ -570,7 +612,7 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
             const int gi = warp + NWARPS * i;
             const int t0 = chunk_start + gi * TG;
             const int lim = total - t0; // valid tokens in this group if < TG
-            if (new_pos < t0 + TG)
+            if (FEAT != 2 && new_pos < t0 + TG)
             {
                 // The group ends with the new token: quantise it exactly as it is stored, put it into
                 // the staged tile (rows behind it were zero-filled by the copies) and, from the first
@@ -588,7 +630,7 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
                     unsigned char* stage = smem + warp * (STAGES * Tr::STAGE_BYTES) + s * Tr::STAGE_BYTES;
                     *reinterpret_cast<uint4*>(stage + lin) = kq;
                     *reinterpret_cast<uint4*>(stage + SLAB + lin) = vq;
-                    if (!FEAT && hg == 0) // (feature form: kv_append_token_kernel stores the token behind this kernel)
+                    if (FEAT == 0 && hg == 0) // (feature form: kv_append_token_kernel stores the token behind this kernel)
                     {
                         const size_t off = head_off + (size_t) (new_pos & tpb_mask) * DH + lane * 16;
                         char* kb = reinterpret_cast<char*>(table_entry(krow, new_pos >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
@@ -663,11 +705,26 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
                     else
                         sv = (float) (sacc[0][nt][c] * kLoWeight + sacc[0][nt][c + 2]);
                     p[nt][c] = sv * sfac[c >> 1];
-                    if constexpr (FEAT)
+                    if constexpr (FEAT == 1)
                     {
                         const int tok = t0 + sigma_row<DH>(nt, 2 * t + (c & 1));
                         p[nt][c] = fmaf(slope[c >> 1], tok == new_pos ? 0.f : (float) (tok - past_true), p[nt][c]);
                     }
+                }
+            }
+            if constexpr (FEAT == 2)
+            {
+                if (t0 + TG > first_new) // the group holds new tokens: each row sees those its mask row names
+                {
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                        for (int c = 0; c < 2 * NR; ++c)
+                        {
+                            const int j = t0 + sigma_row<DH>(nt, 2 * t + (c & 1)) - first_new;
+                            if (j >= 0 && j < 64 && (((j < 32 ? mw[c >> 1][0] : mw[c >> 1][1]) >> (j & 31)) & 1u) == 0u)
+                                p[nt][c] = -INFINITY;
+                        }
                 }
             }
             if (lim < TG)
@@ -684,7 +741,7 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
 #pragma unroll
                 for (int c = 0; c < 2 * NR; ++c)
                     mx[c >> 1] = fmaxf(mx[c >> 1], p[nt][c]);
-            float alpha[NR];
+            float alpha[NR], msub[NR];
             bool changed = false;
 #pragma unroll
             for (int r = 0; r < NR; ++r)
@@ -692,7 +749,9 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
                 const float m_new = fmaxf(m[r], mx[r]);
-                alpha[r] = fast_exp2(m[r] - m_new);
+                // (FEAT = 2: under its mask a row may have seen nothing yet; -inf minus -inf must not reach exp2)
+                msub[r] = (FEAT == 2 && m_new == -INFINITY) ? 0.f : m_new;
+                alpha[r] = fast_exp2(m[r] - msub[r]);
                 changed |= m_new != m[r];
                 m[r] = m_new;
                 l[r] *= alpha[r];
@@ -711,7 +770,7 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4)
                     {
-                        pv[q4] = fast_exp2(p[2 * kh + (q4 >> 1)][2 * r + (q4 & 1)] - m[r]);
+                        pv[q4] = fast_exp2(p[2 * kh + (q4 >> 1)][2 * r + (q4 & 1)] - msub[r]);
                         l[r] += pv[q4];
                     }
                     if constexpr (IS_FP8)
@@ -865,7 +924,7 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
                 L = fmaf(wb[16 * DH + 16 + head], f, L);
                 o = fmaf(wb[head * DH + dh], f, o);
             }
-            const size_t row = (size_t) b * a.num_heads + head0 + head;
+            const size_t row = out_row_of(head);
             if (final_out)
             {
                 reinterpret_cast<T*>(a.out)[row * DH + dh] = TypeOps<T>::from_float(o * ofac / L);

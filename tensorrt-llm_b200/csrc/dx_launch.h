@@ -17,6 +17,7 @@ KernelInfo mha_kernel_info(int dtype, int cache, int dh, int tokens_per_block);
 KernelInfo gqa_kernel_info(int dtype, int cache, int dh, bool heads16);
 KernelInfo gqa_streamk_kernel_info(int dtype, int cache, int dh, bool heads16); // 6-warp CTAs; empty where not built
 KernelInfo gqa_feature_kernel_info(int dtype, int cache, int dh, bool heads16); // beam search / ALiBi form, 8-bit caches
+KernelInfo gqa_multi_token_kernel_info(int dtype, int cache, int dh, bool heads16); // several new tokens per sequence
 KernelInfo wide_kernel_info(int dtype, int dh); // FP8 cache only
 KernelInfo tok_kernel_info(int dtype, int dh, int group); // FP8 cache, Dh 128, group <= 16
 KernelInfo tokws_kernel_info(int dtype, int dh, int group); // the persistent warp-specialised form of it

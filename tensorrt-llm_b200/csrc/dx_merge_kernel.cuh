@@ -131,9 +131,9 @@ __global__ void __launch_bounds__(128) lse_merge_kernel(const AttnArgs a)
 {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * 4 + warp; // b * H + h
-    if (row >= a.batch * a.num_heads)
+    if (row >= a.batch * a.num_heads * max(1, a.q_len))
         return;
-    const int b = row / a.num_heads;
+    const int b = row / (a.num_heads * max(1, a.q_len)); // (q_len > 1: rows are (sequence, new token, head))
     const int total = attended_tokens(a.seq_len[b], a.cyclic_window);
     griddep_wait(); // launched with programmatic stream serialisation: the partials are complete after this
     // partitions this sequence used (partition_of), never more than the launch had and never fewer than one: a

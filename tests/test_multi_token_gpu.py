@@ -154,3 +154,79 @@ def test_what_the_mode_does_not_cover_is_refused(pkg):
     with pytest.raises(P.DecodeAttnError) as e:
         _run(pkg, short, packed, max_attention_window=4096)
     assert e.value.status == P.DX_ERR_BAD_ARG
+
+
+@pytest.mark.parametrize("tree", ["small", "wide"])
+@pytest.mark.parametrize("dtype,cache,heads,dh,tpb,lo,hi", [
+    (torch.bfloat16, "fp8", (16, 2), 128, 64, 3000, 6000),    # split-K partitions, 8 heads per kv head
+    (torch.bfloat16, "int8", (8, 1), 128, 32, 0, 500),        # MQA: all rows on one kv head
+    (torch.float16, "fp8", (24, 2), 64, 128, 0, 900),         # 12 heads per kv head: tokens straddle the 16-row slices
+    (torch.float16, "int8", (4, 2), 64, 64, 0, 200),          # 2 heads per kv head
+])
+def test_grouped_rows_kernel_against_oracle_and_the_per_row_kernel(pkg, tree, dtype, cache, heads, dh, tpb, lo, hi,
+                                                                   monkeypatch):
+    """Grouped heads over an 8-bit cache run on the grouped-head kernel with (token, head) rows (the default); the
+    same call with DX_ATTN_FEATURE_GQA=0 runs one CTA per row.  Both against the oracle; identical pool bytes."""
+    cfg = workloads.DecodeConfig("mtg", 3, heads[0], heads[1], dh, dtype, cache, tpb, lo, hi, True, 311)
+    packed, _ = _tree(tree, cfg.batch)
+    q_len = packed.shape[1]
+    pasts = workloads.draw_lengths(cfg)
+    pasts[0] = lo  # (0 where lo is 0: a sequence with nothing but the new tokens)
+    w = _workload(pkg, cfg, q_len, pasts)
+    ref, pool_ref = _oracle(w, packed)
+    out, pool = _run(pkg, w, packed)
+    assert torch.equal(pool, pool_ref)
+    err = (out - ref).abs()
+    assert torch.isfinite(out).all()
+    assert err.max().item() < MAX_ABS_TOL and err.mean().item() < MEAN_ABS_TOL, (err.max().item(), err.mean().item())
+    monkeypatch.setenv("DX_ATTN_FEATURE_GQA", "0")
+    out_b, pool_b = _run(pkg, w, packed)
+    assert torch.equal(pool_b, pool_ref)
+    err = (out - out_b).abs()
+    assert err.max().item() < MAX_ABS_TOL and err.mean().item() < MEAN_ABS_TOL, (err.max().item(), err.mean().item())
+
+
+@pytest.mark.parametrize("grouped", [True, False])
+def test_report_multi_token_time(pkg, grouped, monkeypatch):
+    """Times a 37-token draft tree on a batch of c4's shape (32 sequences) on the grouped-rows kernel and on the per-row
+    kernel; recorded in feature_path.jsonl of the report directory."""
+    import json
+    import os
+    from helpers import REPORT_DIR
+    if not grouped:
+        monkeypatch.setenv("DX_ATTN_FEATURE_GQA", "0")
+    cfg = workloads.DecodeConfig("mtt", 32, 64, 8, 128, torch.bfloat16, "fp8", 64, 2048, 4096, True, 312)
+    packed, _ = _tree("wide", cfg.batch)
+    q_len = packed.shape[1]
+    w_cpu = _workload(pkg, cfg, q_len)
+    w = workloads.to_device(w_cpu, "cuda:0")
+    plugin = pkg.GPTAttentionPlugin(num_heads=64, num_kv_heads=8, head_size=128, multi_block_mode=True,
+                                    kv_cache_quant_mode=cfg.quant_mode, tokens_per_block=64, type_id=cfg.dtype, device=0)
+    try:
+        pm = packed.cuda()
+        out = torch.empty(cfg.batch * q_len, 64 * 128, dtype=cfg.dtype, device="cuda:0")
+
+        def step():
+            plugin.enqueue_generation(w.qkv, w.sequence_length, w.host_past_key_value_lengths,
+                                      w.kv_cache_block_pointers, w.kv_orig_quant_scale, w.kv_quant_orig_scale, out=out,
+                                      medusa_packed_mask=pm)
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(10):
+            step()
+        b.record()
+        torch.cuda.synchronize()
+        assert plugin.device_status() == 0
+        us = a.elapsed_time(b) / 10 * 1e3
+        kv = float(w_cpu.sequence_length.double().sum() * 8 * 128 * 2)
+        rec = {"case": f"{q_len} draft tokens x 32 sequences, 64 q / 8 kv heads, Dh 128, FP8, past 2048-4096, "
+                       + ("grouped rows" if grouped else "one CTA per row"), "us": us, "unique_kv_GBps": kv / us / 1e3}
+        os.makedirs(REPORT_DIR, exist_ok=True)
+        with open(os.path.join(REPORT_DIR, "feature_path.jsonl"), "a") as f:
+            f.write(json.dumps(rec) + "\n")
+        print(rec)
+    finally:
+        plugin.close()
