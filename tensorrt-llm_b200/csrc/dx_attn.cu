@@ -71,7 +71,7 @@ struct dx_attn
     int min_chunk = 256;         // smallest partition bound, tokens
     int fixed_cost_tokens = 400; // per-CTA fixed cost (prologue, pipeline fill, epilogue) in tokens of streaming time
     KernelInfo k_mha{}, k_gqa[2]{}, k_wide{}, k_tok{}, k_merge{}, k_append{}; // k_gqa[16 heads per CTA?]
-    KernelInfo k_gqa_feat[2]{}; // feature form of k_gqa (beam search, ALiBi), 8-bit caches
+    KernelInfo k_gqa_feat[2]{}; // feature form of k_gqa (beam search, cyclic window, ALiBi)
     KernelInfo k_gqa_multi[2]{}; // several-new-tokens form of k_gqa (rows = (token, head) pairs of a kv head)
     bool feature_gqa = true;    // beams / ALiBi on grouped heads run on it (0: on the per-head feature kernel)
     KernelInfo k_gqa_six{}; // stream-K form of k_gqa[0] with two six-warp CTAs per SM (where built)
@@ -847,7 +847,8 @@ int enqueue_multi_token(dx_attn* h, const dx_attn_generation_params& p, int max_
     // path.  Needs room for the partials behind the bias / rotary copy; without it the per-row kernel below runs.
     const int QG = Q * h->group;
     const KernelInfo& km = h->k_gqa_multi[QG > 8 ? 1 : 0];
-    if (h->feature_gqa && !h->general_only && h->group > 1 && Q <= 64 && c.tokens_per_block >= 32 && km.fn)
+    if (h->feature_gqa && !h->general_only && h->group > 1 && Q <= 64
+        && c.tokens_per_block >= (h->cache_kind == CACHE_T ? 16 : 32) && km.fn)
     {
         Plan plan;
         plan.kind = KIND_GQA;
@@ -1058,7 +1059,7 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
         st = set_smem(h, h->k_mha);
     for (int i = 0; i < 2 && st == DX_OK; ++i)
         st = set_smem(h, h->k_gqa[i]);
-    if (st == DX_OK && h->cache_kind != CACHE_T && h->k_gqa[0].fn)
+    if (st == DX_OK && h->k_gqa[0].fn)
     {
         if (const char* w = getenv("DX_ATTN_FEATURE_GQA"))
             h->feature_gqa = atoi(w) != 0;
@@ -1297,8 +1298,8 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     const bool general = h->general_only || p.beam_width > 1 || p.sink_token_length > 0 || alibi || relative
         || p.cyclic_attention_window_size < max_past + 1 || p.max_attention_window < max_past + 1;
     // beams / windows / sinks / ALiBi over grouped heads with an 8-bit cache share the cache reads of a kv head
-    if (general && h->feature_gqa && !h->general_only && h->group > 1 && c.tokens_per_block >= 32 && !relative
-        && h->k_general.append)
+    if (general && h->feature_gqa && !h->general_only && h->group > 1
+        && c.tokens_per_block >= (h->cache_kind == CACHE_T ? 16 : 32) && !relative && h->k_general.append)
         return enqueue_feature_gqa(h, p, max_past, cuda_stream);
     if (general)
         return enqueue_general(h, p, max_past, cuda_stream);

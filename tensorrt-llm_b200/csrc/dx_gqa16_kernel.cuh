@@ -80,7 +80,10 @@ __device__ __forceinline__ void mma_16bit(float (&d)[4], const uint32_t (&a)[4],
     }
 }
 
-template <typename T, int DH>
+// FEAT = 1 / 2: the feature forms, as in gqa_decode_kernel (dx_gqa_kernel.cuh): beam search / cyclic window / ALiBi with
+// a per-row source block and the new token appended by kv_append_token_kernel; several new tokens per sequence as
+// (token, head) rows under the packed mask.  Classic launches only.
+template <typename T, int DH, int FEAT = 0>
 __global__ void __launch_bounds__(128, Gqa16Traits<DH>::MIN_BLOCKS) gqa16_decode_kernel(const AttnArgs a, const int hgroups, const __grid_constant__ SkSchedule sk)
 {
     using Tr = Gqa16Traits<DH>;
@@ -106,7 +109,8 @@ __global__ void __launch_bounds__(128, Gqa16Traits<DH>::MIN_BLOCKS) gqa16_decode
     else
     {
         int cs, ct, np;
-        partition_of(a.seq_len[blockIdx.z], a.chunk_tokens, (int) blockIdx.x, cs, ct, np);
+        partition_of(FEAT == 1 ? attended_tokens(a.seq_len[blockIdx.z], a.cyclic_window) : a.seq_len[blockIdx.z], a.chunk_tokens,
+            (int) blockIdx.x, cs, ct, np);
         if (np > (int) gridDim.x && blockIdx.x == 0 && threadIdx.x == 0)
             report_status(a.status, STATUS_PLAN_EXCEEDED); // the tokens beyond the last partition are not attended to
         if ((int) blockIdx.x >= np)
@@ -146,17 +150,74 @@ __global__ void __launch_bounds__(128, Gqa16Traits<DH>::MIN_BLOCKS) gqa16_decode
         {
             int np;
             chunk = blockIdx.x, hk = blockIdx.y / hgroups, hg = blockIdx.y % hgroups, b = blockIdx.z;
-            partition_of(a.seq_len[b], a.chunk_tokens, chunk, chunk_start, ctoks, np);
+            partition_of(FEAT == 1 ? attended_tokens(a.seq_len[b], a.cyclic_window) : a.seq_len[b], a.chunk_tokens, chunk,
+                chunk_start, ctoks, np);
             final_out = a.nsplit == 1;
         }
-        const int total = a.seq_len[b];
+        const int past_true = a.seq_len[b] - 1;
+        const int total = FEAT == 1 ? attended_tokens(past_true + 1, a.cyclic_window) : past_true + 1;
         if (a.streamk && total > (int) cur.nb * TG && threadIdx.x == 0)
             report_status(a.status, STATUS_PLAN_EXCEEDED); // longer than the host length the ranges were laid out for
         ctoks = max(0, min(ctoks, total - chunk_start)); // the schedule counts host lengths; the device length decides
         const int n_groups = (ctoks + TG - 1) / TG;
-        const int new_pos = total - 1;
-        const int nh = min(16, G - hg * 16); // q heads handled in this piece
+        const int new_pos = FEAT == 2 ? total : total - 1; // (FEAT = 2: nothing is staged, everything comes from the cache)
+        const int nh = min(16, (FEAT == 2 ? G * a.q_len : G) - hg * 16); // q rows handled in this piece
         const int head0 = hk * G + hg * 16;  // first of them
+        // FEAT = 2: row hl of the slice is new token (hg * 16 + hl) / G, head (hg * 16 + hl) % G of the kv head
+        auto q_row_of = [&](int hl) -> size_t
+        {
+            if constexpr (FEAT == 2)
+            {
+                const int R = hg * 16 + hl, tk = R / G;
+                return ((size_t) b * a.q_len + tk) * (size_t) ((a.num_heads + 2 * a.num_kv_heads) * DH) + (size_t) (hk * G + R - tk * G) * DH;
+            }
+            else
+                return (size_t) b * (size_t) ((a.num_heads + 2 * a.num_kv_heads) * DH) + (size_t) (head0 + hl) * DH;
+        };
+        auto out_row_of = [&](int hl) -> size_t
+        {
+            if constexpr (FEAT == 2)
+            {
+                const int R = hg * 16 + hl, tk = R / G;
+                return ((size_t) b * a.q_len + tk) * a.num_heads + (size_t) (hk * G + R - tk * G);
+            }
+            else
+                return (size_t) b * a.num_heads + head0 + hl;
+        };
+        // feature forms: source of a slot (beam search), ALiBi slopes of rows g and g + 8 (log2 units), mask words
+        int seq0 = b, ctx0 = 0, first_new = 0;
+        const int32_t* indir = nullptr;
+        float slope[2] = {0.f, 0.f};
+        uint32_t mw[2][2] = {{0u, 0u}, {0u, 0u}};
+        if constexpr (FEAT == 1)
+        {
+            if (a.cache_indir != nullptr && a.beam_width > 1)
+            {
+                seq0 = (b / a.beam_width) * a.beam_width;
+                ctx0 = (a.cyclic_window > 0 && past_true > a.cyclic_window) ? 0 : a.context_lengths[b];
+                indir = a.cache_indir + (size_t) b * a.max_attention_window;
+            }
+            if (a.alibi_slopes != nullptr)
+            {
+#pragma unroll
+                for (int r = 0; r < 2; ++r)
+                    slope[r] = TypeOps<T>::to_float(reinterpret_cast<const T*>(a.alibi_slopes)[head0 + min(g + 8 * r, nh - 1)])
+                        * 1.4426950408889634f;
+            }
+        }
+        if constexpr (FEAT == 2)
+        {
+            first_new = total - a.q_len;
+            const int words = (a.q_len + 31) >> 5;
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+            {
+                const int tk = (hg * 16 + min(g + 8 * r, nh - 1)) / G;
+                const int32_t* mrow = a.packed_mask + ((size_t) b * a.q_len + tk) * words;
+                mw[r][0] = (uint32_t) __ldg(mrow);
+                mw[r][1] = words > 1 ? (uint32_t) __ldg(mrow + 1) : 0u;
+            }
+        }
 
         const int64_t* krow = a.block_ptrs + (int64_t) b * 2 * a.max_blocks_per_seq;
         const int64_t* vrow = krow + a.max_blocks_per_seq;
@@ -175,6 +236,29 @@ __global__ void __launch_bounds__(128, Gqa16Traits<DH>::MIN_BLOCKS) gqa16_decode
             const int t0 = chunk_start + gi * TG;
             const int rows = new_pos - t0; // rows already in the cache (>= TG for all but the last group)
             const uint32_t kdst = ring_u32 + ((ring_base + i) % STAGES) * Tr::STAGE_BYTES;
+            if constexpr (FEAT == 1)
+            {
+                // every 16-byte piece looks up the block of its own token row
+#pragma unroll
+                for (int j = 0; j < NCP; ++j)
+                {
+                    const int piece = lane + 32 * j;
+                    const int s = t0 + piece / CPR;
+                    const bool ok = s < new_pos;
+                    const int sc = ok ? s : 0;
+                    const int seq = (indir != nullptr && sc >= ctx0) ? seq0 + __ldg(indir + sc) : seq0;
+                    const int64_t* srow = a.block_ptrs + (int64_t) seq * 2 * a.max_blocks_per_seq;
+                    const size_t o = head_off + (size_t) (sc & tpb_mask) * ROW + (piece % CPR) * 16;
+                    const char* ks = reinterpret_cast<const char*>(
+                        table_entry(srow, sc >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + o;
+                    const char* vs = reinterpret_cast<const char*>(
+                        table_entry(srow + a.max_blocks_per_seq, sc >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + o;
+                    cp_async16_zfill_u32(kdst + cdst[j], ks, ok ? 16u : 0u);
+                    cp_async16_zfill_u32(kdst + SLAB + cdst[j], vs, ok ? 16u : 0u);
+                }
+                cp_async_mbar_arrive_noinc(&bars[(ring_base + i) % STAGES]);
+                return;
+            }
             const size_t off = head_off + (size_t) (t0 & tpb_mask) * ROW + lane * 16;
             const char* kb = reinterpret_cast<const char*>(table_entry(krow, t0 >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
             const char* vb = reinterpret_cast<const char*>(table_entry(vrow, t0 >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
@@ -208,8 +292,8 @@ __global__ void __launch_bounds__(128, Gqa16Traits<DH>::MIN_BLOCKS) gqa16_decode
         const T* qkv_b = reinterpret_cast<const T*>(a.qkv) + (size_t) b * qkv_stride;
         uint32_t qa[KSTEPS][4];
         {
-            const uint32_t* q0 = reinterpret_cast<const uint32_t*>(qkv_b + (size_t) (head0 + g) * DH);
-            const uint32_t* q1 = reinterpret_cast<const uint32_t*>(qkv_b + (size_t) (head0 + g + 8) * DH);
+            const uint32_t* q0 = reinterpret_cast<const uint32_t*>(reinterpret_cast<const T*>(a.qkv) + q_row_of(min(g, nh - 1)));
+            const uint32_t* q1 = reinterpret_cast<const uint32_t*>(reinterpret_cast<const T*>(a.qkv) + q_row_of(min(g + 8, nh - 1)));
             const bool v0 = g < nh, v1 = g + 8 < nh;
 #pragma unroll
             for (int j = 0; j < KSTEPS; ++j)
@@ -255,7 +339,7 @@ __global__ void __launch_bounds__(128, Gqa16Traits<DH>::MIN_BLOCKS) gqa16_decode
             const int gi = warp + NWARPS * i;
             const int t0 = chunk_start + gi * TG;
             const int lim = total - t0; // valid tokens in this group if < TG
-            if (new_pos < t0 + TG)
+            if (FEAT != 2 && new_pos < t0 + TG)
             {
                 // The group ends with the new token: put its k / v rows into the staged tile (rows behind it were
                 // zero-filled by the copies) and, from the first head slice only, append them to the paged cache.
@@ -270,7 +354,7 @@ __global__ void __launch_bounds__(128, Gqa16Traits<DH>::MIN_BLOCKS) gqa16_decode
                     const uint32_t lin = sw16<DH>((uint32_t) r_new, (uint32_t) lane);
                     *reinterpret_cast<uint4*>(stage + lin) = kq;
                     *reinterpret_cast<uint4*>(stage + SLAB + lin) = vq;
-                    if (hg == 0)
+                    if (FEAT == 0 && hg == 0) // (feature form: kv_append_token_kernel stores the token behind this kernel)
                     {
                         const size_t off = head_off + (size_t) (new_pos & tpb_mask) * ROW + lane * 16;
                         char* kb = reinterpret_cast<char*>(table_entry(krow, new_pos >> tpb_log2, a.max_blocks_per_seq, a.status, a.guard)) + off;
@@ -308,7 +392,18 @@ __global__ void __launch_bounds__(128, Gqa16Traits<DH>::MIN_BLOCKS) gqa16_decode
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
+                {
                     p[nt][c] = sacc[nt][c] * sscale;
+                    const int tok = t0 + 8 * nt + 2 * t + (c & 1);
+                    if constexpr (FEAT == 1)
+                        p[nt][c] = fmaf(slope[c >> 1], tok == new_pos ? 0.f : (float) (tok - past_true), p[nt][c]);
+                    if constexpr (FEAT == 2)
+                    {
+                        const int j = tok - first_new;
+                        if (j >= 0 && j < 64 && (((j < 32 ? mw[c >> 1][0] : mw[c >> 1][1]) >> (j & 31)) & 1u) == 0u)
+                            p[nt][c] = -INFINITY;
+                    }
+                }
             if (lim < TG)
             {
 #pragma unroll
@@ -318,7 +413,7 @@ __global__ void __launch_bounds__(128, Gqa16Traits<DH>::MIN_BLOCKS) gqa16_decode
                         if (8 * nt + 2 * t + (c & 1) >= lim)
                             p[nt][c] = -INFINITY;
             }
-            float alpha[2];
+            float alpha[2], msub[2];
             bool changed = false;
 #pragma unroll
             for (int r = 0; r < 2; ++r)
@@ -327,7 +422,9 @@ __global__ void __launch_bounds__(128, Gqa16Traits<DH>::MIN_BLOCKS) gqa16_decode
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
                 const float m_new = fmaxf(m[r], mx);
-                alpha[r] = fast_exp2(m[r] - m_new);
+                // (FEAT = 2: under its mask a row may have seen nothing yet; -inf minus -inf must not reach exp2)
+                msub[r] = (FEAT == 2 && m_new == -INFINITY) ? 0.f : m_new;
+                alpha[r] = fast_exp2(m[r] - msub[r]);
                 changed |= m_new != m[r];
                 m[r] = m_new;
                 l[r] *= alpha[r];
@@ -339,7 +436,7 @@ __global__ void __launch_bounds__(128, Gqa16Traits<DH>::MIN_BLOCKS) gqa16_decode
 #pragma unroll
                 for (int r = 0; r < 2; ++r)
                 {
-                    const float p0 = fast_exp2(p[nt][2 * r] - m[r]), p1 = fast_exp2(p[nt][2 * r + 1] - m[r]);
+                    const float p0 = fast_exp2(p[nt][2 * r] - msub[r]), p1 = fast_exp2(p[nt][2 * r + 1] - msub[r]);
                     l[r] += p0 + p1;
                     pa[2 * nt + r] = TypeOps<T>::pack2(p0, p1);
                 }
@@ -420,7 +517,7 @@ __global__ void __launch_bounds__(128, Gqa16Traits<DH>::MIN_BLOCKS) gqa16_decode
                 L = fmaf(wb[16 * DH + 16 + head], f, L);
                 o = fmaf(wb[head * DH + dh], f, o);
             }
-            const size_t row = (size_t) b * a.num_heads + head0 + head;
+            const size_t row = out_row_of(head);
             if (final_out)
             {
                 reinterpret_cast<T*>(a.out)[row * DH + dh] = TypeOps<T>::from_float(o / L);

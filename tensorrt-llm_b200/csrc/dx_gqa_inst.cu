@@ -28,9 +28,21 @@ static KernelInfo mk_feature()
     return k;
 }
 
+template <typename T, int DH, int FEAT>
+static KernelInfo mk16_feature()
+{
+    KernelInfo k;
+    k.fn = reinterpret_cast<const void*>(&gqa16_decode_kernel<T, DH, FEAT>);
+    k.smem = Gqa16Traits<DH>::SMEM_BYTES;
+    k.resident = Gqa16Traits<DH>::MIN_BLOCKS;
+    return k;
+}
+
 template <typename T, bool H16, int FEAT>
 static KernelInfo feature_by_cache_dh(int cache, int dh)
 {
+    if (cache == CACHE_T)
+        return dh == 64 ? mk16_feature<T, 64, FEAT>() : (dh == 128 ? mk16_feature<T, 128, FEAT>() : KernelInfo{});
     if (dh == 64)
     {
         if (cache == CACHE_INT8) return mk_feature<T, CACHE_INT8, 64, H16, FEAT>();

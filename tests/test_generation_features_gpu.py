@@ -127,6 +127,11 @@ CASES = {
     "window_wrapped_fp8_split": Case((16, 2), 128, torch.bfloat16, "fp8", 64, 2, window=4096, past_lo=3000, past_hi=9000, seed=12),
     "window_sink_alibi_int8": Case((8, 2), 64, torch.float16, "int8", 32, 3, window=256, sink=32, alibi=True, past_lo=100, past_hi=800, seed=13),
     "beam2_window_sink_fp8": Case((8, 2), 128, torch.bfloat16, "fp8", 64, 2, beam=2, window=256, sink=64, past_lo=100, past_hi=700, seed=14),
+    # ... and over a 16-bit cache: the feature form of the 16-bit grouped-head kernel
+    "beam2_gqa_bf16": Case((8, 2), 128, torch.bfloat16, "none", 64, 2, beam=2, seed=15),
+    "alibi_gqa_fp16_split": Case((8, 2), 64, torch.float16, "none", 32, 2, alibi=True, past_lo=3000, past_hi=5000, seed=16),
+    "window_wrapped_gqa_bf16": Case((16, 4), 128, torch.bfloat16, "none", 64, 3, window=256, past_lo=200, past_hi=900, seed=17),
+    "beam3_window_sink_alibi_fp16": Case((12, 3), 64, torch.float16, "none", 16, 2, beam=3, window=128, sink=32, alibi=True, past_lo=50, past_hi=400, seed=18),
 }
 
 
@@ -146,7 +151,8 @@ def test_features_against_oracle(pkg, name):
 
 
 @pytest.mark.parametrize("name", ["beam4_gqa_fp8_split", "beam2_group16_int8", "beam2_alibi_fp8", "window_wrapped_int8",
-                                  "window_sink_fp8", "beam2_window_wrapped", "window_wrapped_fp8_split"])
+                                  "window_sink_fp8", "beam2_window_wrapped", "window_wrapped_fp8_split", "beam2_gqa_bf16",
+                                  "window_wrapped_gqa_bf16"])
 def test_grouped_feature_kernel_agrees_with_the_per_head_kernel(pkg, name, monkeypatch):
     """The same call on the feature form of the grouped-head kernel (default) and, with DX_ATTN_FEATURE_GQA=0, on
     the per-head feature kernel: identical pool bytes, outputs within the output tolerance of each other."""

@@ -162,10 +162,12 @@ def test_what_the_mode_does_not_cover_is_refused(pkg):
     (torch.bfloat16, "int8", (8, 1), 128, 32, 0, 500),        # MQA: all rows on one kv head
     (torch.float16, "fp8", (24, 2), 64, 128, 0, 900),         # 12 heads per kv head: tokens straddle the 16-row slices
     (torch.float16, "int8", (4, 2), 64, 64, 0, 200),          # 2 heads per kv head
+    (torch.bfloat16, "none", (16, 2), 128, 64, 3000, 6000),   # 16-bit cache (the one case the reference's XQA serves)
+    (torch.float16, "none", (8, 2), 64, 16, 0, 300),
 ])
 def test_grouped_rows_kernel_against_oracle_and_the_per_row_kernel(pkg, tree, dtype, cache, heads, dh, tpb, lo, hi,
                                                                    monkeypatch):
-    """Grouped heads over an 8-bit cache run on the grouped-head kernel with (token, head) rows (the default); the
+    """Grouped heads run on the grouped-head kernels with (token, head) rows (the default); the
     same call with DX_ATTN_FEATURE_GQA=0 runs one CTA per row.  Both against the oracle; identical pool bytes."""
     cfg = workloads.DecodeConfig("mtg", 3, heads[0], heads[1], dh, dtype, cache, tpb, lo, hi, True, 311)
     packed, _ = _tree(tree, cfg.batch)
