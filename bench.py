@@ -335,7 +335,9 @@ def run_own_arm(args):
     # something to sample); `steps` and `ms_per_step` mean what they always meant. ----
     est = m.repetition(min(args.steps, 20), barrier) / min(args.steps, 20)  # untimed: sizes the repetitions
     est = max_over_ranks([est])[0]  # every rank must derive the same number of repetitions (they meet at barriers)
-    repeats = args.repeats if args.repeats > 0 else int(min(400, max(25, -(-250.0 // max(1e-6, args.steps * est)))))
+    # (at least 25 repetitions and 70 ms of GPU work; not more: a timed region of several hundred ms of this
+    # kernel runs into the board's power cap and is measured at a lower SM clock)
+    repeats = args.repeats if args.repeats > 0 else int(min(400, max(25, -(-70.0 // max(1e-6, args.steps * est)))))
     sampler = ClockSampler(physical_gpu_index(local_rank), period_s=0.005)
     ev = []
     l0 = plugin.launch_count()
@@ -477,7 +479,7 @@ def run_own_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--config", default="c4", choices=["c1", "c2", "c3", "c4", "c5", "c4kv16"])
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
