@@ -73,6 +73,7 @@ struct dx_attn
     KernelInfo k_mha{}, k_gqa[2]{}, k_wide{}, k_tok{}, k_merge{}, k_append{}; // k_gqa[16 heads per CTA?]
     KernelInfo k_gqa_feat[2]{}; // feature form of k_gqa (beam search, cyclic window, ALiBi)
     KernelInfo k_gqa_multi[2]{}; // several-new-tokens form of k_gqa (rows = (token, head) pairs of a kv head)
+    bool pdl_attention = false;  // the 8-bit grouped-head kernel is launched as a programmatic dependent of its predecessor
     bool feature_gqa = true;    // beams / ALiBi on grouped heads run on it (0: on the per-head feature kernel)
     KernelInfo k_gqa_six{}; // stream-K form of k_gqa[0] with two six-warp CTAs per SM (where built)
     bool wide = false;       // wide-group kernel usable for this configuration
@@ -1061,6 +1062,8 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
         st = set_smem(h, h->k_gqa[i]);
     if (st == DX_OK && h->k_gqa[0].fn)
     {
+        if (const char* w = getenv("DX_ATTN_PDL_ATTENTION"))
+            h->pdl_attention = atoi(w) != 0;
         if (const char* w = getenv("DX_ATTN_FEATURE_GQA"))
             h->feature_gqa = atoi(w) != 0;
         for (int i = 0; i < 2 && h->feature_gqa; ++i)
@@ -1407,7 +1410,24 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
         int hgroups = plan.hgroups;
         void* args[] = {&a, &hgroups, use_sk ? &sk : &h->sk_zero};
         const dim3 grid = use_sk ? dim3(sk_ctas) : dim3(plan.nsplit, c.num_kv_heads * plan.hgroups, p.num_requests);
-        st = check_cuda(h, cudaLaunchKernel(k.fn, grid, dim3(k.threads), args, (size_t) k.smem, stream));
+        if (h->pdl_attention)
+        {
+            // programmatic dependent of the kernel in front of it on the stream (in a decode loop the previous
+            // step's merge): its CTAs become resident while that kernel drains and wait at their top
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = grid;
+            cfg.blockDim = dim3(k.threads);
+            cfg.dynamicSmemBytes = (size_t) k.smem;
+            cfg.stream = stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            st = check_cuda(h, cudaLaunchKernelExC(&cfg, k.fn, args));
+        }
+        else
+            st = check_cuda(h, cudaLaunchKernel(k.fn, grid, dim3(k.threads), args, (size_t) k.smem, stream));
     }
     else
     {

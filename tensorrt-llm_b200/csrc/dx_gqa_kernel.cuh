@@ -229,6 +229,11 @@ __global__ void __launch_bounds__(WARPS * 32, gqa_min_blocks<CACHE, DH, H16, WAR
     const int G = a.num_heads / a.num_kv_heads;
     const int tpb_log2 = a.tpb_log2, tpb_mask = (1 << tpb_log2) - 1;
 
+    // Launched as a programmatic dependent of the kernel in front of it (the previous step's merge), the CTAs become
+    // resident while that kernel drains; nothing in global memory is touched before it has completed.  (Without
+    // that launch attribute the wait returns at once.)
+    griddep_wait();
+
     // Work of this CTA.  Classic launch: one piece, the (partition, kv-head slice, sequence) of its grid
     // position.  Stream-K launch (a.streamk): a contiguous range of 32-token groups of the whole batch
     // (SkSchedule), i.e. a few pieces of consecutive rows, every CTA the same amount.

@@ -129,6 +129,7 @@ __device__ __forceinline__ void merge_row(const AttnArgs& a, int row, int n, int
 template <typename T, int DH>
 __global__ void __launch_bounds__(128) lse_merge_kernel(const AttnArgs a)
 {
+    griddep_launch_dependents(); // the next step's attention grid may become resident; it waits for this grid
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * 4 + warp; // b * H + h
     if (row >= a.batch * a.num_heads * max(1, a.q_len))
@@ -148,6 +149,7 @@ __global__ void __launch_bounds__(128) lse_merge_kernel(const AttnArgs a)
 template <typename T, int DH>
 __global__ void __launch_bounds__(128) lse_merge_sk_kernel(const AttnArgs a, const int hgroups, const __grid_constant__ SkSchedule sk)
 {
+    griddep_launch_dependents(); // the next step's attention grid may become resident; it waits for this grid
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * 4 + warp; // b * H + h
     if (row >= a.batch * a.num_heads)
