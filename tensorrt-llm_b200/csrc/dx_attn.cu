@@ -561,28 +561,61 @@ int launch_prep(dx_attn* h, const dx_attn_generation_params& p, int nseq, cudaSt
     return st;
 }
 
-// Beam search / cyclic window / sink tokens / ALiBi: one CTA per (sequence, q head) reads the cache as it is,
-// then a second kernel appends the new token at its (cyclic) slot.
-int enqueue_general(dx_attn* h, const dx_attn_generation_params& p, int max_past, void* cuda_stream)
+// Cyclic-cache geometry of a generation step (KVBlockArray, kvCacheUtils.h:74-90) and the checks both feature paths
+// share.  A table with a spare block keeps W + tokens_per_block slots cycling.  Returns DX_OK and the period of the
+// non-sink part of the cache, or the status to refuse the call with.
+int window_geometry(const dx_attn* h, const dx_attn_generation_params& p, int max_past, int& cyclic_len)
 {
-    const dx_attn_config& c = h->cfg;
-    const int tpb = c.tokens_per_block;
+    const int tpb = h->cfg.tokens_per_block;
     const int W = p.cyclic_attention_window_size, sink = p.sink_token_length;
-    const int nseq = p.num_requests * p.beam_width; // the reference's batch_beam (gptAttentionCommon.cpp:1186)
-    if (!h->k_general.attn)
-        return DX_ERR_UNSUPPORTED;
     if (p.max_attention_window < W || sink >= W)
         return DX_ERR_BAD_ARG;
     if (sink % tpb != 0)
         return DX_ERR_UNSUPPORTED; // a partly filled sink block needs the reference's position shift
-    // KVBlockArray (kvCacheUtils.h:74-90): a table with a spare block keeps W + tokens_per_block slots cycling
     const bool one_more_block = (int64_t) (p.max_blocks_per_sequence - 1) * tpb >= W;
-    const int cyclic_len = one_more_block ? W + tpb - sink : W - sink;
+    cyclic_len = one_more_block ? W + tpb - sink : W - sink;
     if (max_past > W && one_more_block)
         return DX_ERR_UNSUPPORTED; // the walked slots 0..W-1 are the live window only without the spare block
     const int64_t slots_used = std::min<int64_t>((int64_t) max_past + 1, (int64_t) sink + cyclic_len);
     if (slots_used > (int64_t) p.max_blocks_per_sequence * tpb)
         return DX_ERR_BAD_ARG; // the table cannot hold that many tokens
+    return DX_OK;
+}
+
+// The split-K merge behind an attention launch, as a programmatic dependent: the merge grid is scheduled while the
+// attention grid drains and blocks in griddepcontrol.wait until that grid has completed (hides the launch gap).
+// rows: output rows (sequences x new tokens x q heads).  Stream-K launches pass their schedule.
+int launch_merge(dx_attn* h, AttnArgs& a, size_t rows, int hgroups, const SkSchedule* sk, cudaStream_t stream)
+{
+    void* args[] = {&a, &hgroups, const_cast<SkSchedule*>(sk)}; // (the classic merge kernel takes the first)
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned) ((rows + 3) / 4));
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const int st = check_cuda(h, cudaLaunchKernelExC(&cfg, sk ? h->k_merge_sk : h->k_merge.fn, args));
+    if (st == DX_OK)
+        h->launches.fetch_add(1);
+    return st;
+}
+
+// Beam search / cyclic window / sink tokens / ALiBi: one CTA per (sequence, q head) reads the cache as it is,
+// then a second kernel appends the new token at its (cyclic) slot.
+int enqueue_general(dx_attn* h, const dx_attn_generation_params& p, int max_past, void* cuda_stream)
+{
+    const dx_attn_config& c = h->cfg;
+    const int W = p.cyclic_attention_window_size, sink = p.sink_token_length;
+    const int nseq = p.num_requests * p.beam_width; // the reference's batch_beam (gptAttentionCommon.cpp:1186)
+    if (!h->k_general.attn)
+        return DX_ERR_UNSUPPORTED;
+    int cyclic_len = 0;
+    if (const int gs = window_geometry(h, p, max_past, cyclic_len); gs != DX_OK)
+        return gs;
     if (p.beam_width > 1)
     {
         if (!p.cache_indir || !p.context_lengths)
@@ -662,20 +695,10 @@ int enqueue_feature_gqa(dx_attn* h, const dx_attn_generation_params& p, int max_
         if (((uintptr_t) p.cache_indir | (uintptr_t) p.context_lengths) & 3)
             return DX_ERR_BAD_ARG;
     }
-    // window and sink arithmetic as in enqueue_general (KVBlockArray, kvCacheUtils.h:74-90)
-    const int tpb = c.tokens_per_block;
     const int W = p.cyclic_attention_window_size, sink = p.sink_token_length;
-    if (p.max_attention_window < W || sink >= W)
-        return DX_ERR_BAD_ARG;
-    if (sink % tpb != 0)
-        return DX_ERR_UNSUPPORTED; // a partly filled sink block needs the reference's position shift
-    const bool one_more_block = (int64_t) (p.max_blocks_per_sequence - 1) * tpb >= W;
-    const int cyclic_len = one_more_block ? W + tpb - sink : W - sink;
-    if (max_past > W && one_more_block)
-        return DX_ERR_UNSUPPORTED; // the walked slots 0..W-1 are the live window only without the spare block
-    const int64_t slots_used = std::min<int64_t>((int64_t) max_past + 1, (int64_t) sink + cyclic_len);
-    if (slots_used > (int64_t) p.max_blocks_per_sequence * tpb)
-        return DX_ERR_BAD_ARG; // the table cannot hold that many tokens
+    int cyclic_len = 0;
+    if (const int gs = window_geometry(h, p, max_past, cyclic_len); gs != DX_OK)
+        return gs;
     const bool wrapped = max_past > W; // some sequence walks W slots instead of its whole history
     Plan plan;
     plan.kind = KIND_GQA;
@@ -739,20 +762,9 @@ int enqueue_feature_gqa(dx_attn* h, const dx_attn_generation_params& p, int max_
     h->launches.fetch_add(1);
     if (plan.nsplit > 1)
     {
-        void* margs[] = {&a};
-        cudaLaunchConfig_t cfg{};
-        cfg.gridDim = dim3((nseq * c.num_heads + 3) / 4);
-        cfg.blockDim = dim3(128);
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        st = check_cuda(h, cudaLaunchKernelExC(&cfg, h->k_merge.fn, margs));
+        st = launch_merge(h, a, (size_t) nseq * c.num_heads, hgroups, nullptr, stream);
         if (st != DX_OK)
             return st;
-        h->launches.fetch_add(1);
     }
     // the new token into its (cyclic) slot, behind every read of the old content of that slot
     GeneralArgs g{};
@@ -897,20 +909,9 @@ int enqueue_multi_token(dx_attn* h, const dx_attn_generation_params& p, int max_
             h->launches.fetch_add(1);
             if (plan.nsplit > 1)
             {
-                void* margs[] = {&a};
-                cudaLaunchConfig_t cfg{};
-                cfg.gridDim = dim3((unsigned) ((qrows + 3) / 4));
-                cfg.blockDim = dim3(128);
-                cfg.stream = stream;
-                cudaLaunchAttribute attr[1];
-                attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-                attr[0].val.programmaticStreamSerializationAllowed = 1;
-                cfg.attrs = attr;
-                cfg.numAttrs = 1;
-                st = check_cuda(h, cudaLaunchKernelExC(&cfg, h->k_merge.fn, margs));
+                st = launch_merge(h, a, qrows, hgroups, nullptr, stream);
                 if (st != DX_OK)
                     return st;
-                h->launches.fetch_add(1);
             }
             return DX_OK;
         }
@@ -1440,27 +1441,7 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
     h->launches.fetch_add(1);
 
     if (plan.nsplit > 1)
-    {
-        int hgroups = plan.hgroups;
-        void* args[] = {&a, &hgroups, &sk}; // (the classic merge kernel takes the first)
-        const int rows = p.num_requests * c.num_heads;
-        // Programmatic dependent launch: the merge grid is scheduled while the attention grid drains and
-        // blocks in griddepcontrol.wait until that grid has completed (hides the launch gap).
-        cudaLaunchConfig_t cfg{};
-        cfg.gridDim = dim3((rows + 3) / 4);
-        cfg.blockDim = dim3(128);
-        cfg.dynamicSmemBytes = 0;
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        st = check_cuda(h, cudaLaunchKernelExC(&cfg, use_sk ? h->k_merge_sk : h->k_merge.fn, args));
-        if (st != DX_OK)
-            return st;
-        h->launches.fetch_add(1);
-    }
+        return launch_merge(h, a, (size_t) p.num_requests * c.num_heads, plan.hgroups, use_sk ? &sk : nullptr, stream);
     return DX_OK;
 }
 
