@@ -73,7 +73,9 @@ struct dx_attn
     KernelInfo k_mha{}, k_gqa[2]{}, k_wide{}, k_tok{}, k_merge{}, k_append{}; // k_gqa[16 heads per CTA?]
     KernelInfo k_gqa_feat[2]{}; // feature form of k_gqa (beam search, cyclic window, ALiBi)
     KernelInfo k_gqa_multi[2]{}; // several-new-tokens form of k_gqa (rows = (token, head) pairs of a kv head)
-    bool pdl_attention = false;  // the 8-bit grouped-head kernel is launched as a programmatic dependent of its predecessor
+    int pdl_attention = -1;      // the 8-bit grouped-head kernel as a programmatic dependent of its predecessor:
+                                 // 1 always, 0 never, -1 for stream-K launches with ranges of 4096 tokens or more
+                                 // (measured: c4 / its TP2 shard / c5 gain ~1 %, the short ranges of small shards lose)
     bool feature_gqa = true;    // beams / ALiBi on grouped heads run on it (0: on the per-head feature kernel)
     KernelInfo k_gqa_six{}; // stream-K form of k_gqa[0] with two six-warp CTAs per SM (where built)
     bool wide = false;       // wide-group kernel usable for this configuration
@@ -1064,7 +1066,7 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
     if (st == DX_OK && h->k_gqa[0].fn)
     {
         if (const char* w = getenv("DX_ATTN_PDL_ATTENTION"))
-            h->pdl_attention = atoi(w) != 0;
+            h->pdl_attention = atoi(w) != 0 ? 1 : 0;
         if (const char* w = getenv("DX_ATTN_FEATURE_GQA"))
             h->feature_gqa = atoi(w) != 0;
         for (int i = 0; i < 2 && h->feature_gqa; ++i)
@@ -1411,7 +1413,7 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
         int hgroups = plan.hgroups;
         void* args[] = {&a, &hgroups, use_sk ? &sk : &h->sk_zero};
         const dim3 grid = use_sk ? dim3(sk_ctas) : dim3(plan.nsplit, c.num_kv_heads * plan.hgroups, p.num_requests);
-        if (h->pdl_attention)
+        if (h->pdl_attention == 1 || (h->pdl_attention < 0 && use_sk && plan.chunk_tokens >= 4096))
         {
             // programmatic dependent of the kernel in front of it on the stream (in a decode loop the previous
             // step's merge): its CTAs become resident while that kernel drains and wait at their top
