@@ -73,6 +73,7 @@ struct dx_attn
     KernelInfo k_mha{}, k_gqa[2]{}, k_wide{}, k_tok{}, k_merge{}, k_append{}; // k_gqa[16 heads per CTA?]
     KernelInfo k_gqa_feat[2]{}; // feature form of k_gqa (beam search, cyclic window, ALiBi)
     KernelInfo k_gqa_multi[2]{}; // several-new-tokens form of k_gqa (rows = (token, head) pairs of a kv head)
+    int pdl_other = 1;           // the same for the wide-group and per-head kernels (DX_ATTN_PDL_OTHER; c1 10.2 -> 9.6, c2 135.2 -> 134.4, c3 34.5 -> 33.4 us)
     int pdl_attention = -1;      // the 8-bit grouped-head kernel as a programmatic dependent of its predecessor:
                                  // 1 always, 0 never, -1 for stream-K launches with ranges of 4096 tokens or more
                                  // (measured: c4 / its TP2 shard / c5 gain ~1 %, the short ranges of small shards lose)
@@ -584,6 +585,27 @@ int window_geometry(const dx_attn* h, const dx_attn_generation_params& p, int ma
     return DX_OK;
 }
 
+// Launches an attention kernel, optionally as a programmatic dependent of the kernel in front of it on the stream
+// (in a decode loop the previous step's merge or attention kernel): its CTAs become resident while that kernel
+// drains and wait at their top (griddepcontrol.wait) before they touch global memory.
+int launch_attention(dx_attn* h, const void* fn, dim3 grid, dim3 block, size_t smem, void** args, bool dependent,
+    cudaStream_t stream)
+{
+    if (!dependent)
+        return check_cuda(h, cudaLaunchKernel(fn, grid, block, args, smem, stream));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return check_cuda(h, cudaLaunchKernelExC(&cfg, fn, args));
+}
+
 // The split-K merge behind an attention launch, as a programmatic dependent: the merge grid is scheduled while the
 // attention grid drains and blocks in griddepcontrol.wait until that grid has completed (hides the launch gap).
 // rows: output rows (sequences x new tokens x q heads).  Stream-K launches pass their schedule.
@@ -1010,6 +1032,10 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
     h->group = c.num_heads / c.num_kv_heads;
     while ((1 << h->tpb_log2) < c.tokens_per_block)
         ++h->tpb_log2;
+    if (const char* w = getenv("DX_ATTN_PDL_OTHER"))
+        h->pdl_other = atoi(w) != 0 ? 1 : 0;
+    if (const char* w = getenv("DX_ATTN_PDL_ATTENTION"))
+        h->pdl_attention = atoi(w) != 0 ? 1 : 0;
     if (const char* w = getenv("DX_ATTN_WAVES"))
         h->waves = std::max(1, atoi(w));
     if (const char* w = getenv("DX_ATTN_MIN_CHUNK"))
@@ -1065,8 +1091,6 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
         st = set_smem(h, h->k_gqa[i]);
     if (st == DX_OK && h->k_gqa[0].fn)
     {
-        if (const char* w = getenv("DX_ATTN_PDL_ATTENTION"))
-            h->pdl_attention = atoi(w) != 0 ? 1 : 0;
         if (const char* w = getenv("DX_ATTN_FEATURE_GQA"))
             h->feature_gqa = atoi(w) != 0;
         for (int i = 0; i < 2 && h->feature_gqa; ++i)
@@ -1389,7 +1413,7 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
         int hgroups = plan.hgroups;
         void* args[] = {&a, &hgroups};
         dim3 grid(plan.nsplit, c.num_kv_heads * plan.hgroups, p.num_requests);
-        st = check_cuda(h, cudaLaunchKernel(h->k_wide.fn, grid, dim3(128), args, (size_t) h->k_wide.smem, stream));
+        st = launch_attention(h, h->k_wide.fn, grid, dim3(128), (size_t) h->k_wide.smem, args, h->pdl_other == 1, stream);
     }
     else if (plan.kind == KIND_TOK)
     {
@@ -1413,30 +1437,14 @@ int dx_attn_enqueue_generation(dx_attn_t* h, const dx_attn_generation_params* pa
         int hgroups = plan.hgroups;
         void* args[] = {&a, &hgroups, use_sk ? &sk : &h->sk_zero};
         const dim3 grid = use_sk ? dim3(sk_ctas) : dim3(plan.nsplit, c.num_kv_heads * plan.hgroups, p.num_requests);
-        if (h->pdl_attention == 1 || (h->pdl_attention < 0 && use_sk && plan.chunk_tokens >= 4096))
-        {
-            // programmatic dependent of the kernel in front of it on the stream (in a decode loop the previous
-            // step's merge): its CTAs become resident while that kernel drains and wait at their top
-            cudaLaunchConfig_t cfg{};
-            cfg.gridDim = grid;
-            cfg.blockDim = dim3(k.threads);
-            cfg.dynamicSmemBytes = (size_t) k.smem;
-            cfg.stream = stream;
-            cudaLaunchAttribute attr[1];
-            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            attr[0].val.programmaticStreamSerializationAllowed = 1;
-            cfg.attrs = attr;
-            cfg.numAttrs = 1;
-            st = check_cuda(h, cudaLaunchKernelExC(&cfg, k.fn, args));
-        }
-        else
-            st = check_cuda(h, cudaLaunchKernel(k.fn, grid, dim3(k.threads), args, (size_t) k.smem, stream));
+        const bool dependent = h->pdl_attention == 1 || (h->pdl_attention < 0 && use_sk && plan.chunk_tokens >= 4096);
+        st = launch_attention(h, k.fn, grid, dim3(k.threads), (size_t) k.smem, args, dependent, stream);
     }
     else
     {
         void* args[] = {&a};
         dim3 grid(plan.nsplit, c.num_heads, p.num_requests);
-        st = check_cuda(h, cudaLaunchKernel(h->k_mha.fn, grid, dim3(128), args, (size_t) h->k_mha.smem, stream));
+        st = launch_attention(h, h->k_mha.fn, grid, dim3(128), (size_t) h->k_mha.smem, args, h->pdl_other == 1, stream);
     }
     if (st != DX_OK)
         return st;

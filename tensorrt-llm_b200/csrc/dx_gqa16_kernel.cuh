@@ -97,6 +97,8 @@ __global__ void __launch_bounds__(128, Gqa16Traits<DH>::MIN_BLOCKS) gqa16_decode
     const int G = a.num_heads / a.num_kv_heads;
     const int tpb_log2 = a.tpb_log2, tpb_mask = (1 << tpb_log2) - 1;
 
+    // (as a programmatic dependent of the kernel in front of it, the CTA is resident early and waits here)
+    griddep_wait();
     // Work of this CTA.  Classic launch: one piece, the (partition, kv-head slice, sequence) of its grid
     // position.  Stream-K launch (a.streamk): a contiguous range of 16-token groups of the whole batch
     // (SkSchedule), i.e. a few pieces of consecutive rows, every CTA the same amount.

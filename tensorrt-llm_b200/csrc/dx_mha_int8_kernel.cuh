@@ -46,6 +46,8 @@ __global__ void __launch_bounds__(128) mha_int8_decode_kernel(const AttnArgs a)
     constexpr int STAGES = Tr::STAGES, NWARPS = Tr::NWARPS, ROW_BYTES = Tr::ROW_BYTES, SLAB = Tr::SLAB;
     constexpr int CACHE = CACHE_INT8;
 
+    // (as a programmatic dependent of the kernel in front of it, the CTA is resident early and waits here)
+    griddep_wait();
     const int chunk = blockIdx.x;
     const int h = blockIdx.y;
     const int b = blockIdx.z;

@@ -95,6 +95,8 @@ __global__ void __launch_bounds__(128) mha_decode_kernel(const AttnArgs a)
     constexpr int LPR = Tr::LPR, TPW = Tr::TPW, EPL = Tr::EPL, TG = Tr::TG, PASSES = Tr::PASSES;
     constexpr int STAGES = Tr::STAGES, NWARPS = Tr::NWARPS, ROW_BYTES = Tr::ROW_BYTES, SLAB = Tr::SLAB;
 
+    // (as a programmatic dependent of the kernel in front of it, the CTA is resident early and waits here)
+    griddep_wait();
     const int chunk = blockIdx.x;
     const int h = blockIdx.y;
     const int b = blockIdx.z;

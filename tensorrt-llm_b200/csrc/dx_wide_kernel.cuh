@@ -62,6 +62,8 @@ __global__ void __launch_bounds__(128, WideTraits<DH>::MIN_BLOCKS) wide_decode_k
     // p = 2^(s - m) with m = (lazy row reference) - 4: p <= 2^PMAX = 256 goes into e4m3 without a further scale
     constexpr float PMAX = 8.f;
 
+    // (as a programmatic dependent of the kernel in front of it, the CTA is resident early and waits here)
+    griddep_wait();
     const int chunk = blockIdx.x;
     const int hk = blockIdx.y / hgroups, hg = blockIdx.y % hgroups;
     const int b = blockIdx.z;
