@@ -73,6 +73,7 @@ struct dx_attn
     KernelInfo k_mha{}, k_gqa[2]{}, k_wide{}, k_tok{}, k_merge{}, k_append{}; // k_gqa[16 heads per CTA?]
     KernelInfo k_gqa_feat[2]{}; // feature form of k_gqa (beam search, cyclic window, ALiBi)
     KernelInfo k_gqa_multi[2]{}; // several-new-tokens form of k_gqa (rows = (token, head) pairs of a kv head)
+    bool no_dependent_launch = false; // set while the host-buffer entry point enqueues its step
     int pdl_other = 1;           // the same for the wide-group and per-head kernels (DX_ATTN_PDL_OTHER; c1 10.2 -> 9.6, c2 135.2 -> 134.4, c3 34.5 -> 33.4 us)
     int pdl_attention = -1;      // the 8-bit grouped-head kernel as a programmatic dependent of its predecessor:
                                  // 1 always, 0 never, -1 for stream-K launches with ranges of 4096 tokens or more
@@ -591,7 +592,7 @@ int window_geometry(const dx_attn* h, const dx_attn_generation_params& p, int ma
 int launch_attention(dx_attn* h, const void* fn, dim3 grid, dim3 block, size_t smem, void** args, bool dependent,
     cudaStream_t stream)
 {
-    if (!dependent)
+    if (!dependent || h->no_dependent_launch)
         return check_cuda(h, cudaLaunchKernel(fn, grid, block, args, smem, stream));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
@@ -1544,7 +1545,11 @@ int dx_attn_enqueue_generation_host(
     p.block_pointers = reinterpret_cast<const int64_t*>(base + o_tbl);
     p.sequence_lengths = reinterpret_cast<const int32_t*>(base + o_len);
     p.context_buf = base + o_out;
+    // (between the kernels of consecutive steps this stream waits for copies: nothing to overlap a dependent launch with,
+    // and the attribute costs the pipelined figure 3 %)
+    h->no_dependent_launch = true;
     st = dx_attn_enqueue_generation(h, &p, cuda_stream);
+    h->no_dependent_launch = false;
     if (st != DX_OK)
         return st;
     st = check_cuda(h, cudaEventRecord(h->ev_done[slot], stream));
