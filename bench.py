@@ -65,6 +65,21 @@ def profiled_traffic(workload_key: str):
     return PROFILED_TRAFFIC.get(workload_key)
 
 
+def agreed_repeats(dist, dev, est_ms_per_step: float, steps: int, requested: int) -> int:
+    """Repetitions of the timed loop, the same number on every rank: the ranks meet at a barrier around every
+    repetition, so a count derived from a per-rank timing would leave the faster rank waiting for ever.  The
+    estimate is reduced to its maximum over the ranks first.  At least 25 repetitions and 70 ms of GPU work; not
+    more: a timed region of several hundred ms of this kernel runs into the board's power cap and is measured at
+    a lower SM clock."""
+    t = torch.tensor([est_ms_per_step], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    est = float(t.item())
+    if requested > 0:
+        return requested
+    return int(min(400, max(25, -(-70.0 // max(1e-6, steps * est)))))
+
+
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons of one GPU through NVML (read-only) while running."""
 
@@ -334,10 +349,7 @@ def run_own_arm(args):
     # repetition.  The repetitions only make the figure rest on more GPU time (and give the clock sampler
     # something to sample); `steps` and `ms_per_step` mean what they always meant. ----
     est = m.repetition(min(args.steps, 20), barrier) / min(args.steps, 20)  # untimed: sizes the repetitions
-    est = max_over_ranks([est])[0]  # every rank must derive the same number of repetitions (they meet at barriers)
-    # (at least 25 repetitions and 70 ms of GPU work; not more: a timed region of several hundred ms of this
-    # kernel runs into the board's power cap and is measured at a lower SM clock)
-    repeats = args.repeats if args.repeats > 0 else int(min(400, max(25, -(-70.0 // max(1e-6, args.steps * est)))))
+    repeats = agreed_repeats(dist, dev, est, args.steps, args.repeats)
     sampler = ClockSampler(physical_gpu_index(local_rank), period_s=0.005)
     ev = []
     l0 = plugin.launch_count()

@@ -28,6 +28,11 @@ def _worker(rank, world, port, q):
         assert ws.cfg.num_heads == cfg.num_heads // world and ws.cfg.num_kv_heads == cfg.num_kv_heads // world
         assert torch.equal(ws.host_past_key_value_lengths, w.host_past_key_value_lengths)
         o, _ = oracle_step(ws)                     # stands in for the GPU step: no data-path collective
+        # the two ranks time their calibration loops differently and must still agree on the number of repetitions
+        reps = bench.agreed_repeats(dist, torch.device("cpu"), 0.020 if rank == 0 else 0.140, 20, 0)
+        all_reps = [None] * world
+        dist.all_gather_object(all_reps, reps)
+        assert all_reps == [25] * world, all_reps  # 70 ms / (20 steps x 0.140 ms) = 25; rank 0 alone would say 175
         maxima, sums = bench.reduce_over_ranks(dist, torch.device("cpu"), [10.0 + rank, 3.0 - rank],
                                                [float(ws.kv_bytes), 1.0])
         gathered = [torch.empty_like(o) for _ in range(world)] if rank == 0 else None
