@@ -491,6 +491,8 @@ KernelInfo merge_kernel_info(int dtype, int dh)
         k.fn = dtype == 0 ? merge_fn<__half, 64>() : merge_fn<__nv_bfloat16, 64>();
     else if (dh == 128)
         k.fn = dtype == 0 ? merge_fn<__half, 128>() : merge_fn<__nv_bfloat16, 128>();
+    else if (dh == 256)
+        k.fn = dtype == 0 ? merge_fn<__half, 256>() : merge_fn<__nv_bfloat16, 256>();
     return k;
 }
 } // namespace dx
@@ -1004,7 +1006,8 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
         return DX_ERR_BAD_ARG;
     // Head sizes of the reference's MMHA switch (decoderMaskedMultiheadAttention.cu:68-85).  64 and 128 run on the
     // streaming kernels; the others on the feature-complete kernels (one CTA per sequence and q head).
-    const bool streaming_dh = c.head_size == 64 || c.head_size == 128;
+    // (256: the per-head streaming kernel only; grouped heads then run one CTA per q head)
+    const bool streaming_dh = c.head_size == 64 || c.head_size == 128 || c.head_size == 256;
     {
         static const int sizes[] = {32, 48, 64, 80, 96, 104, 112, 128, 144, 160, 192, 224, 256};
         bool known = false;
@@ -1085,6 +1088,8 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
         }
         else if (!h->k_mha.fn || !h->k_merge.fn)
             st = DX_ERR_UNSUPPORTED;
+        if (!h->k_append.fn)
+            h->k_append.fn = h->k_general.context_append; // (head size 256)
     }
     if (st == DX_OK)
         st = set_smem(h, h->k_mha);

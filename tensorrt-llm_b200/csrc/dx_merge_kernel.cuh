@@ -13,11 +13,31 @@
 namespace dx
 {
 
+// VPL (2, 4 or 8) consecutive floats of a partial row.
+template <int VPL>
+__device__ __forceinline__ void load_partial(const float* p, float (&v)[VPL])
+{
+    if constexpr (VPL == 2)
+    {
+        const float2 q = *reinterpret_cast<const float2*>(p);
+        v[0] = q.x, v[1] = q.y;
+    }
+    else
+    {
+#pragma unroll
+        for (int i = 0; i < VPL; i += 4)
+        {
+            const float4 q = *reinterpret_cast<const float4*>(p + i);
+            v[i] = q.x, v[i + 1] = q.y, v[i + 2] = q.z, v[i + 3] = q.w;
+        }
+    }
+}
+
 // Merges the first n partial results of q row `row` (= b * H + h) into the output row.  One warp.
 template <typename T, int DH>
 __device__ __forceinline__ void merge_row(const AttnArgs& a, int row, int n, int lane)
 {
-    constexpr int VPL = DH / 32; // floats per lane (2 or 4)
+    constexpr int VPL = DH / 32; // floats per lane (2, 4 or 8)
     // (m, l) of up to 32 partitions per pass, one per lane: all loads of a pass are in flight together.
     const float2* ml = a.part_ml + (size_t) row * a.nsplit;
     const float* po = a.part_o + (size_t) row * a.nsplit * DH + lane * VPL;
@@ -28,16 +48,7 @@ __device__ __forceinline__ void merge_row(const AttnArgs& a, int row, int n, int
     for (int j = 0; j < 8; ++j)
     {
         const int c = min(j, n - 1);
-        if constexpr (VPL == 4)
-        {
-            const float4 q = *reinterpret_cast<const float4*>(po + (size_t) c * DH);
-            v0[j][0] = q.x, v0[j][1] = q.y, v0[j][2] = q.z, v0[j][3] = q.w;
-        }
-        else
-        {
-            const float2 q = *reinterpret_cast<const float2*>(po + (size_t) c * DH);
-            v0[j][0] = q.x, v0[j][1] = q.y;
-        }
+        load_partial<VPL>(po + (size_t) c * DH, v0[j]);
     }
     float M = -INFINITY;
     for (int c0 = 0; c0 < n; c0 += 32)
@@ -84,16 +95,7 @@ __device__ __forceinline__ void merge_row(const AttnArgs& a, int row, int n, int
                 for (int j = 0; j < 8; ++j)
                 {
                     const int c = min(c0 + j0 + j, n - 1); // clamped: weight of a padded slot is 0
-                    if constexpr (VPL == 4)
-                    {
-                        const float4 q = *reinterpret_cast<const float4*>(po + (size_t) c * DH);
-                        v[j][0] = q.x, v[j][1] = q.y, v[j][2] = q.z, v[j][3] = q.w;
-                    }
-                    else
-                    {
-                        const float2 q = *reinterpret_cast<const float2*>(po + (size_t) c * DH);
-                        v[j][0] = q.x, v[j][1] = q.y;
-                    }
+                    load_partial<VPL>(po + (size_t) c * DH, v[j]);
                 }
             }
 #pragma unroll
@@ -113,16 +115,20 @@ __device__ __forceinline__ void merge_row(const AttnArgs& a, int row, int n, int
         L += __shfl_xor_sync(0xffffffffu, L, x);
     const float inv = 1.f / L;
     T* dst = reinterpret_cast<T*>(a.out) + (size_t) row * DH + lane * VPL;
-    if constexpr (VPL == 4)
+    if constexpr (VPL == 2)
     {
-        uint2 w;
-        w.x = TypeOps<T>::pack2(o[0] * inv, o[1] * inv);
-        w.y = TypeOps<T>::pack2(o[2] * inv, o[3] * inv);
-        *reinterpret_cast<uint2*>(dst) = w;
+        *reinterpret_cast<uint32_t*>(dst) = TypeOps<T>::pack2(o[0] * inv, o[1] * inv);
     }
     else
     {
-        *reinterpret_cast<uint32_t*>(dst) = TypeOps<T>::pack2(o[0] * inv, o[1] * inv);
+#pragma unroll
+        for (int i = 0; i < VPL; i += 4)
+        {
+            uint2 w;
+            w.x = TypeOps<T>::pack2(o[i] * inv, o[i + 1] * inv);
+            w.y = TypeOps<T>::pack2(o[i + 2] * inv, o[i + 3] * inv);
+            *reinterpret_cast<uint2*>(dst + i) = w;
+        }
     }
 }
 

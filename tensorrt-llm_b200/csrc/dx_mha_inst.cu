@@ -30,6 +30,12 @@ static KernelInfo by_cache_dh(int cache, int dh)
         if (cache == CACHE_INT8) return mk<T, CACHE_INT8, 128>();
         if (cache == CACHE_FP8) return mk<T, CACHE_FP8, 128>();
     }
+    else if (dh == 256) // (GPT-J- / Gemma-shaped heads: the streaming per-head kernel, split-K and merge included)
+    {
+        if (cache == CACHE_T) return mk<T, CACHE_T, 256>();
+        if (cache == CACHE_INT8) return mk<T, CACHE_INT8, 256>();
+        if (cache == CACHE_FP8) return mk<T, CACHE_FP8, 256>();
+    }
     return KernelInfo{};
 }
 

@@ -21,11 +21,11 @@ template <int CACHE, int DH>
 struct MhaTraits
 {
     static constexpr int ECB = (CACHE == CACHE_T) ? 2 : 1; // bytes per cache element
-    static constexpr int ROW_BYTES = DH * ECB;             // 64, 128 or 256
+    static constexpr int ROW_BYTES = DH * ECB;             // 64, 128, 256 or 512 (Dh 256 over a 16-bit cache)
     static constexpr int LPR = ROW_BYTES / 16;             // lanes covering one row with 16 B each
     static constexpr int TPW = 32 / LPR;                   // rows one warp-wide 16 B load covers
     static constexpr int EPL = 16 / ECB;                   // elements per lane
-    static constexpr int TG = (ROW_BYTES == 256) ? 8 : 16; // tokens per stage
+    static constexpr int TG = (ROW_BYTES == 512) ? 4 : (ROW_BYTES == 256) ? 8 : 16; // tokens per stage
     static constexpr int PASSES = TG / TPW;
     static constexpr int STAGES = 4;
     static constexpr int NWARPS = 4;

@@ -151,3 +151,15 @@ def test_rope_and_bias_on_other_head_sizes(pkg, dh, rope):
     assert agree > 0.99, agree
     err = (out.float().cpu() - ref).abs()
     assert err.max().item() < MAX_ABS_TOL and err.mean().item() < MEAN_ABS_TOL, (err.max().item(), err.mean().item())
+
+
+@pytest.mark.parametrize("cache,heads,tpb", [("fp8", (16, 16), 64), ("int8", (8, 2), 32), ("none", (16, 16), 16),
+                                             ("none", (4, 1), 128)])
+def test_head_size_256_on_the_streaming_kernel_with_split_k(pkg, cache, heads, tpb):
+    """Head size 256 (GPT-J- / Gemma-shaped) runs on the streaming per-head kernel: long sequences in a small batch are
+    split into partitions and merged (the merge kernel's 8-floats-per-lane form)."""
+    wl = workloads
+    cfg = wl.DecodeConfig("dh256", 2, heads[0], heads[1], 256, torch.bfloat16, cache, tpb, 1, 9000, True, 3256)
+    lens = torch.tensor([5000, 9000], dtype=torch.int32)
+    res = gpu_step_and_compare(pkg, cfg, lengths=lens)
+    assert res["plan"]["kernel"] == "mha_cuda_core" and res["plan"]["num_partitions"] > 1, res["plan"]
