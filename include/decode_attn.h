@@ -63,8 +63,8 @@ typedef struct dx_attn_config
     int32_t layer_idx;
     int32_t num_heads;    /* q heads on THIS rank (already divided by tp_size, as the plugin is built) */
     int32_t num_kv_heads; /* kv heads on this rank; num_heads % num_kv_heads == 0                     */
-    int32_t head_size;    /* 64 or 128: streaming kernels; 256: the streaming per-head kernel (grouped heads then run one
-                           * CTA per q head).  32, 48, 80, 96, 104, 112, 144, 160, 192, 224
+    int32_t head_size;    /* 64 or 128: streaming kernels; 256: the streaming per-head kernel, or the 16-bit grouped-head
+                           * kernel for grouped heads over an unquantised cache.  32, 48, 80, 96, 104, 112, 144, 160, 192, 224
                            * (the other sizes of the reference's MMHA switch,
                            * decoderMaskedMultiheadAttention.cu:68-85): one CTA per sequence and q head, no
                            * split-K; a cache row must be a multiple of 16 bytes, so 104 needs a 16-bit cache */

@@ -175,6 +175,8 @@ Plan plan_shape(const dx_attn* h, int batch, int& rows_per_seq_out)
         p.heads16 = h->group > 8;
         rows_per_seq = c.num_kv_heads * p.hgroups;
         resident = (h->cache_kind == CACHE_FP8 && c.head_size == 128 && !p.heads16) ? 3 : 2;
+        if (h->k_gqa[p.heads16 ? 1 : 0].resident > 0)
+            resident = h->k_gqa[p.heads16 ? 1 : 0].resident; // (the 16-bit kernel states it: 1 at head size 256)
     }
     else
     {

@@ -31,13 +31,13 @@ struct Gqa16Traits
     static constexpr int CPR = ROW / 16;          // 16-byte chunks per row
     static constexpr int SLAB = TG * ROW;         // bytes of K (or V) per stage
     static constexpr int STAGE_BYTES = 2 * SLAB;
-    static constexpr int STAGES = 3;
+    static constexpr int STAGES = DH == 256 ? 2 : 3; // (Dh 256: 16 KB per stage and warp, one CTA per SM)
     static constexpr int NWARPS = 4;
     static constexpr int NCP = SLAB / 512;        // 16-byte copies per lane and slab
     static constexpr int RING_BYTES = NWARPS * STAGES * STAGE_BYTES;
     static constexpr int MERGE_BYTES = NWARPS * (16 * DH + 32) * 4;
     static constexpr int SMEM_BYTES = (RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES) + NWARPS * STAGES * 8 + 16;
-    static constexpr int MIN_BLOCKS = 2;
+    static constexpr int MIN_BLOCKS = DH == 256 ? 1 : 2;
 };
 
 // Byte offset of 16-byte chunk `chunk` of row `row` inside a slab (chunks swizzled with the row number).

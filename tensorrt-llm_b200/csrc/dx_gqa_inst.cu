@@ -42,7 +42,8 @@ template <typename T, bool H16, int FEAT>
 static KernelInfo feature_by_cache_dh(int cache, int dh)
 {
     if (cache == CACHE_T)
-        return dh == 64 ? mk16_feature<T, 64, FEAT>() : (dh == 128 ? mk16_feature<T, 128, FEAT>() : KernelInfo{});
+        return dh == 64 ? mk16_feature<T, 64, FEAT>()
+                        : (dh == 128 ? mk16_feature<T, 128, FEAT>() : (dh == 256 ? mk16_feature<T, 256, FEAT>() : KernelInfo{}));
     if (dh == 64)
     {
         if (cache == CACHE_INT8) return mk_feature<T, CACHE_INT8, 64, H16, FEAT>();
@@ -85,7 +86,7 @@ template <typename T, bool H16>
 static KernelInfo by_cache_dh(int cache, int dh)
 {
     if (cache == CACHE_T)
-        return dh == 64 ? mk16<T, 64>() : (dh == 128 ? mk16<T, 128>() : KernelInfo{});
+        return dh == 64 ? mk16<T, 64>() : (dh == 128 ? mk16<T, 128>() : (dh == 256 ? mk16<T, 256>() : KernelInfo{}));
     if (dh == 64)
     {
         if (cache == CACHE_INT8) return mk<T, CACHE_INT8, 64, H16>();

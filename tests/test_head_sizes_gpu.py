@@ -154,7 +154,7 @@ def test_rope_and_bias_on_other_head_sizes(pkg, dh, rope):
 
 
 @pytest.mark.parametrize("cache,heads,tpb", [("fp8", (16, 16), 64), ("int8", (8, 2), 32), ("none", (16, 16), 16),
-                                             ("none", (4, 1), 128)])
+                                             ("fp8", (4, 1), 128)])
 def test_head_size_256_on_the_streaming_kernel_with_split_k(pkg, cache, heads, tpb):
     """Head size 256 (GPT-J- / Gemma-shaped) runs on the streaming per-head kernel: long sequences in a small batch are
     split into partitions and merged (the merge kernel's 8-floats-per-lane form)."""
@@ -163,3 +163,25 @@ def test_head_size_256_on_the_streaming_kernel_with_split_k(pkg, cache, heads, t
     lens = torch.tensor([5000, 9000], dtype=torch.int32)
     res = gpu_step_and_compare(pkg, cfg, lengths=lens)
     assert res["plan"]["kernel"] == "mha_cuda_core" and res["plan"]["num_partitions"] > 1, res["plan"]
+
+
+@pytest.mark.parametrize("heads,tpb,lens", [((8, 1), 64, [1, 300, 5000]), ((16, 4), 16, [0, 63, 900]),
+                                            ((24, 2), 128, [17, 2000, 7000])])
+def test_head_size_256_grouped_heads_over_a_16_bit_cache(pkg, heads, tpb, lens):
+    """Gemma-shaped grouped heads (Dh 256, bf16 cache): the tensor-core grouped-head kernel, split-K and merge."""
+    wl = workloads
+    cfg = wl.DecodeConfig("dh256g", len(lens), heads[0], heads[1], 256, torch.bfloat16, "none", tpb, 0, max(lens), True, 3257)
+    res = gpu_step_and_compare(pkg, cfg, lengths=torch.tensor(lens, dtype=torch.int32))
+    assert res["plan"]["kernel"] == "gqa_tensor_core", res["plan"]
+
+
+def test_head_size_256_draft_tokens_over_a_16_bit_cache(pkg):
+    import test_multi_token_gpu as mt
+    cfg = workloads.DecodeConfig("mt256", 2, 8, 1, 256, torch.bfloat16, "none", 32, 0, 600, True, 3258)
+    packed, _ = mt._tree("small", cfg.batch)
+    w = mt._workload(pkg, cfg, packed.shape[1])
+    ref, pool_ref = mt._oracle(w, packed)
+    out, pool = mt._run(pkg, w, packed)
+    assert torch.equal(pool, pool_ref)
+    err = (out - ref).abs()
+    assert err.max().item() < MAX_ABS_TOL and err.mean().item() < MEAN_ABS_TOL, (err.max().item(), err.mean().item())
