@@ -39,3 +39,17 @@ def test_checked_build_reports_and_redirects(pkg):
         assert c["pointer_outside_pool"] == bounds, (name, c)
         assert c["foreign_untouched"], name
         assert c["clean_parity_after"], name
+
+
+@pytest.mark.gpu
+def test_checked_build_passes_the_feature_and_multi_token_parity_tests(pkg):
+    """The checks sit in every block-table look-up, including the per-row look-ups of the feature forms: the parity
+    tests of beams / windows / ALiBi / draft tokens must come out the same on the checked build."""
+    assert CHECKED.exists()
+    env = dict(os.environ, DX_DECODE_ATTN_LIB=str(CHECKED))
+    r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu",
+                        str(ROOT / "tests" / "test_generation_features_gpu.py"), "-k", "against_oracle",
+                        str(ROOT / "tests" / "test_multi_token_gpu.py")],
+                       env=env, capture_output=True, text=True, timeout=900, cwd=str(ROOT))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+    assert " passed" in r.stdout and "failed" not in r.stdout
