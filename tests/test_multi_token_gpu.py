@@ -188,8 +188,9 @@ def test_grouped_rows_kernel_against_oracle_and_the_per_row_kernel(pkg, tree, dt
     assert err.max().item() < MAX_ABS_TOL and err.mean().item() < MEAN_ABS_TOL, (err.max().item(), err.mean().item())
 
 
+@pytest.mark.parametrize("cache", ["fp8", "none"])
 @pytest.mark.parametrize("grouped", [True, False])
-def test_report_multi_token_time(pkg, grouped, monkeypatch):
+def test_report_multi_token_time(pkg, grouped, cache, monkeypatch):
     """Times a 37-token draft tree on a batch of c4's shape (32 sequences) on the grouped-rows kernel and on the per-row
     kernel; recorded in feature_path.jsonl of the report directory."""
     import json
@@ -197,7 +198,7 @@ def test_report_multi_token_time(pkg, grouped, monkeypatch):
     from helpers import REPORT_DIR
     if not grouped:
         monkeypatch.setenv("DX_ATTN_FEATURE_GQA", "0")
-    cfg = workloads.DecodeConfig("mtt", 32, 64, 8, 128, torch.bfloat16, "fp8", 64, 2048, 4096, True, 312)
+    cfg = workloads.DecodeConfig("mtt", 32, 64, 8, 128, torch.bfloat16, cache, 64, 2048, 4096, True, 312)
     packed, _ = _tree("wide", cfg.batch)
     q_len = packed.shape[1]
     w_cpu = _workload(pkg, cfg, q_len)
@@ -223,8 +224,8 @@ def test_report_multi_token_time(pkg, grouped, monkeypatch):
         torch.cuda.synchronize()
         assert plugin.device_status() == 0
         us = a.elapsed_time(b) / 10 * 1e3
-        kv = float(w_cpu.sequence_length.double().sum() * 8 * 128 * 2)
-        rec = {"case": f"{q_len} draft tokens x 32 sequences, 64 q / 8 kv heads, Dh 128, FP8, past 2048-4096, "
+        kv = float(w_cpu.sequence_length.double().sum() * 8 * 128 * 2 * cfg.elem_bytes)
+        rec = {"case": f"{q_len} draft tokens x 32 sequences, 64 q / 8 kv heads, Dh 128, {cache} cache, past 2048-4096, "
                        + ("grouped rows" if grouped else "one CTA per row"), "us": us, "unique_kv_GBps": kv / us / 1e3}
         os.makedirs(REPORT_DIR, exist_ok=True)
         with open(os.path.join(REPORT_DIR, "feature_path.jsonl"), "a") as f:
