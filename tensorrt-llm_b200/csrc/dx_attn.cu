@@ -90,6 +90,9 @@ struct dx_attn
     int ws_min_u1 = 8;       // below this many tiles per static range the schedule stays single-level
     GeneralKernels k_general{}; // beams / cyclic window / sinks / ALiBi
     const void* k_merge_sk = nullptr;
+    const void* k_merge_many = nullptr; // classic merge with one CTA per q row, for launches with many partitions
+    int merge_many_from = 32;           // partitions from which it is used (DX_ATTN_MERGE_MANY_FROM; 0: never): c5 TP8 shard, 50
+                                        // partitions: 22.2 -> 20.8 us; no difference at 25 partitions
     bool streamk = true;        // grouped-head kernels: equal ranges of token groups per CTA instead of per-row partitions
     int sk_min_units = 48;      // stream-K only when a CTA's range is at least this many token groups: below, the
                                 // second prologue / epilogue of a CTA that straddles a row boundary costs more
@@ -468,6 +471,23 @@ const void* merge_fn()
 }
 
 template <typename T, int DH>
+const void* merge_many_fn()
+{
+    return reinterpret_cast<const void*>(&lse_merge_many_kernel<T, DH>);
+}
+
+const void* merge_many_kernel(int dtype, int dh)
+{
+    if (dh == 64)
+        return dtype == 0 ? merge_many_fn<__half, 64>() : merge_many_fn<__nv_bfloat16, 64>();
+    if (dh == 128)
+        return dtype == 0 ? merge_many_fn<__half, 128>() : merge_many_fn<__nv_bfloat16, 128>();
+    if (dh == 256)
+        return dtype == 0 ? merge_many_fn<__half, 256>() : merge_many_fn<__nv_bfloat16, 256>();
+    return nullptr;
+}
+
+template <typename T, int DH>
 const void* merge_sk_fn()
 {
     return reinterpret_cast<const void*>(&lse_merge_sk_kernel<T, DH>);
@@ -617,8 +637,10 @@ int launch_attention(dx_attn* h, const void* fn, dim3 grid, dim3 block, size_t s
 int launch_merge(dx_attn* h, AttnArgs& a, size_t rows, int hgroups, const SkSchedule* sk, cudaStream_t stream)
 {
     void* args[] = {&a, &hgroups, const_cast<SkSchedule*>(sk)}; // (the classic merge kernel takes the first)
+    // many partitions per row: a CTA per row (its four warps share the partitions) instead of a warp per row
+    const bool many = !sk && h->k_merge_many && h->merge_many_from > 0 && a.nsplit >= h->merge_many_from;
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3((unsigned) ((rows + 3) / 4));
+    cfg.gridDim = many ? dim3((unsigned) rows) : dim3((unsigned) ((rows + 3) / 4));
     cfg.blockDim = dim3(128);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = stream;
@@ -627,7 +649,7 @@ int launch_merge(dx_attn* h, AttnArgs& a, size_t rows, int hgroups, const SkSche
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const int st = check_cuda(h, cudaLaunchKernelExC(&cfg, sk ? h->k_merge_sk : h->k_merge.fn, args));
+    const int st = check_cuda(h, cudaLaunchKernelExC(&cfg, many ? h->k_merge_many : (sk ? h->k_merge_sk : h->k_merge.fn), args));
     if (st == DX_OK)
         h->launches.fetch_add(1);
     return st;
@@ -1072,6 +1094,9 @@ int dx_attn_create(const dx_attn_config* config, dx_attn_t** out)
         h->k_mha = mha_kernel_info(c.type_id, h->cache_kind, c.head_size, c.tokens_per_block);
         h->k_merge = merge_kernel_info(c.type_id, c.head_size);
         h->k_merge_sk = merge_sk_kernel(c.type_id, c.head_size);
+        h->k_merge_many = merge_many_kernel(c.type_id, c.head_size);
+        if (const char* w = getenv("DX_ATTN_MERGE_MANY_FROM"))
+            h->merge_many_from = std::max(0, atoi(w));
         h->k_append = append_kernel_info(c.type_id, h->cache_kind, c.head_size);
         h->k_general = general_kernel_info(c.type_id, h->cache_kind, c.head_size);
         const char* g16 = getenv("DX_ATTN_GQA16"); // "0": grouped heads over a 16-bit cache stay on the per-head kernel

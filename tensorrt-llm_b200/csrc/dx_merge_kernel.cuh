@@ -150,6 +150,92 @@ __global__ void __launch_bounds__(128) lse_merge_kernel(const AttnArgs a)
     merge_row<T, DH>(a, row, n, lane);
 }
 
+// Many partitions per row (long sequences in a small batch): one CTA per q row instead of one warp.  Warp w merges
+// partitions w, w + 4, ... into a state of its own (8 row loads in flight per round, a quarter of the rounds of the
+// one-warp form), the four states meet in shared memory.  Same arithmetic, same result up to the order of the sums.
+template <typename T, int DH>
+__global__ void __launch_bounds__(128) lse_merge_many_kernel(const AttnArgs a)
+{
+    griddep_launch_dependents(); // the next step's attention grid may become resident; it waits for this grid
+    constexpr int VPL = DH / 32;
+    __shared__ float st_o[4][DH];
+    __shared__ float st_ml[4][2];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x; // b * H + h (x new tokens)
+    const int b = row / (a.num_heads * max(1, a.q_len));
+    const int total = attended_tokens(a.seq_len[b], a.cyclic_window);
+    griddep_wait();
+    const int n = max(1, min((total + a.chunk_tokens - 1) / a.chunk_tokens, a.nsplit));
+    const float2* ml = a.part_ml + (size_t) row * a.nsplit;
+    const float* po = a.part_o + (size_t) row * a.nsplit * DH + lane * VPL;
+    const int nw = (n - warp + 3) / 4; // partitions of this warp: warp + 4 j, j < nw (may be 0)
+    float M = -INFINITY;
+    for (int j0 = 0; j0 < nw; j0 += 32)
+        if (j0 + lane < nw)
+            M = fmaxf(M, __ldcg(ml + warp + 4 * (j0 + lane)).x);
+#pragma unroll
+    for (int x = 16; x >= 1; x >>= 1)
+        M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, x));
+    float L = 0.f, o[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i)
+        o[i] = 0.f;
+    for (int j0 = 0; j0 < nw; j0 += 32)
+    {
+        float f = 0.f, lw = 0.f; // lane j holds the weight of this warp's partition j0 + j
+        if (j0 + lane < nw)
+        {
+            const float2 v = __ldcg(ml + warp + 4 * (j0 + lane));
+            f = (v.x == -INFINITY) ? 0.f : fast_exp2(v.x - M);
+            lw = v.y * f;
+        }
+        L += lw;
+        const int cnt = min(32, nw - j0);
+        for (int k0 = 0; k0 < cnt; k0 += 8)
+        {
+            float v[8][VPL];
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                load_partial<VPL>(po + (size_t) (warp + 4 * min(j0 + k0 + k, nw - 1)) * DH, v[k]);
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+            {
+                float fk = __shfl_sync(0xffffffffu, f, (k0 + k) & 31);
+                if (k0 + k >= cnt)
+                    fk = 0.f;
+#pragma unroll
+                for (int i = 0; i < VPL; ++i)
+                    o[i] = fmaf(v[k][i], fk, o[i]);
+            }
+        }
+    }
+#pragma unroll
+    for (int x = 16; x >= 1; x >>= 1)
+        L += __shfl_xor_sync(0xffffffffu, L, x);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i)
+        st_o[warp][lane * VPL + i] = o[i];
+    if (lane == 0)
+        st_ml[warp][0] = M, st_ml[warp][1] = L;
+    __syncthreads();
+    for (int d = threadIdx.x; d < DH; d += blockDim.x)
+    {
+        float Mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+            Mx = fmaxf(Mx, st_ml[w][0]);
+        float Lx = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+        {
+            const float f = (st_ml[w][0] == -INFINITY) ? 0.f : fast_exp2(st_ml[w][0] - Mx);
+            Lx = fmaf(st_ml[w][1], f, Lx);
+            acc = fmaf(st_o[w][d], f, acc);
+        }
+        reinterpret_cast<T*>(a.out)[(size_t) row * DH + d] = TypeOps<T>::from_float(acc / Lx);
+    }
+}
+
 // Stream-K launches: a row cut into several pieces has one partial per piece; rows that one CTA covered alone
 // were written out by the attention kernel.
 template <typename T, int DH>

@@ -102,3 +102,15 @@ def test_eight_generation_steps(pkg):
         assert err.max().item() < MAX_ABS_TOL and err.mean().item() < MEAN_ABS_TOL
         past = past + 1
     plugin.close()
+
+
+@pytest.mark.parametrize("cache,heads,dh", [("fp8", (8, 2), 128), ("int8", (4, 4), 64), ("none", (8, 2), 128)])
+def test_many_partitions_per_row_are_merged_by_a_cta_per_row(pkg, cache, heads, dh, monkeypatch):
+    """With 32 or more partitions the merge runs one CTA per q row (four warps share the partitions): forced here
+    with 128-token partitions over sequences of up to 6000 tokens, a ragged batch, against the oracle."""
+    monkeypatch.setenv("DX_ATTN_FORCE_CHUNK", "128")
+    wl = workloads
+    cfg = wl.DecodeConfig("many", 3, heads[0], heads[1], dh, torch.bfloat16 if dh == 128 else torch.float16, cache, 64,
+                          1, 6000, True, 4321)
+    res = gpu_step_and_compare(pkg, cfg, lengths=torch.tensor([130, 4200, 6000], dtype=torch.int32))
+    assert res["plan"]["num_partitions"] >= 32, res["plan"]
